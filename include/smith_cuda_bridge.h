@@ -1,0 +1,187 @@
+/*
+ * smith_cuda_bridge.h -- flat C ABI of libsmith_cuda.so, the CUDA (sm_100a)
+ * replacement for Smith's Metal bridge on the quantized-matmul path.
+ *
+ * Part 1 keeps, name for name and argument for argument, the functions the
+ * reference declares in native/gpu_bridge.h and binds in src/device.js:10-50,
+ * so the JS host can dlopen this library instead of libsmith.dylib.  Each
+ * declaration cites the reference declaration it replaces.
+ *
+ * Part 2 is additive: things a CUDA device needs that unified-memory Metal
+ * did not (explicit residency, an error channel, device packers, a direct
+ * matmul entry, CUDA-graph capture, multi-GPU helpers).
+ *
+ * No C++ or framework types cross this boundary: pointers, sizes, integers.
+ *
+ * Memory model.  SMITH_SHARED buffers are page-locked host memory; the pointer
+ * from smith_buffer_contents() is a plain host pointer, valid for the life of
+ * the buffer, exactly what the JS side wraps in an ArrayBuffer.  A dispatch of
+ * a registered kernel copies its SHARED inputs host->device before the launch
+ * and its SHARED outputs device->host after it, on the context's stream, so
+ * the host view is coherent whenever a synchronous end_* call returns.
+ * SMITH_PRIVATE buffers live in device memory only.  A SHARED buffer that holds
+ * long-lived data (packed weights) can be pinned on the device with
+ * smith_buffer_make_resident(); it is then read from the device copy and is no
+ * longer re-uploaded on every dispatch.
+ */
+#ifndef SMITH_CUDA_BRIDGE_H
+#define SMITH_CUDA_BRIDGE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMITH_SHARED 0  /* host-visible, staged to the device per dispatch (native/gpu_bridge.h:12) */
+#define SMITH_PRIVATE 1 /* device memory only                              (native/gpu_bridge.h:13) */
+
+/* ===================== Part 1: the reference's bridge surface ===================== */
+
+/* native/gpu_bridge.h:18.  Creates the context on the device named by the
+ * environment (SMITH_CUDA_DEVICE, else LOCAL_RANK, else 0).  NULL on failure. */
+void* smith_init(void);
+/* native/gpu_bridge.h:21 */
+void smith_destroy(void* ctx);
+
+/* native/gpu_bridge.h:26.  malloc'd string, caller frees. */
+char* smith_device_name(void* ctx);
+/* native/gpu_bridge.h:29.  Largest opt-in dynamic shared memory per block, bytes. */
+uint64_t smith_max_threadgroup_memory(void* ctx);
+/* native/gpu_bridge.h:32 */
+uint64_t smith_max_threads_per_threadgroup(void* ctx);
+
+/* native/gpu_bridge.h:37.  Returns an opaque buffer handle (not the data pointer). */
+void* smith_alloc(void* ctx, uint64_t bytes, uint32_t mode);
+/* native/gpu_bridge.h:40.  Host pointer for SHARED buffers, NULL for PRIVATE. */
+void* smith_buffer_contents(void* buffer);
+/* native/gpu_bridge.h:43 */
+uint64_t smith_buffer_length(void* buffer);
+/* native/gpu_bridge.h:46.  Drops one reference; frees at zero. */
+void smith_release_buffer(void* buffer);
+/* native/gpu_bridge.h:127.  -1 for NULL. */
+int64_t smith_buffer_retain_count(void* buffer);
+
+/* native/gpu_bridge.h:49 and :52.  Allocate 1 MiB, (use it in a launch,) release;
+ * return the bytes that came back. */
+int64_t smith_test_release(void* ctx);
+int64_t smith_test_release_after_use(void* ctx);
+
+/* native/gpu_bridge.h:57.  The kernels are compiled into this library, so the
+ * path is not opened; a handle to the built-in registry is returned. */
+void* smith_load_library(void* ctx, const char* path);
+/* native/gpu_bridge.h:61.  Run-time compilation is not offered: returns NULL and,
+ * if error_out is non-NULL, a malloc'd message. */
+void* smith_compile_source(void* ctx, const char* source, char** error_out);
+/* native/gpu_bridge.h:64.  Known names: "matmul_q4", "matmul_q8" (buffers 0=A
+ * f32 [M,K], 1=packed B, 2=C f32 [M,N]; bytes at 3 = uint32 {M,N,K,groups}, as
+ * src/ops/quantize.js:80-87 binds them) and the new "quantize_q4",
+ * "quantize_q8" (buffers 0=W f32 [K,N], 1=packed out; bytes at 2 = uint32
+ * {K,N}).  NULL for anything else. */
+void* smith_create_pipeline(void* ctx, void* library, const char* fn_name);
+
+typedef struct SmithEncoder SmithEncoder;
+
+/* native/gpu_bridge.h:72 */
+SmithEncoder* smith_begin(void* ctx);
+/* native/gpu_bridge.h:75 */
+void smith_set_buffer(SmithEncoder* enc, void* buffer, uint32_t index);
+/* native/gpu_bridge.h:78.  The bytes are copied at call time. */
+void smith_set_bytes(SmithEncoder* enc, const void* data, uint32_t length, uint32_t index);
+/* native/gpu_bridge.h:81 */
+void smith_set_pipeline(SmithEncoder* enc, void* pipeline);
+/* native/gpu_bridge.h:85.  Accepted and ignored: the CUDA launchers size their own shared memory. */
+void smith_set_threadgroup_memory(SmithEncoder* enc, uint64_t length, uint32_t index);
+/* native/gpu_bridge.h:88-90.  The Metal thread grid is recorded but the CUDA
+ * launch geometry is derived from the bound parameters. */
+void smith_dispatch(SmithEncoder* enc, uint64_t grid_x, uint64_t grid_y, uint64_t grid_z,
+                    uint64_t group_x, uint64_t group_y, uint64_t group_z);
+/* native/gpu_bridge.h:93.  Stage in, launch, stage out, wait.  Frees enc. */
+void smith_end_sync(SmithEncoder* enc);
+/* native/gpu_bridge.h:96 and :99.  Submit without waiting; smith_wait(token) waits and frees the token. */
+void* smith_end_async(SmithEncoder* enc);
+void smith_wait(void* token);
+
+/* native/gpu_bridge.h:104-108 */
+void smith_dispatch_sync(void* ctx, void* pipeline, void** buffers, uint32_t* indices,
+                         uint32_t buffer_count, const void* params, uint32_t params_length,
+                         uint32_t params_index, uint64_t grid_x, uint64_t grid_y, uint64_t grid_z,
+                         uint64_t group_x, uint64_t group_y, uint64_t group_z);
+
+/* native/gpu_bridge.h:113-117.  Seconds, seconds, milliseconds; start/end are
+ * measured from context creation with CUDA events placed around the kernels. */
+typedef struct {
+  double gpu_start;
+  double gpu_end;
+  double gpu_ms;
+} SmithTiming;
+
+/* native/gpu_bridge.h:121.  calloc'd, caller frees; NULL on failure. */
+SmithTiming* smith_end_timed(SmithEncoder* enc);
+/* native/gpu_bridge.h:124.  Device bytes currently held through this context. */
+uint64_t smith_allocated_size(void* ctx);
+
+/* ===================== Part 2: additions (no reference counterpart) ===================== */
+
+/* Error channel for the void functions above: message of the most recent
+ * failure on the calling thread ("" if none).  Status-returning functions
+ * below return 0 on success and non-zero on failure, and also set it. */
+const char* smith_last_error(void);
+void smith_clear_error(void);
+
+int32_t smith_device_count(void);
+void* smith_init_device(int32_t device); /* context on an explicit device */
+int32_t smith_device_index(void* ctx);
+void* smith_stream(void* ctx);           /* the context's cudaStream_t */
+int32_t smith_synchronize(void* ctx);
+
+/* Device address backing a buffer (PRIVATE, wrapped or resident SHARED), else NULL. */
+void* smith_buffer_device_ptr(void* buffer);
+/* Keep a device copy of a SHARED buffer and read from it in later dispatches
+ * (uploads the current host contents now).  smith_buffer_evict drops it. */
+int32_t smith_buffer_make_resident(void* buffer);
+int32_t smith_buffer_evict(void* buffer);
+/* Buffer handle over device memory owned by someone else (not freed on release). */
+void* smith_wrap_device_memory(void* ctx, void* device_ptr, uint64_t bytes);
+/* Blocking copies between host memory and any buffer's device side. */
+int32_t smith_upload(void* buffer, uint64_t offset, const void* host, uint64_t bytes);
+int32_t smith_download(void* buffer, uint64_t offset, void* host, uint64_t bytes);
+
+/* Device packers: W f32 [K,N] (device side of w) -> packed blocks (device side
+ * of out).  Q4 reproduces src/ops/quantize.js:14-68 bit for bit; Q8 is the
+ * build-defined rule documented with the kernel.  Asynchronous on the
+ * context's stream. */
+int32_t smith_q4_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
+int32_t smith_q8_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
+
+/* Direct, asynchronous C[M,N] = A[M,K] * dequant(B) on device-side buffers.
+ * kind: 4 or 8.  path: 0 = choose by shape, 1 = any-shape CUDA-core kernel,
+ * 2 = decode kernel (M <= 16), 3 = tensor-core (tcgen05) kernel. */
+#define SMITH_PATH_AUTO 0
+#define SMITH_PATH_GENERIC 1
+#define SMITH_PATH_DECODE 2
+#define SMITH_PATH_TENSOR 3
+int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint64_t M, uint64_t N,
+                      uint64_t K, uint64_t groups, uint32_t path);
+/* Which path 0 would resolve to for a shape (for tests and reports). */
+int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
+/* How many kernels this context has launched so far. */
+uint64_t smith_launch_count(void* ctx);
+
+/* CUDA-graph capture of a sequence of the asynchronous calls above. */
+int32_t smith_graph_begin(void* ctx);
+void* smith_graph_end(void* ctx); /* executable graph handle, NULL on failure */
+int32_t smith_graph_launch(void* ctx, void* graph);
+void smith_graph_destroy(void* graph);
+
+/* Synthetic data on the device: f32 ~ N(0, std) from a counter-based generator
+ * keyed by (seed, element index); for benchmarks and large-shape tests. */
+int32_t smith_fill_normal(void* ctx, void* buffer, uint64_t count, uint64_t seed, float std);
+/* Writes `bytes` of a scratch buffer to push earlier data out of L2. */
+int32_t smith_flush_l2(void* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMITH_CUDA_BRIDGE_H */

@@ -1,0 +1,167 @@
+"""ctypes front-end of the CPU checkers.  TEST INFRASTRUCTURE ONLY.
+
+Loads ``oracle/liboracle.so`` (this repository's C restatement of the
+reference's quantizeQ4 / matmul_q4 / matmul_q8 arithmetic plus the build-defined
+quantizeQ8) and, when it has been built, ``oracle/_ref/libsmith_ref.so`` (the
+reference's own shader source compiled as C++).  Nothing in the shipped package
+imports this module: it is the checker for the tests, the smoke check and the
+benchmark's CPU-baseline leg.
+
+Reference locations restated by the C side: src/ops/quantize.js:14-68,
+src/dtype.js:29-79, shaders/matmul_q4.metal:24-65, shaders/matmul_q8.metal:20-57.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "liboracle.so")
+_REF = os.path.join(_HERE, "_ref", "libsmith_ref.so")
+
+Q4_GROUP, Q4_BYTES = 32, 24
+Q8_GROUP, Q8_BYTES = 32, 34
+
+
+def build(quiet=True):
+    """Compile the checkers with the recipe in oracle/Makefile."""
+    subprocess.run(["make", "-C", _HERE], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def _load(path):
+    lib = C.CDLL(path)
+    return lib
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB):
+            build()
+        _lib = _load(_LIB)
+        i64, p = C.c_int64, C.c_void_p
+        _lib.oracle_quantize_q4.restype = i64
+        _lib.oracle_quantize_q4.argtypes = [p, i64, i64, p]
+        _lib.oracle_quantize_q8.restype = i64
+        _lib.oracle_quantize_q8.argtypes = [p, i64, i64, p]
+        _lib.oracle_to_float16.restype = C.c_uint16
+        _lib.oracle_to_float16.argtypes = [C.c_double]
+        _lib.oracle_from_float16.restype = C.c_double
+        _lib.oracle_from_float16.argtypes = [C.c_uint16]
+        for name in ("oracle_dequant_q4", "oracle_dequant_q8"):
+            f = getattr(_lib, name)
+            f.restype = None
+            f.argtypes = [p, i64, i64, p]
+        for name in ("oracle_matmul_q4", "oracle_matmul_q8"):
+            f = getattr(_lib, name)
+            f.restype = None
+            f.argtypes = [p, p, p, i64, i64, i64, i64, i64, i64, C.c_int]
+        _lib.oracle_max_threads.restype = C.c_int
+    return _lib
+
+
+def have_ref():
+    return os.path.exists(_REF)
+
+
+def ref():
+    """The reference's shader source compiled as C++ (None when not built)."""
+    global _ref
+    if _ref is None and have_ref():
+        _ref = _load(_REF)
+        i64, p = C.c_int64, C.c_void_p
+        for name in ("ref_matmul_q4", "ref_matmul_q8"):
+            f = getattr(_ref, name)
+            f.restype = None
+            f.argtypes = [p, p, p, i64, i64, i64, i64, i64, i64, C.c_int]
+        _ref.ref_max_threads.restype = C.c_int
+    return _ref
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32_2d(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    assert a.ndim == 2
+    return a
+
+
+def groups_of(K):
+    return (K + 31) // 32
+
+
+def quantize_q4(w):
+    """f32 [K,N] -> uint8 [groups*N*24], the reference's Q4 block layout."""
+    w = _f32_2d(w)
+    K, N = w.shape
+    out = np.zeros(groups_of(K) * N * Q4_BYTES, dtype=np.uint8)
+    lib().oracle_quantize_q4(_ptr(w), K, N, _ptr(out))
+    return out
+
+
+def quantize_q8(w):
+    """f32 [K,N] -> uint8 [groups*N*34], the layout matmul_q8 consumes."""
+    w = _f32_2d(w)
+    K, N = w.shape
+    out = np.zeros(groups_of(K) * N * Q8_BYTES, dtype=np.uint8)
+    lib().oracle_quantize_q8(_ptr(w), K, N, _ptr(out))
+    return out
+
+
+def to_float16(v):
+    return int(lib().oracle_to_float16(float(v)))
+
+
+def from_float16(h):
+    return float(lib().oracle_from_float16(int(h)))
+
+
+def dequant(packed, K, N, kind):
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    w = np.zeros((K, N), dtype=np.float32)
+    getattr(lib(), "oracle_dequant_" + kind)(_ptr(packed), K, N, _ptr(w))
+    return w
+
+
+def _matmul(fn, a, packed, K, N, groups, cols, threads):
+    a = _f32_2d(a)
+    M = a.shape[0]
+    assert a.shape[1] == K
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    groups = groups_of(K) if groups is None else groups
+    c0, c1 = (0, N) if cols is None else cols
+    out = np.zeros((M, N), dtype=np.float32)
+    fn(_ptr(a), _ptr(packed), _ptr(out), M, N, K, groups, c0, c1, int(threads))
+    return out
+
+
+def matmul(a, packed, K, N, kind, groups=None, cols=None, threads=1):
+    """Sequential-f32 shader arithmetic on the CPU (this repository's restatement)."""
+    return _matmul(getattr(lib(), "oracle_matmul_" + kind), a, packed, K, N, groups, cols, threads)
+
+
+def ref_matmul(a, packed, K, N, kind, groups=None, cols=None, threads=1):
+    """Same call served by the reference's compiled shader source."""
+    r = ref()
+    if r is None:
+        raise RuntimeError("oracle/_ref/libsmith_ref.so has not been built")
+    return _matmul(getattr(r, "ref_matmul_" + kind), a, packed, K, N, groups, cols, threads)
+
+
+def max_threads():
+    return int(lib().oracle_max_threads())
+
+
+def tolerance_bound(a, w_deq, rel=1e-3):
+    """Per-output bound rel * ||a_m||_2 * ||w_deq[:,n]||_2  ->  [M,N] float64."""
+    an = np.linalg.norm(np.asarray(a, dtype=np.float64), axis=1)
+    wn = np.linalg.norm(np.asarray(w_deq, dtype=np.float64), axis=0)
+    return rel * an[:, None] * wn[None, :]

@@ -1,0 +1,860 @@
+// bridge.cu -- the C ABI of libsmith_cuda.so (declared in include/smith_cuda_bridge.h).
+//
+// Mirrors the reference's Metal bridge (native/gpu_bridge.m) function for
+// function: context, buffers, a "library" that is the built-in kernel
+// registry, pipelines looked up by kernel name, an encoder that records
+// pipeline + bound buffers + inline bytes, and sync / async / timed
+// submission.  The CUDA-specific part is the memory model: SHARED buffers are
+// page-locked host memory that the launchers stage to and from the device
+// around each dispatch; PRIVATE, wrapped and resident buffers are read and
+// written in place on the device.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/smith_cuda_bridge.h"
+#include "kernels.h"
+
+using namespace smith;
+
+namespace {
+
+constexpr uint32_t kCtxMagic = 0x534D4358;  // "SMCX"
+constexpr uint32_t kBufMagic = 0x534D4246;  // "SMBF"
+constexpr uint32_t kPsoMagic = 0x534D5053;  // "SMPS"
+constexpr uint32_t kLibMagic = 0x534D4C42;  // "SMLB"
+constexpr int kMaxBind = 8;
+
+thread_local std::string g_err;
+
+int fail(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return 1;
+}
+
+#define CU_TRY(expr)                                                              \
+  do {                                                                            \
+    cudaError_t e_ = (expr);                                                      \
+    if (e_ != cudaSuccess) return fail("%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+enum KernelId { kMatmulQ4 = 0, kMatmulQ8 = 1, kQuantQ4 = 2, kQuantQ8 = 3, kNumKernels };
+const char* const kKernelNames[kNumKernels] = {"matmul_q4", "matmul_q8", "quantize_q4", "quantize_q8"};
+
+struct Context {
+  uint32_t magic = kCtxMagic;
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t base = nullptr;
+  std::atomic<uint64_t> held{0};  // bytes held by live buffers + arenas
+  uint64_t launches = 0;
+  void* stage[3] = {nullptr, nullptr, nullptr};
+  size_t stage_bytes[3] = {0, 0, 0};
+  Workspace ws;
+  void* flush = nullptr;
+  size_t flush_bytes = 0;
+  bool capturing = false;
+  char name[256] = {0};
+  uint64_t smem_optin = 0;
+  uint64_t max_threads = 0;
+};
+
+struct Buffer {
+  uint32_t magic = kBufMagic;
+  Context* ctx = nullptr;
+  uint64_t bytes = 0;
+  uint32_t mode = SMITH_SHARED;
+  void* host = nullptr;   // SHARED: page-locked host memory
+  void* dev = nullptr;    // PRIVATE / wrapped / resident SHARED
+  bool owns_dev = false;
+  bool wrapped = false;
+  bool resident = false;
+  std::atomic<int64_t> refs{1};
+};
+
+struct Library {
+  uint32_t magic = kLibMagic;
+};
+Library g_library;
+
+struct Pipeline {
+  uint32_t magic = kPsoMagic;
+  int id = 0;
+};
+Pipeline g_pipelines[kNumKernels];
+
+struct Graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};
+
+struct Token {
+  Context* ctx;
+  cudaEvent_t done;
+};
+
+Context* as_ctx(void* p) {
+  Context* c = static_cast<Context*>(p);
+  if (!c || c->magic != kCtxMagic) {
+    fail("not a smith context");
+    return nullptr;
+  }
+  cudaSetDevice(c->device);
+  g_launch_counter = &c->launches;
+  return c;
+}
+
+Buffer* as_buf(void* p) {
+  Buffer* b = static_cast<Buffer*>(p);
+  if (!b || b->magic != kBufMagic) {
+    fail("not a smith buffer");
+    return nullptr;
+  }
+  return b;
+}
+
+int grow(Context* c, void** ptr, size_t* have, size_t need) {
+  if (*have >= need) return 0;
+  if (c->capturing) return fail("scratch memory must be sized before graph capture (need %zu bytes)", need);
+  size_t want = need + need / 4;
+  want = (want + 255) & ~size_t(255);
+  if (*ptr) {
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    CU_TRY(cudaFree(*ptr));
+    c->held -= *have;
+    *ptr = nullptr;
+    *have = 0;
+  }
+  CU_TRY(cudaMalloc(ptr, want));
+  *have = want;
+  c->held += want;
+  return 0;
+}
+
+int env_device() {
+  const char* names[2] = {"SMITH_CUDA_DEVICE", "LOCAL_RANK"};
+  for (const char* n : names) {
+    const char* v = getenv(n);
+    if (v && *v) return atoi(v);
+  }
+  return 0;
+}
+
+void* make_context(int device) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+    fail("no CUDA device available");
+    return nullptr;
+  }
+  if (device < 0 || device >= count) {
+    fail("device %d out of range (%d visible)", device, count);
+    return nullptr;
+  }
+  if (cudaSetDevice(device) != cudaSuccess) {
+    fail("cudaSetDevice(%d) failed", device);
+    return nullptr;
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    fail("cudaGetDeviceProperties failed");
+    return nullptr;
+  }
+  if (prop.major != 10) {
+    fail("device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major, prop.minor);
+    return nullptr;
+  }
+  Context* c = new Context();
+  c->device = device;
+  snprintf(c->name, sizeof c->name, "%s", prop.name);
+  c->smem_optin = prop.sharedMemPerBlockOptin;
+  c->max_threads = (uint64_t)prop.maxThreadsPerBlock;
+  if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreate(&c->base) != cudaSuccess || cudaEventRecord(c->base, c->stream) != cudaSuccess) {
+    fail("stream/event creation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    delete c;
+    return nullptr;
+  }
+  return c;
+}
+
+// Device address a launch should read input `b` from.  SHARED buffers without
+// a device copy are uploaded into staging slot `slot` first.
+int input_ptr(Context* c, Buffer* b, int slot, size_t need, const void** out) {
+  if (b->bytes < need) return fail("buffer at index %d holds %llu bytes, the launch needs %zu", slot,
+                                   (unsigned long long)b->bytes, need);
+  if (b->dev && (b->mode == SMITH_PRIVATE || b->wrapped || b->resident)) {
+    *out = b->dev;
+    return 0;
+  }
+  if (!b->host) return fail("buffer at index %d has neither host nor device memory", slot);
+  if (grow(c, &c->stage[slot], &c->stage_bytes[slot], need)) return 1;
+  if (need) CU_TRY(cudaMemcpyAsync(c->stage[slot], b->host, need, cudaMemcpyHostToDevice, c->stream));
+  *out = c->stage[slot];
+  return 0;
+}
+
+// Device address a launch should write output `b` to, and whether the result
+// has to be copied back to the host view afterwards.
+int output_ptr(Context* c, Buffer* b, int slot, size_t need, void** out, bool* copy_back) {
+  if (b->bytes < need) return fail("output buffer at index %d holds %llu bytes, the launch needs %zu", slot,
+                                   (unsigned long long)b->bytes, need);
+  *copy_back = (b->mode == SMITH_SHARED && !b->wrapped && b->host != nullptr);
+  if (b->dev && (b->mode == SMITH_PRIVATE || b->wrapped || b->resident)) {
+    *out = b->dev;
+    return 0;
+  }
+  if (grow(c, &c->stage[slot], &c->stage_bytes[slot], need)) return 1;
+  *out = c->stage[slot];
+  return 0;
+}
+
+int ensure_workspace(Context* c, size_t need) { return grow(c, &c->ws.ptr, &c->ws.bytes, need); }
+
+int do_qmatmul(Context* c, int kind, const float* A, const uint8_t* B, float* C, uint64_t M, uint64_t N,
+               uint64_t K, uint64_t groups, uint32_t path) {
+  if (kind != 4 && kind != 8) return fail("kind must be 4 or 8, got %d", kind);
+  if (M == 0 || N == 0) return 0;
+  int p = (int)path;
+  if (p == kAuto) p = resolve_path(kind, (int64_t)M, (int64_t)N, (int64_t)K, (int64_t)groups);
+  cudaError_t e;
+  switch (p) {
+    case kGeneric:
+      e = launch_qmatmul_generic(kind, A, B, C, M, N, K, groups, c->stream);
+      break;
+    case kDecode:
+      if (!qdecode_supports(kind, M, N, K, groups))
+        return fail("decode kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,
+                    (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
+      e = launch_qdecode(kind, A, B, C, M, N, K, groups, c->stream);
+      break;
+    case kTensor: {
+      if (!qgemm_tc_supports(kind, M, N, K, groups))
+        return fail("tensor-core kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,
+                    (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
+      if (ensure_workspace(c, qgemm_tc_workspace_bytes(kind, M, N, K))) return 1;
+      e = launch_qgemm_tc(kind, A, B, C, M, N, K, groups, c->ws, c->stream);
+      break;
+    }
+    default:
+      return fail("unknown path %u", path);
+  }
+  if (e != cudaSuccess) return fail("matmul_q%d launch failed: %s", kind, cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
+struct SmithEncoder {
+  Context* ctx = nullptr;
+  Pipeline* pso = nullptr;
+  Buffer* bufs[kMaxBind] = {nullptr};
+  std::vector<uint8_t> bytes[kMaxBind];
+  uint64_t grid[3] = {0, 0, 0}, group[3] = {0, 0, 0};
+  bool dispatched = false;
+};
+
+namespace {
+
+// Stage in, launch, stage out.  Events e0/e1 (optional) bracket the kernels only.
+int submit(SmithEncoder* enc, cudaEvent_t e0, cudaEvent_t e1) {
+  Context* c = as_ctx(enc->ctx);
+  if (!c) return 1;
+  if (!enc->pso) return fail("no pipeline set");
+  if (!enc->dispatched) return fail("smith_dispatch was not called");
+  const int id = enc->pso->id;
+  if (id == kMatmulQ4 || id == kMatmulQ8) {
+    const int kind = (id == kMatmulQ4) ? 4 : 8;
+    const size_t bb = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+    if (!enc->bufs[0] || !enc->bufs[1] || !enc->bufs[2]) return fail("matmul_q%d needs buffers 0, 1 and 2", kind);
+    if (enc->bytes[3].size() < 16) return fail("matmul_q%d needs 16 bytes {M,N,K,groups} at index 3", kind);
+    uint32_t prm[4];
+    memcpy(prm, enc->bytes[3].data(), 16);
+    const uint64_t M = prm[0], N = prm[1], K = prm[2], G = prm[3];
+    const void *a = nullptr, *b = nullptr;
+    void* cc = nullptr;
+    bool back = false;
+    if (input_ptr(c, enc->bufs[0], 0, M * K * 4, &a)) return 1;
+    if (input_ptr(c, enc->bufs[1], 1, G * N * bb, &b)) return 1;
+    if (output_ptr(c, enc->bufs[2], 2, M * N * 4, &cc, &back)) return 1;
+    if (e0) CU_TRY(cudaEventRecord(e0, c->stream));
+    if (do_qmatmul(c, kind, (const float*)a, (const uint8_t*)b, (float*)cc, M, N, K, G, kAuto)) return 1;
+    if (e1) CU_TRY(cudaEventRecord(e1, c->stream));
+    if (back && M * N)
+      CU_TRY(cudaMemcpyAsync(enc->bufs[2]->host, cc, M * N * 4, cudaMemcpyDeviceToHost, c->stream));
+    return 0;
+  }
+  if (id == kQuantQ4 || id == kQuantQ8) {
+    const int kind = (id == kQuantQ4) ? 4 : 8;
+    const size_t bb = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+    if (!enc->bufs[0] || !enc->bufs[1]) return fail("quantize_q%d needs buffers 0 and 1", kind);
+    if (enc->bytes[2].size() < 8) return fail("quantize_q%d needs 8 bytes {K,N} at index 2", kind);
+    uint32_t prm[2];
+    memcpy(prm, enc->bytes[2].data(), 8);
+    const uint64_t K = prm[0], N = prm[1], G = (K + 31) / 32;
+    const void* w = nullptr;
+    void* o = nullptr;
+    bool back = false;
+    if (input_ptr(c, enc->bufs[0], 0, K * N * 4, &w)) return 1;
+    if (output_ptr(c, enc->bufs[1], 1, G * N * bb, &o, &back)) return 1;
+    if (e0) CU_TRY(cudaEventRecord(e0, c->stream));
+    cudaError_t e = (kind == 4) ? launch_pack_q4((const float*)w, (uint8_t*)o, K, N, c->stream)
+                                : launch_pack_q8((const float*)w, (uint8_t*)o, K, N, c->stream);
+    if (e != cudaSuccess) return fail("quantize_q%d launch failed: %s", kind, cudaGetErrorString(e));
+    if (e1) CU_TRY(cudaEventRecord(e1, c->stream));
+    if (back && G * N)
+      CU_TRY(cudaMemcpyAsync(enc->bufs[1]->host, o, G * N * bb, cudaMemcpyDeviceToHost, c->stream));
+    return 0;
+  }
+  return fail("pipeline id %d has no launcher", id);
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------- lifecycle
+void* smith_init(void) { return make_context(env_device()); }
+void* smith_init_device(int32_t device) { return make_context(device); }
+
+void smith_destroy(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return;
+  cudaStreamSynchronize(c->stream);
+  for (int i = 0; i < 3; i++)
+    if (c->stage[i]) cudaFree(c->stage[i]);
+  if (c->ws.ptr) cudaFree(c->ws.ptr);
+  if (c->flush) cudaFree(c->flush);
+  cudaEventDestroy(c->base);
+  cudaStreamDestroy(c->stream);
+  c->magic = 0;
+  if (g_launch_counter == &c->launches) g_launch_counter = nullptr;
+  delete c;
+}
+
+const char* smith_last_error(void) { return g_err.c_str(); }
+void smith_clear_error(void) { g_err.clear(); }
+
+int32_t smith_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int32_t smith_device_index(void* p) {
+  Context* c = as_ctx(p);
+  return c ? c->device : -1;
+}
+
+void* smith_stream(void* p) {
+  Context* c = as_ctx(p);
+  return c ? (void*)c->stream : nullptr;
+}
+
+int32_t smith_synchronize(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return 1;
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+// ---------------------------------------------------------------- device info
+char* smith_device_name(void* p) {
+  Context* c = as_ctx(p);
+  const char* s = c ? c->name : "";
+  char* out = (char*)malloc(strlen(s) + 1);
+  if (out) strcpy(out, s);
+  return out;
+}
+
+uint64_t smith_max_threadgroup_memory(void* p) {
+  Context* c = as_ctx(p);
+  return c ? c->smem_optin : 0;
+}
+
+uint64_t smith_max_threads_per_threadgroup(void* p) {
+  Context* c = as_ctx(p);
+  return c ? c->max_threads : 0;
+}
+
+// ---------------------------------------------------------------- buffers
+void* smith_alloc(void* p, uint64_t bytes, uint32_t mode) {
+  Context* c = as_ctx(p);
+  if (!c) return nullptr;
+  if (mode != SMITH_SHARED && mode != SMITH_PRIVATE) {
+    fail("unknown storage mode %u", mode);
+    return nullptr;
+  }
+  Buffer* b = new Buffer();
+  b->ctx = c;
+  b->bytes = bytes;
+  b->mode = mode;
+  const size_t n = bytes ? (size_t)bytes : 1;
+  cudaError_t e;
+  if (mode == SMITH_SHARED) {
+    e = cudaHostAlloc(&b->host, n, cudaHostAllocPortable);
+  } else {
+    e = cudaMalloc(&b->dev, n);
+    b->owns_dev = true;
+  }
+  if (e != cudaSuccess) {
+    fail("allocation of %llu bytes (mode %u) failed: %s", (unsigned long long)bytes, mode, cudaGetErrorString(e));
+    cudaGetLastError();
+    delete b;
+    return nullptr;
+  }
+  c->held += bytes;
+  return b;
+}
+
+void* smith_buffer_contents(void* p) {
+  Buffer* b = as_buf(p);
+  return b ? b->host : nullptr;
+}
+
+uint64_t smith_buffer_length(void* p) {
+  Buffer* b = as_buf(p);
+  return b ? b->bytes : 0;
+}
+
+int64_t smith_buffer_retain_count(void* p) {
+  if (!p) return -1;
+  Buffer* b = as_buf(p);
+  return b ? b->refs.load() : -1;
+}
+
+void smith_release_buffer(void* p) {
+  if (!p) return;
+  Buffer* b = as_buf(p);
+  if (!b) return;
+  if (--b->refs > 0) return;
+  Context* c = b->ctx;
+  if (c && c->magic == kCtxMagic) {
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);  // nothing in flight may still touch it
+  }
+  uint64_t freed = 0;
+  if (b->host) {
+    cudaFreeHost(b->host);
+    freed += b->bytes;
+  }
+  if (b->dev && b->owns_dev) {
+    cudaFree(b->dev);
+    freed += b->bytes;
+  }
+  if (c && c->magic == kCtxMagic) c->held -= freed;
+  b->magic = 0;
+  delete b;
+}
+
+void* smith_buffer_device_ptr(void* p) {
+  Buffer* b = as_buf(p);
+  return b ? b->dev : nullptr;
+}
+
+int32_t smith_buffer_make_resident(void* p) {
+  Buffer* b = as_buf(p);
+  if (!b) return 1;
+  Context* c = as_ctx(b->ctx);
+  if (!c) return 1;
+  if (b->mode != SMITH_SHARED || b->wrapped) return 0;  // already device memory
+  if (!b->dev) {
+    CU_TRY(cudaMalloc(&b->dev, b->bytes ? b->bytes : 1));
+    b->owns_dev = true;
+    c->held += b->bytes;
+  }
+  if (b->bytes) CU_TRY(cudaMemcpyAsync(b->dev, b->host, b->bytes, cudaMemcpyHostToDevice, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  b->resident = true;
+  return 0;
+}
+
+int32_t smith_buffer_evict(void* p) {
+  Buffer* b = as_buf(p);
+  if (!b) return 1;
+  Context* c = as_ctx(b->ctx);
+  if (!c) return 1;
+  if (b->mode != SMITH_SHARED || b->wrapped || !b->dev) return 0;
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  CU_TRY(cudaFree(b->dev));
+  c->held -= b->bytes;
+  b->dev = nullptr;
+  b->owns_dev = false;
+  b->resident = false;
+  return 0;
+}
+
+void* smith_wrap_device_memory(void* p, void* device_ptr, uint64_t bytes) {
+  Context* c = as_ctx(p);
+  if (!c) return nullptr;
+  if (!device_ptr && bytes) {
+    fail("cannot wrap a null device pointer");
+    return nullptr;
+  }
+  Buffer* b = new Buffer();
+  b->ctx = c;
+  b->bytes = bytes;
+  b->mode = SMITH_PRIVATE;
+  b->dev = device_ptr;
+  b->wrapped = true;
+  return b;
+}
+
+int32_t smith_upload(void* p, uint64_t offset, const void* host, uint64_t bytes) {
+  Buffer* b = as_buf(p);
+  if (!b) return 1;
+  Context* c = as_ctx(b->ctx);
+  if (!c) return 1;
+  if (!b->dev) return fail("buffer has no device side");
+  if (offset + bytes > b->bytes) return fail("upload of %llu bytes at %llu overruns a %llu-byte buffer",
+                                             (unsigned long long)bytes, (unsigned long long)offset,
+                                             (unsigned long long)b->bytes);
+  if (bytes) CU_TRY(cudaMemcpyAsync((char*)b->dev + offset, host, bytes, cudaMemcpyHostToDevice, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+int32_t smith_download(void* p, uint64_t offset, void* host, uint64_t bytes) {
+  Buffer* b = as_buf(p);
+  if (!b) return 1;
+  Context* c = as_ctx(b->ctx);
+  if (!c) return 1;
+  if (!b->dev) return fail("buffer has no device side");
+  if (offset + bytes > b->bytes) return fail("download of %llu bytes at %llu overruns a %llu-byte buffer",
+                                             (unsigned long long)bytes, (unsigned long long)offset,
+                                             (unsigned long long)b->bytes);
+  if (bytes) CU_TRY(cudaMemcpyAsync(host, (const char*)b->dev + offset, bytes, cudaMemcpyDeviceToHost, c->stream));
+  CU_TRY(cudaStreamSynchronize(c->stream));
+  return 0;
+}
+
+int64_t smith_test_release(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return 0;
+  void* b = smith_alloc(p, 1048576, SMITH_SHARED);
+  if (!b) return 0;
+  const uint64_t after_alloc = c->held.load();
+  smith_release_buffer(b);
+  return (int64_t)(after_alloc - c->held.load());
+}
+
+int64_t smith_test_release_after_use(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return 0;
+  void* b = smith_alloc(p, 1048576, SMITH_PRIVATE);
+  if (!b) return 0;
+  const uint64_t after_alloc = c->held.load();
+  launch_fill_bytes(static_cast<Buffer*>(b)->dev, 1048576, 0u, c->stream);
+  cudaStreamSynchronize(c->stream);
+  smith_release_buffer(b);
+  return (int64_t)(after_alloc - c->held.load());
+}
+
+uint64_t smith_allocated_size(void* p) {
+  Context* c = as_ctx(p);
+  return c ? c->held.load() : 0;
+}
+
+// ---------------------------------------------------------------- library / pipelines
+void* smith_load_library(void* p, const char* path) {
+  (void)path;
+  return as_ctx(p) ? &g_library : nullptr;
+}
+
+void* smith_compile_source(void* p, const char* source, char** error_out) {
+  (void)p;
+  (void)source;
+  const char* msg = "run-time kernel compilation is not available in the CUDA bridge";
+  fail("%s", msg);
+  if (error_out) {
+    *error_out = (char*)malloc(strlen(msg) + 1);
+    if (*error_out) strcpy(*error_out, msg);
+  }
+  return nullptr;
+}
+
+void* smith_create_pipeline(void* p, void* library, const char* fn_name) {
+  if (!as_ctx(p)) return nullptr;
+  Library* l = static_cast<Library*>(library);
+  if (!l || l->magic != kLibMagic) {
+    fail("not a smith library handle");
+    return nullptr;
+  }
+  if (!fn_name) {
+    fail("kernel name is null");
+    return nullptr;
+  }
+  for (int i = 0; i < kNumKernels; i++)
+    if (strcmp(fn_name, kKernelNames[i]) == 0) {
+      g_pipelines[i].id = i;
+      return &g_pipelines[i];
+    }
+  fail("kernel '%s' not found", fn_name);
+  return nullptr;
+}
+
+// ---------------------------------------------------------------- encoder
+SmithEncoder* smith_begin(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return nullptr;
+  SmithEncoder* e = new SmithEncoder();
+  e->ctx = c;
+  return e;
+}
+
+void smith_set_buffer(SmithEncoder* enc, void* buffer, uint32_t index) {
+  if (!enc) return;
+  if (index >= kMaxBind) {
+    fail("buffer index %u out of range", index);
+    return;
+  }
+  enc->bufs[index] = as_buf(buffer);
+}
+
+void smith_set_bytes(SmithEncoder* enc, const void* data, uint32_t length, uint32_t index) {
+  if (!enc) return;
+  if (index >= kMaxBind) {
+    fail("bytes index %u out of range", index);
+    return;
+  }
+  const uint8_t* d = static_cast<const uint8_t*>(data);
+  enc->bytes[index].assign(d, d + (data ? length : 0));
+}
+
+void smith_set_pipeline(SmithEncoder* enc, void* pipeline) {
+  if (!enc) return;
+  Pipeline* q = static_cast<Pipeline*>(pipeline);
+  if (!q || q->magic != kPsoMagic) {
+    fail("not a smith pipeline");
+    enc->pso = nullptr;
+    return;
+  }
+  enc->pso = q;
+}
+
+void smith_set_threadgroup_memory(SmithEncoder* enc, uint64_t length, uint32_t index) {
+  (void)enc;
+  (void)length;
+  (void)index;
+}
+
+void smith_dispatch(SmithEncoder* enc, uint64_t gx, uint64_t gy, uint64_t gz, uint64_t tx, uint64_t ty,
+                    uint64_t tz) {
+  if (!enc) return;
+  enc->grid[0] = gx, enc->grid[1] = gy, enc->grid[2] = gz;
+  enc->group[0] = tx, enc->group[1] = ty, enc->group[2] = tz;
+  enc->dispatched = true;
+}
+
+void smith_end_sync(SmithEncoder* enc) {
+  if (!enc) return;
+  Context* c = enc->ctx;
+  if (submit(enc, nullptr, nullptr) == 0) {
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) fail("kernel execution failed: %s", cudaGetErrorString(e));
+  } else if (c && c->magic == kCtxMagic) {
+    cudaStreamSynchronize(c->stream);  // drain any staging copy already queued
+  }
+  delete enc;
+}
+
+void* smith_end_async(SmithEncoder* enc) {
+  if (!enc) return nullptr;
+  Context* c = enc->ctx;
+  Token* t = nullptr;
+  if (submit(enc, nullptr, nullptr) == 0) {
+    t = new Token{c, nullptr};
+    if (cudaEventCreateWithFlags(&t->done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventRecord(t->done, c->stream) != cudaSuccess) {
+      fail("could not record completion event");
+      delete t;
+      t = nullptr;
+      cudaStreamSynchronize(c->stream);
+    }
+  }
+  delete enc;
+  return t;
+}
+
+void smith_wait(void* token) {
+  if (!token) return;
+  Token* t = static_cast<Token*>(token);
+  cudaSetDevice(t->ctx->device);
+  cudaError_t e = cudaEventSynchronize(t->done);
+  if (e != cudaSuccess) fail("kernel execution failed: %s", cudaGetErrorString(e));
+  cudaEventDestroy(t->done);
+  delete t;
+}
+
+SmithTiming* smith_end_timed(SmithEncoder* enc) {
+  if (!enc) return nullptr;
+  Context* c = enc->ctx;
+  SmithTiming* out = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
+    if (submit(enc, e0, e1) == 0) {
+      cudaError_t e = cudaStreamSynchronize(c->stream);
+      float ms = 0.f, since = 0.f;
+      if (e == cudaSuccess && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess &&
+          cudaEventElapsedTime(&since, c->base, e0) == cudaSuccess) {
+        out = (SmithTiming*)calloc(1, sizeof(SmithTiming));
+        if (out) {
+          out->gpu_start = (double)since * 1e-3;
+          out->gpu_end = ((double)since + (double)ms) * 1e-3;
+          out->gpu_ms = (double)ms;
+        }
+      } else {
+        fail("timed dispatch failed: %s", cudaGetErrorString(e != cudaSuccess ? e : cudaGetLastError()));
+      }
+    } else if (c && c->magic == kCtxMagic) {
+      cudaStreamSynchronize(c->stream);
+    }
+  } else {
+    fail("could not create timing events");
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  delete enc;
+  return out;
+}
+
+void smith_dispatch_sync(void* ctx, void* pipeline, void** buffers, uint32_t* indices, uint32_t buffer_count,
+                         const void* params, uint32_t params_length, uint32_t params_index, uint64_t gx,
+                         uint64_t gy, uint64_t gz, uint64_t tx, uint64_t ty, uint64_t tz) {
+  SmithEncoder* enc = smith_begin(ctx);
+  if (!enc) return;
+  smith_set_pipeline(enc, pipeline);
+  for (uint32_t i = 0; i < buffer_count; i++) smith_set_buffer(enc, buffers[i], indices[i]);
+  if (params && params_length > 0) smith_set_bytes(enc, params, params_length, params_index);
+  smith_dispatch(enc, gx, gy, gz, tx, ty, tz);
+  smith_end_sync(enc);
+}
+
+// ---------------------------------------------------------------- direct entries
+int32_t smith_q4_pack(void* p, void* w, void* out, uint64_t K, uint64_t N) {
+  Context* c = as_ctx(p);
+  Buffer *bw = as_buf(w), *bo = as_buf(out);
+  if (!c || !bw || !bo) return 1;
+  if (!bw->dev || !bo->dev) return fail("smith_q4_pack needs buffers with a device side");
+  const uint64_t G = (K + 31) / 32;
+  if (bw->bytes < K * N * 4 || bo->bytes < G * N * kQ4Bytes) return fail("smith_q4_pack: buffer too small");
+  cudaError_t e = launch_pack_q4((const float*)bw->dev, (uint8_t*)bo->dev, K, N, c->stream);
+  return e == cudaSuccess ? 0 : fail("pack_q4 launch failed: %s", cudaGetErrorString(e));
+}
+
+int32_t smith_q8_pack(void* p, void* w, void* out, uint64_t K, uint64_t N) {
+  Context* c = as_ctx(p);
+  Buffer *bw = as_buf(w), *bo = as_buf(out);
+  if (!c || !bw || !bo) return 1;
+  if (!bw->dev || !bo->dev) return fail("smith_q8_pack needs buffers with a device side");
+  const uint64_t G = (K + 31) / 32;
+  if (bw->bytes < K * N * 4 || bo->bytes < G * N * kQ8Bytes) return fail("smith_q8_pack: buffer too small");
+  cudaError_t e = launch_pack_q8((const float*)bw->dev, (uint8_t*)bo->dev, K, N, c->stream);
+  return e == cudaSuccess ? 0 : fail("pack_q8 launch failed: %s", cudaGetErrorString(e));
+}
+
+int32_t smith_qmatmul(void* p, uint32_t kind, void* a, void* b, void* cbuf, uint64_t M, uint64_t N, uint64_t K,
+                      uint64_t groups, uint32_t path) {
+  Context* c = as_ctx(p);
+  Buffer *ba = as_buf(a), *bb = as_buf(b), *bc = as_buf(cbuf);
+  if (!c || !ba || !bb || !bc) return 1;
+  if (!ba->dev || !bb->dev || !bc->dev) return fail("smith_qmatmul needs buffers with a device side");
+  const uint64_t blk = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  if (ba->bytes < M * K * 4) return fail("smith_qmatmul: A holds %llu bytes, needs %llu", (unsigned long long)ba->bytes,
+                                         (unsigned long long)(M * K * 4));
+  if (bb->bytes < groups * N * blk) return fail("smith_qmatmul: B holds %llu bytes, needs %llu",
+                                                (unsigned long long)bb->bytes, (unsigned long long)(groups * N * blk));
+  if (bc->bytes < M * N * 4) return fail("smith_qmatmul: C holds %llu bytes, needs %llu", (unsigned long long)bc->bytes,
+                                         (unsigned long long)(M * N * 4));
+  return do_qmatmul(c, (int)kind, (const float*)ba->dev, (const uint8_t*)bb->dev, (float*)bc->dev, M, N, K, groups, path);
+}
+
+int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
+  return resolve_path((int)kind, (int64_t)M, (int64_t)N, (int64_t)K, (int64_t)((K + 31) / 32));
+}
+
+uint64_t smith_launch_count(void* p) {
+  Context* c = as_ctx(p);
+  return c ? c->launches : 0;
+}
+
+// ---------------------------------------------------------------- graphs
+int32_t smith_graph_begin(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return 1;
+  if (c->capturing) return fail("a capture is already open on this context");
+  CU_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+  c->capturing = true;
+  return 0;
+}
+
+void* smith_graph_end(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return nullptr;
+  if (!c->capturing) {
+    fail("no capture is open on this context");
+    return nullptr;
+  }
+  c->capturing = false;
+  Graph* g = new Graph();
+  cudaError_t e = cudaStreamEndCapture(c->stream, &g->graph);
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+  if (e != cudaSuccess) {
+    fail("graph capture failed: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    return nullptr;
+  }
+  return g;
+}
+
+int32_t smith_graph_launch(void* p, void* graph) {
+  Context* c = as_ctx(p);
+  Graph* g = static_cast<Graph*>(graph);
+  if (!c || !g || !g->exec) return fail("invalid graph handle");
+  CU_TRY(cudaGraphLaunch(g->exec, c->stream));
+  return 0;
+}
+
+void smith_graph_destroy(void* graph) {
+  Graph* g = static_cast<Graph*>(graph);
+  if (!g) return;
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  delete g;
+}
+
+// ---------------------------------------------------------------- synthetic data / cache flush
+int32_t smith_fill_normal(void* p, void* buffer, uint64_t count, uint64_t seed, float std) {
+  Context* c = as_ctx(p);
+  Buffer* b = as_buf(buffer);
+  if (!c || !b) return 1;
+  if (!b->dev) return fail("smith_fill_normal needs a buffer with a device side");
+  if (b->bytes < count * 4) return fail("smith_fill_normal: buffer too small");
+  cudaError_t e = launch_fill_normal((float*)b->dev, count, seed, std, c->stream);
+  return e == cudaSuccess ? 0 : fail("fill_normal launch failed: %s", cudaGetErrorString(e));
+}
+
+int32_t smith_flush_l2(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return 1;
+  if (grow(c, &c->flush, &c->flush_bytes, (size_t)256 << 20)) return 1;
+  cudaError_t e = launch_fill_bytes(c->flush, c->flush_bytes, 0u, c->stream);
+  return e == cudaSuccess ? 0 : fail("flush launch failed: %s", cudaGetErrorString(e));
+}
+
+}  // extern "C"

@@ -1,0 +1,55 @@
+// kernels.h -- launch entry points shared between the kernel files and the
+// C-ABI layer (bridge.cu).  Everything here takes raw device pointers and a
+// stream and launches asynchronously.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace smith {
+
+constexpr int kQ4Group = 32;  // elements per Q4 block (src/ops/quantize.js:9)
+constexpr int kQ4Bytes = 24;  // 16 nibble bytes + f32 scale + f32 zero (src/ops/quantize.js:10)
+constexpr int kQ8Group = 32;  // elements per Q8 block (src/ops/quantize.js:94)
+constexpr int kQ8Bytes = 34;  // f16 scale + 32 int8 (src/ops/quantize.js:95)
+
+enum Path : int { kAuto = 0, kGeneric = 1, kDecode = 2, kTensor = 3 };
+
+// Scratch memory a matmul launch may use (owned by the caller of the launch).
+struct Workspace {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+// Counts kernel launches made through these entry points.
+extern thread_local uint64_t* g_launch_counter;
+inline void count_launch(int n = 1) {
+  if (g_launch_counter) *g_launch_counter += (uint64_t)n;
+}
+
+// pack.cu
+cudaError_t launch_pack_q4(const float* w, uint8_t* out, int64_t K, int64_t N, cudaStream_t s);
+cudaError_t launch_pack_q8(const float* w, uint8_t* out, int64_t K, int64_t N, cudaStream_t s);
+
+// qmatmul_generic.cu : any shape, CUDA cores, sequential-k f32 accumulation.
+cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
+                                   int64_t N, int64_t K, int64_t groups, cudaStream_t s);
+
+// qdecode.cu : M <= 16, streams packed rows through shared memory, f32 accumulate.
+bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
+cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
+                           int64_t N, int64_t K, int64_t groups, cudaStream_t s);
+
+// qgemm_tc.cu : M > 16, dequantise to bf16 tiles in shared memory, tcgen05 MMA, TMEM accumulators.
+bool qgemm_tc_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
+size_t qgemm_tc_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
+cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
+                            int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
+
+// util.cu
+cudaError_t launch_fill_normal(float* out, uint64_t count, uint64_t seed, float std, cudaStream_t s);
+cudaError_t launch_fill_bytes(void* out, size_t bytes, uint32_t value, cudaStream_t s);
+
+// Path resolution for kAuto.
+int resolve_path(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
+
+}  // namespace smith

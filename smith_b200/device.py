@@ -1,0 +1,406 @@
+"""ctypes binding of libsmith_cuda.so -- the role src/device.js plays in the reference.
+
+The reference binds 26 bridge functions with bun:ffi (src/device.js:10-50) and
+wraps each in a thin function (src/device.js:93-215).  This module binds the
+same functions of the CUDA bridge under the same (camelCase) names, plus the
+additive entry points declared in include/smith_cuda_bridge.h.
+
+The shared library is loaded when this module is imported and import fails
+loudly if it is missing: there is no CPU fallback.  The device context is
+created on first use (``ctx()``), so that importing on a machine without a GPU
+(for symbol checks and host-logic tests) still works.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+SHARED = 0   # src/device.js:53
+PRIVATE = 1  # src/device.js:54
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsmith_cuda.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"smith: {LIB_PATH} is missing. Build it with `python -m smith_b200.build` "
+        "(nvcc, sm_100a). There is no CPU fallback.")
+
+lib = C.CDLL(LIB_PATH)
+
+_p, _u64, _u32, _i64, _i32 = C.c_void_p, C.c_uint64, C.c_uint32, C.c_int64, C.c_int32
+
+
+class SmithTiming(C.Structure):
+    """native/gpu_bridge.h:113-117"""
+    _fields_ = [("gpu_start", C.c_double), ("gpu_end", C.c_double), ("gpu_ms", C.c_double)]
+
+
+# name -> (restype, argtypes).  Part 1 is the table of src/device.js:10-50.
+SYMBOLS = {
+    "smith_init": (_p, []),
+    "smith_destroy": (None, [_p]),
+    "smith_device_name": (_p, [_p]),
+    "smith_max_threadgroup_memory": (_u64, [_p]),
+    "smith_max_threads_per_threadgroup": (_u64, [_p]),
+    "smith_alloc": (_p, [_p, _u64, _u32]),
+    "smith_buffer_contents": (_p, [_p]),
+    "smith_buffer_length": (_u64, [_p]),
+    "smith_release_buffer": (None, [_p]),
+    "smith_load_library": (_p, [_p, C.c_char_p]),
+    "smith_compile_source": (_p, [_p, C.c_char_p, C.POINTER(C.c_char_p)]),
+    "smith_create_pipeline": (_p, [_p, _p, C.c_char_p]),
+    "smith_begin": (_p, [_p]),
+    "smith_set_buffer": (None, [_p, _p, _u32]),
+    "smith_set_bytes": (None, [_p, _p, _u32, _u32]),
+    "smith_set_threadgroup_memory": (None, [_p, _u64, _u32]),
+    "smith_set_pipeline": (None, [_p, _p]),
+    "smith_dispatch": (None, [_p, _u64, _u64, _u64, _u64, _u64, _u64]),
+    "smith_end_sync": (None, [_p]),
+    "smith_end_async": (_p, [_p]),
+    "smith_wait": (None, [_p]),
+    "smith_end_timed": (C.POINTER(SmithTiming), [_p]),
+    "smith_allocated_size": (_u64, [_p]),
+    "smith_test_release": (_i64, [_p]),
+    "smith_test_release_after_use": (_i64, [_p]),
+    "smith_buffer_retain_count": (_i64, [_p]),
+    "smith_dispatch_sync": (None, [_p, _p, C.POINTER(_p), C.POINTER(_u32), _u32, _p, _u32, _u32,
+                                   _u64, _u64, _u64, _u64, _u64, _u64]),
+    # Part 2: additions
+    "smith_last_error": (C.c_char_p, []),
+    "smith_clear_error": (None, []),
+    "smith_device_count": (_i32, []),
+    "smith_init_device": (_p, [_i32]),
+    "smith_device_index": (_i32, [_p]),
+    "smith_stream": (_p, [_p]),
+    "smith_synchronize": (_i32, [_p]),
+    "smith_buffer_device_ptr": (_p, [_p]),
+    "smith_buffer_make_resident": (_i32, [_p]),
+    "smith_buffer_evict": (_i32, [_p]),
+    "smith_wrap_device_memory": (_p, [_p, _p, _u64]),
+    "smith_upload": (_i32, [_p, _u64, _p, _u64]),
+    "smith_download": (_i32, [_p, _u64, _p, _u64]),
+    "smith_q4_pack": (_i32, [_p, _p, _p, _u64, _u64]),
+    "smith_q8_pack": (_i32, [_p, _p, _p, _u64, _u64]),
+    "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
+    "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
+    "smith_launch_count": (_u64, [_p]),
+    "smith_graph_begin": (_i32, [_p]),
+    "smith_graph_end": (_p, [_p]),
+    "smith_graph_launch": (_i32, [_p, _p]),
+    "smith_graph_destroy": (None, [_p]),
+    "smith_fill_normal": (_i32, [_p, _p, _u64, _u64, C.c_float]),
+    "smith_flush_l2": (_i32, [_p]),
+}
+
+for _name, (_res, _args) in SYMBOLS.items():
+    _f = getattr(lib, _name)  # AttributeError here = the library does not export a declared symbol
+    _f.restype = _res
+    _f.argtypes = _args
+
+_libc = C.CDLL(None)
+_libc.free.argtypes = [C.c_void_p]
+_libc.free.restype = None
+
+PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR = 0, 1, 2, 3
+
+
+class SmithError(RuntimeError):
+    pass
+
+
+def lastError():
+    return (lib.smith_last_error() or b"").decode()
+
+
+def _raise(prefix):
+    raise SmithError(f"smith: {prefix}: {lastError()}")
+
+
+def _check(status, what):
+    if status != 0:
+        _raise(what)
+
+
+_ctx = None
+
+
+def ctx():
+    """The process-wide device context (src/device.js:57-58), created on first use."""
+    global _ctx
+    if _ctx is None:
+        c = lib.smith_init()
+        if not c:
+            raise SmithError("smith: failed to initialize CUDA device. NVIDIA B200 (sm_100a) GPU required. "
+                             + lastError())
+        _ctx = c
+    return _ctx
+
+
+def destroy():
+    global _ctx, _shaderLib
+    if _ctx is not None:
+        lib.smith_destroy(_ctx)
+        _ctx = None
+        _shaderLib = None
+        _pipelines.clear()
+
+
+def selfTest():
+    """The import-time release self-test of src/device.js:61-65, on request."""
+    return int(lib.smith_test_release(ctx())), int(lib.smith_test_release_after_use(ctx()))
+
+
+_shaderLib = None
+_pipelines = {}
+
+
+def shaderLib():
+    """src/device.js:71-78 -- here the handle of the built-in kernel registry."""
+    global _shaderLib
+    if not _shaderLib:
+        _shaderLib = lib.smith_load_library(ctx(), b"builtin")
+        if not _shaderLib:
+            raise SmithError("smith: failed to load kernel library")
+    return _shaderLib
+
+
+def pipeline(kernelName):
+    """src/device.js:83-91"""
+    p = _pipelines.get(kernelName)
+    if not p:
+        p = lib.smith_create_pipeline(ctx(), shaderLib(), kernelName.encode())
+        if not p:
+            raise SmithError(f"smith: kernel '{kernelName}' not found in shader library")
+        _pipelines[kernelName] = p
+    return p
+
+
+# --- device info (src/device.js:95-108) ---
+
+def deviceName():
+    ptr = lib.smith_device_name(ctx())
+    s = C.string_at(ptr).decode()
+    _libc.free(ptr)
+    return s
+
+
+def maxThreadgroupMemory():
+    return int(lib.smith_max_threadgroup_memory(ctx()))
+
+
+def maxThreadsPerThreadgroup():
+    return int(lib.smith_max_threads_per_threadgroup(ctx()))
+
+
+def deviceCount():
+    return int(lib.smith_device_count())
+
+
+def deviceIndex():
+    return int(lib.smith_device_index(ctx()))
+
+
+# --- buffers (src/device.js:112-140) ---
+
+def alloc(nbytes, mode=SHARED):
+    buf = lib.smith_alloc(ctx(), int(nbytes), mode)
+    if not buf:
+        raise SmithError(f"smith: failed to allocate {nbytes} bytes (mode={mode})")
+    return buf
+
+
+def bufferContents(buffer):
+    return lib.smith_buffer_contents(buffer)
+
+
+def bufferLength(buffer):
+    return int(lib.smith_buffer_length(buffer))
+
+
+def releaseBuffer(buffer):
+    lib.smith_release_buffer(buffer)
+
+
+def bufferRetainCount(buffer):
+    return int(lib.smith_buffer_retain_count(buffer))
+
+
+def viewBuffer(buffer, byteLength, dtype=np.float32):
+    """Zero-copy typed view of a SHARED buffer's host memory (src/device.js:136-140)."""
+    raw = lib.smith_buffer_contents(buffer)
+    if not raw:
+        raise SmithError("smith: buffer has no host-visible contents (PRIVATE buffer?)")
+    dt = np.dtype(dtype)
+    n = int(byteLength) // dt.itemsize
+    arr = np.ctypeslib.as_array(C.cast(raw, C.POINTER(C.c_uint8)), shape=(n * dt.itemsize,))
+    return arr.view(dt)
+
+
+def devicePtr(buffer):
+    return lib.smith_buffer_device_ptr(buffer)
+
+
+def makeResident(buffer):
+    _check(lib.smith_buffer_make_resident(buffer), "make_resident")
+
+
+def evict(buffer):
+    _check(lib.smith_buffer_evict(buffer), "evict")
+
+
+def wrapDeviceMemory(ptr, nbytes):
+    buf = lib.smith_wrap_device_memory(ctx(), ptr, int(nbytes))
+    if not buf:
+        _raise("wrap_device_memory")
+    return buf
+
+
+def upload(buffer, array, offset=0):
+    a = np.ascontiguousarray(array)
+    _check(lib.smith_upload(buffer, offset, a.ctypes.data_as(C.c_void_p), a.nbytes), "upload")
+
+
+def download(buffer, nbytes, dtype=np.uint8, offset=0):
+    out = np.empty(int(nbytes) // np.dtype(dtype).itemsize, dtype=dtype)
+    _check(lib.smith_download(buffer, offset, out.ctypes.data_as(C.c_void_p), out.nbytes), "download")
+    return out
+
+
+# --- compute dispatch (src/device.js:144-178) ---
+
+def begin():
+    return lib.smith_begin(ctx())
+
+
+def setBuffer(enc, buffer, index):
+    lib.smith_set_buffer(enc, buffer, index)
+
+
+def setBytes(enc, data, length, index):
+    a = np.ascontiguousarray(data)
+    lib.smith_set_bytes(enc, a.ctypes.data_as(C.c_void_p), int(length), index)
+
+
+def setThreadgroupMemory(enc, length, index):
+    lib.smith_set_threadgroup_memory(enc, length, index)
+
+
+def setPipeline(enc, pipelinePtr):
+    lib.smith_set_pipeline(enc, pipelinePtr)
+
+
+def dispatch(enc, gridX, gridY, gridZ, groupX, groupY, groupZ):
+    lib.smith_dispatch(enc, gridX, gridY, gridZ, groupX, groupY, groupZ)
+
+
+def endSync(enc):
+    lib.smith_clear_error()
+    lib.smith_end_sync(enc)
+    if lastError():
+        _raise("dispatch failed")
+
+
+def endAsync(enc):
+    lib.smith_clear_error()
+    tok = lib.smith_end_async(enc)
+    if not tok:
+        _raise("dispatch failed")
+    return tok
+
+
+def wait(token):
+    lib.smith_clear_error()
+    lib.smith_wait(token)
+    if lastError():
+        _raise("wait failed")
+
+
+def endTimed(enc):
+    """src/device.js:182-193 -- decodes (and here also frees) the SmithTiming struct."""
+    lib.smith_clear_error()
+    t = lib.smith_end_timed(enc)
+    if not t:
+        if lastError():
+            _raise("dispatch failed")
+        return {"gpuStart": 0.0, "gpuEnd": 0.0, "gpuMs": 0.0}
+    out = {"gpuStart": t.contents.gpu_start, "gpuEnd": t.contents.gpu_end, "gpuMs": t.contents.gpu_ms}
+    _libc.free(C.cast(t, C.c_void_p))
+    return out
+
+
+def allocatedSize():
+    return int(lib.smith_allocated_size(ctx()))
+
+
+def compileSource(source):
+    err = C.c_char_p()
+    library = lib.smith_compile_source(ctx(), source.encode(), C.byref(err))
+    if not library:
+        msg = err.value.decode() if err.value else "unknown error"
+        raise SmithError(f"smith: shader compilation failed: {msg}")
+    return library
+
+
+def createPipeline(library, fnName):
+    p = lib.smith_create_pipeline(ctx(), library, fnName.encode())
+    if not p:
+        raise SmithError(f"smith: kernel '{fnName}' not found")
+    return p
+
+
+# --- additions: direct entries, graphs, utilities ---
+
+def stream():
+    return lib.smith_stream(ctx())
+
+
+def synchronize():
+    _check(lib.smith_synchronize(ctx()), "synchronize")
+
+
+def q4Pack(wBuffer, outBuffer, K, N):
+    _check(lib.smith_q4_pack(ctx(), wBuffer, outBuffer, K, N), "q4_pack")
+
+
+def q8Pack(wBuffer, outBuffer, K, N):
+    _check(lib.smith_q8_pack(ctx(), wBuffer, outBuffer, K, N), "q8_pack")
+
+
+def qmatmul(kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path=PATH_AUTO):
+    _check(lib.smith_qmatmul(ctx(), kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path), "qmatmul")
+
+
+def qmatmulPath(kind, M, N, K):
+    return int(lib.smith_qmatmul_path(kind, M, N, K))
+
+
+def launchCount():
+    return int(lib.smith_launch_count(ctx()))
+
+
+def graphBegin():
+    _check(lib.smith_graph_begin(ctx()), "graph_begin")
+
+
+def graphEnd():
+    g = lib.smith_graph_end(ctx())
+    if not g:
+        _raise("graph_end")
+    return g
+
+
+def graphLaunch(graph):
+    _check(lib.smith_graph_launch(ctx(), graph), "graph_launch")
+
+
+def graphDestroy(graph):
+    lib.smith_graph_destroy(graph)
+
+
+def fillNormal(buffer, count, seed, std):
+    _check(lib.smith_fill_normal(ctx(), buffer, count, seed, std), "fill_normal")
+
+
+def flushL2():
+    _check(lib.smith_flush_l2(ctx()), "flush_l2")

@@ -1,0 +1,119 @@
+"""Per-kernel GPU timing -- the role of src/profile.js in the reference.
+
+When profiling is on, dispatch.run ends each dispatch with the bridge's timed
+submit and reports the kernel's device milliseconds here (src/dispatch.js:42-44,
+src/profile.js:35-55).  ``profile(fn)`` and ``benchmark(name, fn)`` keep the
+reference's result shapes (src/profile.js:103-175).
+"""
+import math
+import time
+
+from . import device
+
+_enabled = False
+_kernelStats = {}
+_totalDispatches = 0
+_totalGpuMs = 0.0
+_peakMemory = 0
+_startMemory = 0
+
+
+def _round(v):
+    return math.floor(v * 1000 + 0.5) / 1000
+
+
+def enableProfiling():
+    global _enabled, _startMemory, _peakMemory
+    _enabled = True
+    _startMemory = device.allocatedSize()
+    _peakMemory = _startMemory
+
+
+def disableProfiling():
+    global _enabled
+    _enabled = False
+
+
+def isProfilingEnabled():
+    return _enabled
+
+
+def recordKernel(kernelName, gpuMs):
+    global _totalDispatches, _totalGpuMs, _peakMemory
+    _totalDispatches += 1
+    _totalGpuMs += gpuMs
+    s = _kernelStats.setdefault(kernelName, {"calls": 0, "totalGpuMs": 0.0, "minMs": math.inf, "maxMs": 0.0,
+                                             "samples": []})
+    s["calls"] += 1
+    s["totalGpuMs"] += gpuMs
+    s["minMs"] = min(s["minMs"], gpuMs)
+    s["maxMs"] = max(s["maxMs"], gpuMs)
+    if len(s["samples"]) < 100:
+        s["samples"].append(gpuMs)
+    else:
+        s["samples"][s["calls"] % 100] = gpuMs
+    mem = device.allocatedSize()
+    if mem > _peakMemory:
+        _peakMemory = mem
+
+
+def report():
+    entries = []
+    for name, s in _kernelStats.items():
+        avg = s["totalGpuMs"] / s["calls"] if s["calls"] else 0
+        pct = s["totalGpuMs"] / _totalGpuMs * 100 if _totalGpuMs > 0 else 0
+        entries.append({"kernel": name, "calls": s["calls"], "totalMs": _round(s["totalGpuMs"]),
+                        "avgMs": _round(avg), "minMs": _round(0 if s["minMs"] == math.inf else s["minMs"]),
+                        "maxMs": _round(s["maxMs"]), "pct": _round(pct)})
+    entries.sort(key=lambda e: -e["totalMs"])
+    return {"dispatches": _totalDispatches, "totalGpuMs": _round(_totalGpuMs),
+            "memory": {"startBytes": _startMemory, "peakBytes": _peakMemory,
+                       "currentBytes": device.allocatedSize(), "deltaBytes": _peakMemory - _startMemory},
+            "kernels": entries}
+
+
+def resetProfile():
+    global _totalDispatches, _totalGpuMs, _peakMemory, _startMemory
+    _kernelStats.clear()
+    _totalDispatches = 0
+    _totalGpuMs = 0.0
+    _peakMemory = device.allocatedSize()
+    _startMemory = _peakMemory
+
+
+def profile(fn):
+    was = _enabled
+    enableProfiling()
+    resetProfile()
+    t0 = time.perf_counter()
+    result = fn()
+    cpuMs = (time.perf_counter() - t0) * 1000
+    rep = report()
+    if not was:
+        disableProfiling()
+    return {"result": result, "cpuMs": _round(cpuMs), "gpuMs": rep["totalGpuMs"], "dispatches": rep["dispatches"],
+            "memory": rep["memory"], "kernels": rep["kernels"]}
+
+
+def computeStats(sortedTimes):
+    n = len(sortedTimes)
+    if n == 0:
+        return {"mean": 0, "median": 0, "min": 0, "max": 0, "p95": 0, "stddev": 0}
+    mean = sum(sortedTimes) / n
+    median = (sortedTimes[n // 2 - 1] + sortedTimes[n // 2]) / 2 if n % 2 == 0 else sortedTimes[n // 2]
+    p95 = sortedTimes[min(math.ceil(n * 0.95) - 1, n - 1)]
+    var = sum((v - mean) ** 2 for v in sortedTimes) / n
+    return {"mean": _round(mean), "median": _round(median), "min": _round(sortedTimes[0]),
+            "max": _round(sortedTimes[-1]), "p95": _round(p95), "stddev": _round(math.sqrt(var))}
+
+
+def benchmark(name, fn, warmup=3, iterations=10):
+    for _ in range(warmup):
+        fn()
+    cpu, gpu = [], []
+    for _ in range(iterations):
+        p = profile(fn)
+        cpu.append(p["cpuMs"])
+        gpu.append(p["gpuMs"])
+    return {"name": name, "iterations": iterations, "cpu": computeStats(sorted(cpu)),
+            "gpu": computeStats(sorted(gpu))}

@@ -1,0 +1,307 @@
+"""-m gpu: the CUDA path against the oracle, through the C ABI.
+
+Packed bytes must be bit-identical to the CPU restatement of the reference
+packer; matmul outputs must satisfy max |delta_mn| <= 1e-3 * ||a_m|| * ||w_deq[:,n]||
+against the sequential-f32 shader arithmetic (and be bit-identical on the
+any-shape kernel, which keeps the shader's operation order)."""
+import numpy as np
+import pytest
+
+import smith_b200 as smith
+from gpu_util import DevBuf, matmul_on_device, pack_on_device
+from helpers import bits_equal, golden_cases, load_golden, within_tolerance
+from oracle import oracle as O
+from smith_b200 import device
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-3  # tolerance factor stated by the north star for f32 accumulation
+
+
+def _data(seed, M, K, N, std=0.02):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((K, N)) * std).astype(np.float32)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    return a, w
+
+
+# ------------------------------------------------------------------ packers
+@pytest.mark.parametrize("name", golden_cases())
+def test_packers_reproduce_golden_bytes(name):
+    g = load_golden(name)
+    assert np.array_equal(pack_on_device(g["w"], "q4"), g["packed_q4"])
+    assert np.array_equal(pack_on_device(g["w"], "q8"), g["packed_q8"])
+
+
+@pytest.mark.parametrize("K,N", [(4096, 512), (4096, 1000), (1000, 257), (31, 3), (33, 300), (14336, 64)])
+@pytest.mark.parametrize("kind", ["q4", "q8"])
+def test_packers_bit_exact_random(kind, K, N):
+    rng = np.random.default_rng(K + N)
+    for w in ((rng.standard_normal((K, N)) * 0.02).astype(np.float32), rng.random((K, N), dtype=np.float32),
+              (rng.standard_normal((K, N)) * 1e4).astype(np.float32)):
+        want = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
+        assert np.array_equal(pack_on_device(w, kind), want)
+
+
+def test_packer_rounding_boundaries():
+    # values engineered to sit on and next to .5 code boundaries after v/scale + zero
+    K, N = 32, 4096
+    rng = np.random.default_rng(5)
+    w = np.zeros((K, N), np.float32)
+    w[0] = 0.0
+    w[31] = 15.0                                     # scale exactly 1, zero -0.0
+    half = rng.integers(0, 15, (30, N)) + 0.5
+    w[1:31] = half + rng.choice([0.0, 1e-6, -1e-6, 2.0 ** -20, -2.0 ** -20], (30, N))
+    assert np.array_equal(pack_on_device(w, "q4"), O.quantize_q4(w))
+    assert np.array_equal(pack_on_device(w, "q8"), O.quantize_q8(w))
+
+
+# ------------------------------------------------------------------ matmul: golden + every path
+@pytest.mark.parametrize("name", golden_cases())
+@pytest.mark.parametrize("kind", ["q4", "q8"])
+def test_matmul_golden(name, kind):
+    g = load_golden(name)
+    K, N = g["w"].shape
+    packed, a, want = g["packed_" + kind], g["a"], g["c_" + kind]
+    got = matmul_on_device(a, packed, K, N, kind, device.PATH_GENERIC)
+    if "quirks" not in name:
+        assert bits_equal(got, want), "any-shape kernel must keep the shader's operation order"
+    ok, worst = within_tolerance(got, want, a, packed, K, N, kind, REL)
+    assert ok, worst
+    got = matmul_on_device(a, packed, K, N, kind, device.PATH_AUTO)
+    ok, worst = within_tolerance(got, want, a, packed, K, N, kind, REL)
+    assert ok, worst
+
+
+SHAPES = [
+    # M, K, N
+    (1, 4096, 4096),      # cfg1
+    (1, 4096, 14336 // 8),
+    (4, 4096, 1792),
+    (16, 4096, 1792),
+    (2, 512, 130),
+    (7, 2048, 1000),
+    (16, 14336, 512),     # down-projection-shaped K
+    (64, 4096, 1024),
+    (100, 1024, 768),
+    (256, 4096, 512),
+    (512, 1024, 1376),
+    (33, 96, 66),
+    (3, 100, 40),         # ragged K
+    (130, 200, 56),       # ragged K, M > 128
+]
+
+
+@pytest.mark.parametrize("M,K,N", SHAPES)
+@pytest.mark.parametrize("kind", ["q4", "q8"])
+def test_matmul_auto_path_within_tolerance(kind, M, K, N):
+    a, w = _data(M * 7 + K + N, M, K, N)
+    packed = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
+    want = O.matmul(a, packed, K, N, kind, threads=O.max_threads())
+    got = matmul_on_device(a, packed, K, N, kind)
+    ok, worst = within_tolerance(got, want, a, packed, K, N, kind, REL)
+    assert ok, f"worst err/bound = {worst}"
+
+
+@pytest.mark.parametrize("path", [device.PATH_GENERIC, device.PATH_DECODE, device.PATH_TENSOR])
+@pytest.mark.parametrize("kind", ["q4", "q8"])
+def test_matmul_each_path_where_supported(kind, path):
+    shapes = {device.PATH_GENERIC: [(1, 64, 32), (9, 1000, 77)],
+              device.PATH_DECODE: [(1, 4096, 1024), (5, 1024, 256), (16, 2048, 640), (8, 4096, 98)],
+              device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384)]}[path]
+    for M, K, N in shapes:
+        a, w = _data(M + K + N + path, M, K, N)
+        packed = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
+        want = O.matmul(a, packed, K, N, kind, threads=O.max_threads())
+        try:
+            got = matmul_on_device(a, packed, K, N, kind, path)
+        except device.SmithError as e:
+            assert "does not take" in str(e), e
+            continue
+        if path == device.PATH_GENERIC:
+            assert bits_equal(got, want)
+        ok, worst = within_tolerance(got, want, a, packed, K, N, kind, REL)
+        assert ok, f"path {path} M={M} K={K} N={N}: worst err/bound = {worst}"
+
+
+def test_structured_inputs_ones_and_uniform():
+    # the reference test's own shape of data: U[0,1) weights, all-ones activations (no cancellation)
+    rng = np.random.default_rng(3)
+    for M, K, N in [(1, 4096, 1024), (8, 4096, 512), (128, 1024, 256)]:
+        w = rng.random((K, N), dtype=np.float32)
+        a = np.ones((M, K), np.float32)
+        for kind in ("q4", "q8"):
+            packed = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
+            want = O.matmul(a, packed, K, N, kind)
+            got = matmul_on_device(a, packed, K, N, kind)
+            ok, worst = within_tolerance(got, want, a, packed, K, N, kind, REL)
+            assert ok, worst
+
+
+def test_linearity_at_full_size():
+    # size-independent property at the headline shape: f(a1 + a2) ~= f(a1) + f(a2), f(2a) == 2 f(a)
+    K, N = 4096, 14336
+    wb = DevBuf(K * N * 4)
+    device.fillNormal(wb.handle, K * N, 1, 0.02)
+    pb = DevBuf((K // 32) * N * 24)
+    device.q4Pack(wb.handle, pb.handle, K, N)
+    device.synchronize()
+    wb.free()
+    rng = np.random.default_rng(9)
+    a1 = rng.standard_normal((1, K)).astype(np.float32)
+    a2 = rng.standard_normal((1, K)).astype(np.float32)
+
+    def f(a):
+        ab, cb = DevBuf.of(a), DevBuf(a.shape[0] * N * 4)
+        device.qmatmul(4, ab.handle, pb.handle, cb.handle, a.shape[0], N, K, K // 32, 0)
+        device.synchronize()
+        out = cb.get(np.float32).reshape(a.shape[0], N)
+        ab.free()
+        cb.free()
+        return out
+
+    y1, y2, y12, y2x = f(a1), f(a2), f(a1 + a2), f(2 * a1)
+    assert np.array_equal(y2x, 2 * y1)
+    scale = np.abs(y1).max() + np.abs(y2).max()
+    assert np.abs(y12 - (y1 + y2)).max() <= 1e-4 * scale
+    # sampled columns against the oracle
+    packed = pb.get()
+    cols = (5000, 5064)
+    want = O.matmul(a1, packed, K, N, "q4", cols=cols)
+    ok, worst = within_tolerance(y1[:, cols[0]:cols[1]], want[:, cols[0]:cols[1]], a1,
+                                 packed.reshape(K // 32, N, 24)[:, cols[0]:cols[1]].reshape(-1), K, cols[1] - cols[0],
+                                 "q4", REL)
+    assert ok, worst
+    pb.free()
+
+
+def test_empty_and_degenerate_shapes():
+    K, N = 64, 16
+    a, w = _data(1, 2, K, N)
+    packed = O.quantize_q4(w)
+    assert matmul_on_device(a[:0], packed, K, N, "q4").shape == (0, N)
+    # groups smaller than ceil(K/32): the shader simply stops early
+    want = O.matmul(a, packed, K, N, "q4", groups=1)
+    got = matmul_on_device(a, packed, K, N, "q4", device.PATH_GENERIC, groups=1)
+    assert bits_equal(got, want)
+
+
+# ------------------------------------------------------------------ operator API (reference test restated)
+def test_operator_api_reference_test():
+    # tests/inference.test.js:94-123
+    K, N = 64, 32
+    smith.tensor.seed(0)
+    w = smith.rand([K, N])
+    wq = smith.quantizeQ4(w)
+    assert (wq.K, wq.N, wq.groups) == (K, N, 2) and wq["totalBytes"] == 2 * N * 24
+    a = smith.ones([1, K])
+    out = smith.matmulQ4(a, wq)
+    assert out.shape == [1, N]
+    expected = smith.toNumpy(w).sum(axis=0)
+    actual = np.array(smith.toArray(out))
+    assert np.all(np.abs(actual[0] - expected) / (np.abs(expected) + 1e-6) < 0.15)
+    # tests/inference.test.js:125-135
+    wq2 = smith.quantizeQ4(smith.rand([256, 256]))
+    assert wq2.totalBytes < 256 * 256 * 4 and wq2.totalBytes / (256 * 256 * 4) < 0.35
+
+
+def test_operator_api_q8_and_profile():
+    K, N, M = 256, 128, 4
+    smith.tensor.seed(1)
+    w, a = smith.randn([K, N]), smith.randn([M, K])
+    wq = smith.quantizeQ8(w)
+    assert wq.totalBytes == (K // 32) * N * 34
+    out = smith.toNumpy(smith.matmulQ8(a, wq))
+    packed = O.quantize_q8(smith.toNumpy(w))
+    assert np.array_equal(device.download(wq.buffer, wq.totalBytes), packed)
+    want = O.matmul(smith.toNumpy(a), packed, K, N, "q8")
+    ok, worst = within_tolerance(out, want, smith.toNumpy(a), packed, K, N, "q8", REL)
+    assert ok, worst
+    p = smith.profileFn(lambda: smith.matmulQ8(a, wq))
+    assert p["dispatches"] == 1 and p["kernels"][0]["kernel"] == "matmul_q8" and p["gpuMs"] >= 0
+    b = smith.benchmark("q8", lambda: smith.matmulQ8(a, wq), warmup=1, iterations=3)
+    assert b["iterations"] == 3 and b["gpu"]["min"] >= 0
+    with pytest.raises(ValueError, match="matmulQ8: inner dims don't match: 256 vs 512"):
+        smith.matmulQ8(a, {"buffer": wq.buffer, "K": 512, "N": N, "groups": 16})
+
+
+def test_shared_weights_and_residency():
+    # a caller-supplied SHARED packed buffer (the reference's own storage mode) works, staged or resident
+    K, N, M = 128, 64, 3
+    a_np, w_np = _data(2, M, K, N)
+    packed = O.quantize_q4(w_np)
+    buf = device.alloc(packed.size, device.SHARED)
+    device.viewBuffer(buf, packed.size, np.uint8)[:] = packed
+    a = smith.tensorFrom(a_np, [M, K])
+    want = O.matmul(a_np, packed, K, N, "q4")
+    wq = {"buffer": buf, "K": K, "N": N, "groups": K // 32}
+    out1 = smith.toNumpy(smith.matmulQ4(a, wq))
+    device.makeResident(buf)
+    out2 = smith.toNumpy(smith.matmulQ4(a, wq))
+    assert np.array_equal(out1, out2)
+    assert within_tolerance(out1, want, a_np, packed, K, N, "q4", REL)[0]
+    device.evict(buf)
+    device.releaseBuffer(buf)
+
+
+# ------------------------------------------------------------------ bridge behaviour
+def test_bridge_info_and_self_tests():
+    info = smith.info()
+    assert "B200" in info["device"] or "NVIDIA" in info["device"]
+    assert info["maxThreadgroupMemory"] >= 200 * 1024 and info["maxThreadsPerThreadgroup"] == 1024
+    assert device.selfTest() == (1048576, 1048576)          # src/device.js:61-65 expects ~1 MiB twice
+    with pytest.raises(device.SmithError, match="not found"):
+        device.pipeline("no_such_kernel")
+    with pytest.raises(device.SmithError, match="compilation"):
+        device.compileSource("kernel void f() {}")
+
+
+def test_bridge_buffers_and_errors():
+    before = device.allocatedSize()
+    b = device.alloc(4096, device.SHARED)
+    assert device.bufferLength(b) == 4096 and device.bufferContents(b) and device.bufferRetainCount(b) == 1
+    assert device.allocatedSize() == before + 4096
+    p = device.alloc(4096, device.PRIVATE)
+    assert device.bufferContents(p) is None and device.devicePtr(p)
+    device.releaseBuffer(b)
+    device.releaseBuffer(p)
+    assert device.allocatedSize() == before
+    # a launch whose buffers are too small for its parameters is refused on the host
+    small = DevBuf(64)
+    with pytest.raises(device.SmithError, match="needs"):
+        device.qmatmul(4, small.handle, small.handle, small.handle, 4, 64, 64, 2, 0)
+    a = smith.ones([1, 64])
+    with pytest.raises(device.SmithError, match="needs"):
+        smith.matmulQ4(a, {"buffer": small.handle, "K": 64, "N": 4096, "groups": 2})
+    small.free()
+
+
+def test_async_submit_and_graph_replay():
+    K, N, M = 1024, 512, 1
+    a_np, w_np = _data(4, M, K, N)
+    packed = O.quantize_q4(w_np)
+    ab, bb, cb = DevBuf.of(a_np), DevBuf.of(packed), DevBuf(M * N * 4)
+    device.qmatmul(4, ab.handle, bb.handle, cb.handle, M, N, K, K // 32, 0)   # sizes any scratch before capture
+    device.synchronize()
+    first = cb.get(np.float32)
+    device.upload(cb.handle, np.zeros(M * N, np.float32))
+    n0 = device.launchCount()
+    device.graphBegin()
+    for _ in range(3):
+        device.qmatmul(4, ab.handle, bb.handle, cb.handle, M, N, K, K // 32, 0)
+    g = device.graphEnd()
+    assert device.launchCount() - n0 >= 3
+    device.graphLaunch(g)
+    device.synchronize()
+    assert np.array_equal(cb.get(np.float32), first)
+    device.graphDestroy(g)
+    # encoder path, asynchronous submit
+    enc = device.begin()
+    device.setPipeline(enc, device.pipeline("matmul_q4"))
+    for i, h in enumerate((ab.handle, bb.handle, cb.handle)):
+        device.setBuffer(enc, h, i)
+    prm = np.array([M, N, K, K // 32], np.uint32)
+    device.setBytes(enc, prm, prm.nbytes, 3)
+    device.dispatch(enc, N, M, 1, 16, 1, 1)
+    device.wait(device.endAsync(enc))
+    assert np.array_equal(cb.get(np.float32), first)

@@ -1,0 +1,144 @@
+"""CPU tests of the host layer: the C ABI's symbol table, and the host-side
+mirror of the reference interface (pool, lifecycle, dtype, operator argument
+checks).  Nothing here computes on a device."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import smith_b200 as smith
+from smith_b200 import device, lifecycle, pool
+from smith_b200.ops import quantize as Q
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "smith_cuda_bridge.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(smith_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_symbols()
+    assert len(names) >= 27
+    lib = ctypes.CDLL(device.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/smith_cuda_bridge.h but not exported"
+
+
+def test_binding_table_covers_the_header():
+    assert sorted(device.SYMBOLS) == _declared_symbols()
+
+
+def test_reference_ffi_names_are_all_present():
+    # the 26 names bound by src/device.js:10-50, plus smith_dispatch_sync (native/gpu_bridge.h:104)
+    ref = """smith_init smith_destroy smith_device_name smith_max_threadgroup_memory
+    smith_max_threads_per_threadgroup smith_alloc smith_buffer_contents smith_buffer_length
+    smith_release_buffer smith_load_library smith_compile_source smith_create_pipeline smith_begin
+    smith_set_buffer smith_set_bytes smith_set_threadgroup_memory smith_set_pipeline smith_dispatch
+    smith_end_sync smith_end_async smith_wait smith_end_timed smith_allocated_size smith_test_release
+    smith_test_release_after_use smith_buffer_retain_count smith_dispatch_sync""".split()
+    assert len(ref) == 27
+    for n in ref:
+        assert n in device.SYMBOLS
+
+
+def test_calls_without_a_device_fail_cleanly():
+    if device.deviceCount() > 0:
+        pytest.skip("a device is present")
+    assert device.lib.smith_init() is None
+    assert "no CUDA device" in device.lastError()
+    assert device.lib.smith_buffer_length(None) == 0
+    assert device.lib.smith_buffer_retain_count(None) == -1
+    assert device.lib.smith_allocated_size(None) == 0
+    with pytest.raises(device.SmithError):
+        device.ctx()
+
+
+def test_constants_match_reference():
+    assert (Q.GROUP_SIZE, Q.GROUP_BYTES, Q.Q8_BLOCK_SIZE, Q.Q8_BLOCK_BYTES) == (32, 24, 32, 34)
+    assert (smith.SHARED, smith.PRIVATE) == (0, 1)
+
+
+class _FakeTensor:
+    def __init__(self, shape):
+        self.shape, self.dtype, self.buffer = list(shape), "f32", None
+
+
+@pytest.mark.parametrize("fn,name", [(Q.matmulQ4, "matmulQ4"), (Q.matmulQ8, "matmulQ8")])
+def test_inner_dimension_mismatch_message(fn, name):
+    # src/ops/quantize.js:75-77 and :103-105 -- raised before anything touches the device
+    with pytest.raises(ValueError) as e:
+        fn(_FakeTensor([2, 48]), {"buffer": None, "K": 64, "N": 8, "groups": 2})
+    assert str(e.value) == f"{name}: inner dims don't match: 48 vs 64"
+    with pytest.raises(ValueError):
+        fn(_FakeTensor([2, 48]), Q.Quantized(buffer=None, K=64, N=8, groups=2, totalBytes=0))
+
+
+def test_pool_bucketing_and_recycling():
+    assert [pool.bucketSize(n) for n in (0, 1, 256, 257, 1000, 1024, 1025, 23_000_000)] == \
+        [256, 256, 256, 512, 1024, 1024, 2048, 1 << 25]
+    pool.poolDrain()
+    made = []
+    pool.setAllocFn(lambda nbytes, mode: made.append((nbytes, mode)) or ("buf", len(made)))
+    try:
+        a = pool.poolAlloc(1000)
+        b = pool.poolAlloc(1000, smith.PRIVATE)
+        assert made == [(1024, 0), (1024, 1)]
+        pool.poolFree(a, 1000)
+        assert pool.poolStats()["shared"] == {"count": 1, "bytes": 1024}
+        assert pool.poolAlloc(700) is a          # same bucket, recycled
+        assert pool.poolAlloc(700) != a          # bin empty again -> new allocation
+        s = pool.poolStats()
+        assert (s["hits"], s["misses"], s["totalAllocated"]) == (1, 3, 3072)
+        pool.poolFree(b, 1000, smith.PRIVATE)
+        assert pool.poolStats()["private"]["count"] == 1
+        pool.poolFree(None, 10)                  # ignored
+    finally:
+        pool.setAllocFn(None)
+        pool.poolDrain()
+
+
+class _T:
+    def __init__(self):
+        self.buffer, self.data = object(), object()
+
+
+def test_lifecycle_scopes_and_refcounts():
+    released = []
+    lifecycle.setReleaseFn(lambda t: released.append(t))
+    try:
+        kept = {}
+
+        def body():
+            a, b = _T(), _T()
+            lifecycle.trackAllocation(a)
+            lifecycle.trackAllocation(b)
+            kept["b"] = lifecycle.retain(b)
+            assert lifecycle.activeScopeDepth() == 1
+            return a
+
+        a = lifecycle.using(body)
+        assert lifecycle.isDisposed(a) and a.buffer is None and released == [a]
+        assert not lifecycle.isDisposed(kept["b"]) and kept["b"]._refCount == 1
+        lifecycle.dispose(kept["b"])
+        assert lifecycle.isDisposed(kept["b"]) and len(released) == 2
+        lifecycle.dispose(kept["b"])             # idempotent
+        assert len(released) == 2
+        with pytest.raises(RuntimeError):
+            lifecycle.withNoAlloc(lambda: lifecycle.trackAllocation(_T()))
+        lifecycle.trackAllocation(_T())          # guard is lifted afterwards
+    finally:
+        from smith_b200 import tensor  # restores the pool hook
+        from smith_b200.dtype import dtypeBytes
+        lifecycle.setReleaseFn(lambda t: pool.poolFree(t.buffer, t.size * dtypeBytes(t.dtype), t.mode))
+
+
+def test_profile_stats_shape():
+    from smith_b200.profile import computeStats
+    s = computeStats(sorted([1.0, 2.0, 3.0, 4.0]))
+    assert s == {"mean": 2.5, "median": 2.5, "min": 1.0, "max": 4.0, "p95": 4.0, "stddev": 1.118}
+    assert computeStats([])["mean"] == 0
