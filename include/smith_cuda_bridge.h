@@ -166,6 +166,11 @@ int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint6
                       uint64_t K, uint64_t groups, uint32_t path);
 /* Which path 0 would resolve to for a shape (for tests and reports). */
 int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
+/* Device-side waits in these kernels (on a shared-memory barrier, a peer's
+ * flag) are bounded; one that gives up marks the launch's result invalid.
+ * Returns 1 if that happened on this context's device since the last call
+ * (and clears the mark), 0 if not, negative on error.  Synchronises the stream. */
+int32_t smith_kernel_status(void* ctx);
 /* How many kernels this context has launched so far. */
 uint64_t smith_launch_count(void* ctx);
 

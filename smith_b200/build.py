@@ -1,6 +1,6 @@
 """Builds smith_b200/libsmith_cuda.so in-tree with nvcc for sm_100a.
 
-Usage: ``python -m smith_b200.build [--force] [--verbose]``.  nvcc
+Usage: ``python smith_b200/build.py [--force] [--verbose]``.  nvcc
 cross-compiles, so no GPU is needed to build.  This module must not import the
 package's device layer (which needs the library this produces).
 """

@@ -786,6 +786,13 @@ int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
   return resolve_path((int)kind, (int64_t)M, (int64_t)N, (int64_t)K, (int64_t)((K + 31) / 32));
 }
 
+int32_t smith_kernel_status(void* p) {
+  Context* c = as_ctx(p);
+  if (!c) return -1;
+  if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
+  return qdecode_take_status();
+}
+
 uint64_t smith_launch_count(void* p) {
   Context* c = as_ctx(p);
   return c ? c->launches : 0;

@@ -38,6 +38,8 @@ cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, f
 bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                            int64_t N, int64_t K, int64_t groups, cudaStream_t s);
+// 1 if a bounded wait inside a decode launch gave up since the last call (then clears it), 0 if not, -1 on error.
+int qdecode_take_status();
 
 // qgemm_tc.cu : M > 16, dequantise to bf16 tiles in shared memory, tcgen05 MMA, TMEM accumulators.
 bool qgemm_tc_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);

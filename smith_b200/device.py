@@ -23,7 +23,7 @@ LIB_PATH = os.path.join(_HERE, "libsmith_cuda.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"smith: {LIB_PATH} is missing. Build it with `python -m smith_b200.build` "
+        f"smith: {LIB_PATH} is missing. Build it with `python smith_b200/build.py` "
         "(nvcc, sm_100a). There is no CPU fallback.")
 
 lib = C.CDLL(LIB_PATH)
@@ -84,6 +84,7 @@ SYMBOLS = {
     "smith_q8_pack": (_i32, [_p, _p, _p, _u64, _u64]),
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
+    "smith_kernel_status": (_i32, [_p]),
     "smith_launch_count": (_u64, [_p]),
     "smith_graph_begin": (_i32, [_p]),
     "smith_graph_end": (_p, [_p]),
@@ -373,6 +374,11 @@ def qmatmul(kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path=PATH_AUTO):
 
 def qmatmulPath(kind, M, N, K):
     return int(lib.smith_qmatmul_path(kind, M, N, K))
+
+
+def kernelStatus():
+    """1 if a bounded device-side wait gave up since the last call, else 0."""
+    return int(lib.smith_kernel_status(ctx()))
 
 
 def launchCount():

@@ -11,8 +11,8 @@ if ROOT not in sys.path:
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
     # Make sure the library and the CPU checkers exist before collection imports them.
-    from smith_b200 import build as b
-    b.build()
+    import __graft_entry__
+    __graft_entry__._builder().build()
     from oracle import oracle
     if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")):
         oracle.build()

@@ -57,6 +57,7 @@ def matmul_on_device(a, packed, K, N, kind, path=device.PATH_AUTO, groups=None):
     ab, bb, cb = DevBuf.of(a), DevBuf.of(packed), DevBuf(M * N * 4)
     device.qmatmul(4 if kind == "q4" else 8, ab.handle, bb.handle, cb.handle, M, N, K, groups, path)
     device.synchronize()
+    assert device.kernelStatus() == 0, "a bounded device-side wait gave up"
     out = cb.get(np.float32).reshape(M, N)
     for b in (ab, bb, cb):
         b.free()
