@@ -157,11 +157,13 @@ int32_t smith_q8_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
 
 /* Direct, asynchronous C[M,N] = A[M,K] * dequant(B) on device-side buffers.
  * kind: 4 or 8.  path: 0 = choose by shape, 1 = any-shape CUDA-core kernel,
- * 2 = decode kernel (M <= 16), 3 = tensor-core (tcgen05) kernel. */
+ * 2 = decode kernel (M <= 16, mma.sync), 3 = tensor-core (tcgen05) kernel,
+ * 4 = GEMV kernel (M <= 4, dp4a).  A forced path that does not take the shape fails. */
 #define SMITH_PATH_AUTO 0
 #define SMITH_PATH_GENERIC 1
 #define SMITH_PATH_DECODE 2
 #define SMITH_PATH_TENSOR 3
+#define SMITH_PATH_GEMV 4
 int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint64_t M, uint64_t N,
                       uint64_t K, uint64_t groups, uint32_t path);
 /* Which path 0 would resolve to for a shape (for tests and reports). */

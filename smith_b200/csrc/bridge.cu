@@ -238,6 +238,12 @@ int do_qmatmul(Context* c, int kind, const float* A, const uint8_t* B, float* C,
                     (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
       e = launch_qdecode(kind, A, B, C, M, N, K, groups, c->stream);
       break;
+    case kGemv:
+      if (!qgemv_supports(kind, M, N, K, groups))
+        return fail("GEMV kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,
+                    (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
+      e = launch_qgemv(kind, A, B, C, M, N, K, groups, c->stream);
+      break;
     case kTensor: {
       if (!qgemm_tc_supports(kind, M, N, K, groups))
         return fail("tensor-core kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,
@@ -790,7 +796,7 @@ int32_t smith_kernel_status(void* p) {
   Context* c = as_ctx(p);
   if (!c) return -1;
   if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
-  return qdecode_take_status();
+  return kernel_take_status();
 }
 
 uint64_t smith_launch_count(void* p) {

@@ -12,7 +12,7 @@ constexpr int kQ4Bytes = 24;  // 16 nibble bytes + f32 scale + f32 zero (src/ops
 constexpr int kQ8Group = 32;  // elements per Q8 block (src/ops/quantize.js:94)
 constexpr int kQ8Bytes = 34;  // f16 scale + 32 int8 (src/ops/quantize.js:95)
 
-enum Path : int { kAuto = 0, kGeneric = 1, kDecode = 2, kTensor = 3 };
+enum Path : int { kAuto = 0, kGeneric = 1, kDecode = 2, kTensor = 3, kGemv = 4 };
 
 // Scratch memory a matmul launch may use (owned by the caller of the launch).
 struct Workspace {
@@ -38,8 +38,6 @@ cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, f
 bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                            int64_t N, int64_t K, int64_t groups, cudaStream_t s);
-// 1 if a bounded wait inside a decode launch gave up since the last call (then clears it), 0 if not, -1 on error.
-int qdecode_take_status();
 
 // qgemm_tc.cu : M > 16, dequantise to bf16 tiles in shared memory, tcgen05 MMA, TMEM accumulators.
 bool qgemm_tc_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
@@ -47,7 +45,16 @@ size_t qgemm_tc_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
 cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                             int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
 
+// qgemv.cu : M <= 4, activations as int8 digit pairs, dp4a against the packed codes.
+bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
+cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
+                         int64_t K, int64_t groups, cudaStream_t s);
+
 // util.cu
+// 1 if a bounded device-side wait gave up since the last call (then clears it), 0 if not, -1 on error.
+int kernel_take_status();
+// Device address of that status word on the current device (nullptr on error).
+int* kernel_status_ptr();
 cudaError_t launch_fill_normal(float* out, uint64_t count, uint64_t seed, float std, cudaStream_t s);
 cudaError_t launch_fill_bytes(void* out, size_t bytes, uint32_t value, cudaStream_t s);
 

@@ -40,6 +40,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "pipeline.cuh"
 
 namespace smith {
 namespace {
@@ -50,9 +51,6 @@ constexpr int kMaxSlices = 16;                   // TN <= 128 columns
 constexpr int kMaxStages = 6;
 constexpr int kRingBudget = 196 * 1024;          // bytes of shared memory for the ring
 constexpr int kHeaderBytes = 1024;               // barriers + per-row scales
-constexpr unsigned long long kWaitLimitNs = 200ull * 1000ull * 1000ull;
-
-__device__ int g_qdecode_status = 0;
 
 struct Params {
   const float* A;
@@ -63,75 +61,14 @@ struct Params {
   int row_pitch;   // bytes between group-rows inside a stage
   int stages;      // ring depth
   int stage_bytes;
+  int* status;     // device-wide "a wait gave up" word
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false if the limit ran out or another thread of the CTA gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (int spin = 0;; spin++) {
-    if (mbar_try(bar, parity)) return true;
-    if ((spin & 63) == 63) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        atomicExch(&g_qdecode_status, 1);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
-                                          uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
-      : "memory");
-}
-
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-  return v;
-}
+// Plain shared-memory loads: the compiler may schedule them freely among
+// themselves, but not above the barrier wait (whose asm clobbers memory).
+__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ uint32_t lds16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+__device__ __forceinline__ float2 lds_f2(const uint8_t* p) { return *reinterpret_cast<const float2*>(p); }
 
 // {upper 16 bits = cvt(hi_slot), lower 16 bits = cvt(lo_slot)}
 __device__ __forceinline__ uint32_t pack_bf16(float lo_slot, float hi_slot) {
@@ -148,12 +85,12 @@ __device__ __forceinline__ uint32_t pack_f16(float lo_slot, float hi_slot) {
 template <int KIND>
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   if (KIND == 4) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   } else {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -295,22 +232,27 @@ __global__ void __launch_bounds__(kThreads, 1) qdecode_kernel(const Params p) {
 
   if (warp == kWarps) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      uint64_t policy;
-      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-      for (int st = 0; st < nst; st++) {
-        const int slot = st % p.stages;
-        if (st >= p.stages) {
-          if (!mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag)) break;
-        }
-        const int rows = min(kWarps, p.G - st * kWarps);
-        const uint32_t bar = smem_u32(&full[slot]);
-        mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
-        const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
-        const uint8_t* src = p.B + ((size_t)(st * kWarps) * p.N + col0) * BB;
-        for (int rr = 0; rr < rows; rr++)
-          bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * p.N * BB, row_bytes, bar, policy);
+    // One lane per group-row: the rows of a stage are issued by the warp in
+    // parallel (a single thread issuing them one by one is too slow to keep
+    // the stream busy).  Lane 0 arms the barrier before any copy can complete.
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    bool live = true;
+    for (int st = 0; st < nst && live; st++) {
+      const int slot = st % p.stages;
+      if (st >= p.stages) {
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag, p.status);
+        live = __shfl_sync(0xffffffffu, okw, 0) != 0;
+        if (!live) break;
       }
+      const int rows = min(kWarps, p.G - st * kWarps);
+      const uint32_t bar = smem_u32(&full[slot]);
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
+      __syncwarp();
+      const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
+      const uint8_t* src = p.B + ((size_t)(st * kWarps) * p.N + col0) * BB;
+      if (lane < rows) bulk_load(dst + lane * p.row_pitch, src + (size_t)lane * p.N * BB, row_bytes, bar, policy);
     }
     return;  // consumers observe every full barrier, so the copies land before the CTA ends
   }
@@ -361,9 +303,9 @@ __global__ void __launch_bounds__(kThreads, 1) qdecode_kernel(const Params p) {
       build_a<KIND, WIDE>(af, xr, rs0, rs1);
       if (g + kWarps < p.G) load_x<WIDE>(xr, p.A, p.M, p.K, g + kWarps, r, j);
     }
-    ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag);
+    ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag, p.status);
     if (ok && g < p.G) {
-      const uint32_t row_base = smem_u32(ring + (size_t)slot * p.stage_bytes) + (uint32_t)warp * p.row_pitch;
+      const uint8_t* row_base = ring + (size_t)slot * p.stage_bytes + (size_t)warp * p.row_pitch;
 #pragma unroll
       for (int s = 0; s < kMaxSlices; s++) {
         if (s < ns) {
@@ -381,8 +323,11 @@ __global__ void __launch_bounds__(kThreads, 1) qdecode_kernel(const Params p) {
             b[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
             b[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
           } else {
-            const uint32_t a = row_base + (uint32_t)(s * 8 + r) * BB + 2 + 8 * j;
-            const uint32_t al = a & ~3u, sh = (a & 3u) * 8;
+            // the stage base is 1024-byte aligned and row pitches are multiples of 16,
+            // so the byte offset inside the stage decides the word alignment
+            const uint32_t off = (uint32_t)(s * 8 + r) * BB + 2 + 8 * j;
+            const uint8_t* al = row_base + (off & ~3u);
+            const uint32_t sh = (off & 3u) * 8;
             const uint32_t w0 = lds32(al), w1 = lds32(al + 4), w2 = lds32(al + 8);
             const uint32_t lo = __funnelshift_r(w0, w1, sh) ^ 0x80808080u;
             const uint32_t hi = __funnelshift_r(w1, w2, sh) ^ 0x80808080u;
@@ -526,17 +471,11 @@ cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C,
   Params p;
   p.A = A, p.B = B, p.C = C;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
+  p.status = kernel_status_ptr();
+  if (!p.status) return cudaErrorUnknown;
   p.TN = pl.TN, p.row_pitch = pl.row_pitch, p.stages = pl.stages, p.stage_bytes = pl.stage_bytes;
   if (kind == 4) return (M > 8) ? launch_one<4, true>(p, pl, s) : launch_one<4, false>(p, pl, s);
   return (M > 8) ? launch_one<8, true>(p, pl, s) : launch_one<8, false>(p, pl, s);
-}
-
-// Reads and clears the "a bounded wait gave up" flag of this device.
-int qdecode_take_status() {
-  int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_qdecode_status, sizeof v) != cudaSuccess) return -1;
-  if (v) cudaMemcpyToSymbol(g_qdecode_status, &zero, sizeof zero);
-  return v;
 }
 
 }  // namespace smith

@@ -1,0 +1,400 @@
+// qgemv.cu -- GEMV-shaped quantized matmul, M <= 4 rows of activations.
+//
+// C[M,N] = A[M,K] (f32) x dequant(B); B in Smith's Q4 (24-byte) or Q8 (34-byte)
+// block layout, block (g, col) at (g*N + col) * block_bytes
+// (shaders/matmul_q4.metal:47-55, shaders/matmul_q8.metal:40-48).
+//
+// One packed weight is touched by exactly one multiply-add per activation
+// row, so at M = 1 the kernel has about two instructions per weight to spend
+// before it stops being bound by HBM.  The design spends them like this:
+//
+//  * Activations are converted once per CTA into block fixed point: for each
+//    group of 32 the values are scaled by a power of two so the largest fits
+//    15 bits, rounded to an integer, and stored as two int8 digits
+//    (x_int = hi * 128 + lo, hi signed, lo in 0..127).  The digits sit in
+//    shared memory in the order the weight codes come out of a 32-bit word.
+//  * The 4-bit codes of a word are split with two masks (even codes in place,
+//    odd codes left multiplied by 16) and multiplied into the digit words
+//    with dp4a: four codes per instruction, exact int32 sums.  Q8 codes are
+//    already bytes.  The group's integer dot product is exact; it is converted
+//    to f32 once per block and scaled:
+//        Q4: acc += (scale * 2^-e) * (dot - zero * sum_k x_int)
+//        Q8: acc += (scale * 2^-e) * dot
+//    The only rounding beyond the f32 accumulation over groups is the 15-bit
+//    rounding of the activations (relative to the largest value of its group).
+//  * One CTA owns TN adjacent columns and all of K.  Thread t owns column
+//    t % TN and the group-rows of phase t / TN, so any TN that is a multiple of
+//    8 fills whole warps when the phase count is a multiple of 4.  Packed
+//    group-rows (TN * block_bytes contiguous bytes each) arrive through a ring
+//    of shared-memory stages filled by 1-D bulk async copies from a producer
+//    thread (full/empty mbarriers, no multicast); lanes read adjacent blocks.
+//  * The phases of a column are summed through shared memory in fixed order
+//    and each output is written once.  No atomics, no global scratch.
+//
+// Waits are time-bounded as in pipeline.cuh.
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "pipeline.cuh"
+
+namespace smith {
+namespace {
+
+constexpr int kMaxRowsM = 4;
+constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage
+constexpr int kMaxStages = 8;
+constexpr int kHeader = 256;               // barriers + abort flag
+constexpr int kSmemBudget = 220 * 1024;
+constexpr int kMaxConsumerThreads = 512;
+
+struct Params {
+  const float* A;
+  const uint8_t* B;
+  float* C;
+  int M, N, K, G;
+  int TN, phases, nthreads;  // consumer threads = TN * phases
+  int row_pitch, stage_rows, stage_bytes, stages;
+  int xdig_off, xsc_off, ring_off;  // byte offsets in dynamic shared memory
+  int* status;
+};
+
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_su(int a, unsigned b, int c) {  // a signed bytes, b unsigned bytes
+  int d;
+  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// Quantise the activations of one (row, group) to digit words; eight threads
+// per group, four consecutive k each (lane8 = position inside the group).
+//   digits: 64 bytes.  Q4: word i*4 + {0,1,2,3} = {even-k hi, even-k lo, odd-k hi, odd-k lo}
+//                          of k = 8i .. 8i+7 (byte b of an even word is k = 8i + 2b).
+//                      Q8: word i*2 + {0,1} = {hi, lo} of k = 4i .. 4i+3.
+//   sc: {2^-e, float(sum_k x_int)}.
+template <int KIND>
+__device__ __forceinline__ void quantise_quarter(const float* __restrict__ x, int lane8, uint8_t* digits,
+                                                 float2* sc) {
+  const float4 t = __ldg(reinterpret_cast<const float4*>(x) + lane8);
+  const float v[4] = {t.x, t.y, t.z, t.w};
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  int bad = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) bad |= !(fabsf(v[i]) <= 3.4028234e38f);  // inf or NaN
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+  }
+  const int ex = (int)(__float_as_uint(amax) >> 23) & 0xFF;
+  int e = (ex == 0) ? 0 : (13 - (ex - 127));  // amax * 2^e in [2^13, 2^14)
+  e = max(-126, min(126, e));
+  const float up = __uint_as_float((unsigned)(127 + e) << 23);
+  float down = __uint_as_float((unsigned)(127 - e) << 23);
+  if (bad) down = __int_as_float(0x7FC00000);  // let inf / NaN reach the outputs of every column
+  int q[4], sum = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    q[i] = max(-16383, min(16383, __float2int_rn(v[i] * up)));
+    sum += q[i];
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (KIND == 4) {
+    // k = 4*lane8 + i lives in code word (lane8 >> 1); even k -> bytes {0,1} or {2,3} of the even words
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int word = lane8 >> 1, byte = ((lane8 & 1) << 1) | (i >> 1), odd = i & 1;
+      uint8_t* w = digits + word * 16 + odd * 8 + byte;
+      w[0] = (uint8_t)(q[i] >> 7);
+      w[4] = (uint8_t)(q[i] & 127);
+    }
+  } else {
+    uint32_t hi = 0, lo = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      hi |= (uint32_t)((q[i] >> 7) & 0xFF) << (8 * i);
+      lo |= (uint32_t)(q[i] & 127) << (8 * i);
+    }
+    reinterpret_cast<uint2*>(digits)[lane8] = make_uint2(hi, lo);
+  }
+  if (lane8 == 0) *sc = make_float2(down, (float)sum);
+}
+
+// One 32-weight block against MR activation rows.
+template <int KIND, int MR>
+__device__ __forceinline__ void block_dot(const uint8_t* __restrict__ blk, uint32_t off_in_stage,
+                                          const uint4* __restrict__ xd, const float2* __restrict__ xs, int G,
+                                          float (&acc)[MR]) {
+  if (KIND == 4) {
+    const uint2 n0 = *reinterpret_cast<const uint2*>(blk);
+    const uint2 n1 = *reinterpret_cast<const uint2*>(blk + 8);
+    const float2 sz = *reinterpret_cast<const float2*>(blk + 16);
+    const uint32_t w[4] = {n0.x, n0.y, n1.x, n1.y};
+    uint32_t be[4], bo[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      be[i] = w[i] & 0x0F0F0F0Fu;   // codes of even k
+      bo[i] = w[i] & 0xF0F0F0F0u;   // 16 * codes of odd k
+    }
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      int eh = 0, el = 0, oh = 0, ol = 0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint4 d = xd[(size_t)m * G * 4 + i];
+        eh = dp4a_su((int)d.x, be[i], eh);
+        el = dp4a_su((int)d.y, be[i], el);
+        oh = dp4a_su((int)d.z, bo[i], oh);
+        ol = dp4a_su((int)d.w, bo[i], ol);
+      }
+      const int dot = (eh * 128 + el) + ((oh * 128 + ol) >> 4);  // odd part is an exact multiple of 16
+      const float2 s = xs[(size_t)m * G];
+      acc[m] = fmaf(sz.x * s.x, fmaf(-sz.y, s.y, (float)dot), acc[m]);
+    }
+  } else {
+    // 34-byte blocks are only 2-byte aligned: read the aligned words around the
+    // 32 code bytes and shift.  Stage base and row pitch are multiples of 16, so
+    // the offset inside the stage gives the alignment.
+    const uint32_t off = off_in_stage + 2;
+    const uint32_t sh = (off & 3u) * 8;
+    const uint32_t* al = reinterpret_cast<const uint32_t*>(blk + 2 - (off & 3u));
+    uint32_t raw[9];
+#pragma unroll
+    for (int i = 0; i < 9; i++) raw[i] = al[i];
+    uint32_t cw[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) cw[i] = __funnelshift_r(raw[i], raw[i + 1], sh);
+    const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(blk)));
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      int dh = 0, dl = 0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint4 d = xd[(size_t)m * G * 4 + i];
+        dh = dp4a_ss((int)d.x, (int)cw[2 * i], dh);
+        dl = dp4a_ss((int)d.y, (int)cw[2 * i], dl);
+        dh = dp4a_ss((int)d.z, (int)cw[2 * i + 1], dh);
+        dl = dp4a_ss((int)d.w, (int)cw[2 * i + 1], dl);
+      }
+      const float2 s = xs[(size_t)m * G];
+      acc[m] = fmaf(scale * s.x, (float)(dh * 128 + dl), acc[m]);
+    }
+  }
+}
+
+template <int KIND, int MR>
+__global__ void __launch_bounds__(kMaxConsumerThreads + 32, 1) qgemv_kernel(const Params p) {
+  constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+  uint4* xdig = reinterpret_cast<uint4*>(smem + p.xdig_off);     // [MR][G][4] uint4
+  float2* xsc = reinterpret_cast<float2*>(smem + p.xsc_off);     // [MR][G]
+  uint8_t* ring = smem + p.ring_off;
+
+  const int tid = threadIdx.x;
+  const int col0 = blockIdx.x * p.TN;
+  const int tn = min(p.TN, p.N - col0);
+  const int nthr = tn * p.phases;                 // consumer threads with work in this CTA
+  const int nwarps = (p.nthreads + 31) / 32;      // consumer warps launched
+  const int nst = (p.G + p.stage_rows - 1) / p.stage_rows;
+  const uint32_t row_bytes = (uint32_t)tn * BB;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; s++) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), nwarps);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (tid >= nwarps * 32) {
+    // ------------------------------------------------------------ producer warp
+    // One lane per group-row: the rows of a stage are issued by the warp in
+    // parallel (a single thread issuing them one by one is too slow to keep
+    // the stream busy).  Lane 0 arms the barrier before any copy can complete.
+    const int lane = tid & 31;
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    bool live = true;
+    for (int st = 0; st < nst && live; st++) {
+      const int slot = st % p.stages;
+      if (st >= p.stages) {
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag, p.status);
+        live = __shfl_sync(0xffffffffu, okw, 0) != 0;
+        if (!live) break;
+      }
+      const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
+      const uint32_t bar = smem_u32(&full[slot]);
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
+      __syncwarp();
+      const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
+      const uint8_t* src = p.B + ((size_t)st * p.stage_rows * p.N + col0) * BB;
+      for (int rr = lane; rr < rows; rr += 32)
+        bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * p.N * BB, row_bytes, bar, policy);
+    }
+    return;  // consumers observe every full barrier, so the copies land before the CTA ends
+  }
+
+  // -------------------------------------------------------------- consumers
+  // Activations -> digit words (overlaps the first weight copies).
+  // (row, group) pairs are laid out as [MR][G], which is also the order of A's 32-element chunks.
+  for (int i = tid; i < ((MR * p.G * 8 + 31) & ~31); i += nwarps * 32) {
+    const int grp = min(i >> 3, MR * p.G - 1);  // clamp keeps whole warps in the shuffles; duplicates rewrite equal bytes
+    quantise_quarter<KIND>(p.A + (size_t)grp * 32, i & 7, reinterpret_cast<uint8_t*>(xdig + (size_t)grp * 4),
+                           xsc + grp);
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+
+  const bool active = tid < nthr;
+  const int col = active ? (tid % tn) : 0;
+  const int phase = active ? (tid / tn) : 0;
+  float acc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; m++) acc[m] = 0.f;
+
+  bool ok = true;
+  for (int st = 0; st < nst && ok; st++) {
+    const int slot = st % p.stages;
+    ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag, p.status);
+    if (ok && active) {
+      const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+      const int g0 = st * p.stage_rows + phase;
+      if (st * p.stage_rows + p.stage_rows <= p.G) {
+#pragma unroll
+        for (int rr = 0; rr < kRowsPerPhase; rr++) {
+          const int row = phase + rr * p.phases;
+          const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)col * BB;
+          const int g = g0 + rr * p.phases;
+          block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, p.G, acc);
+        }
+      } else {
+        for (int rr = 0; rr < kRowsPerPhase; rr++) {
+          const int row = phase + rr * p.phases;
+          const int g = g0 + rr * p.phases;
+          if (g < p.G) {
+            const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)col * BB;
+            block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, p.G, acc);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(smem_u32(&empty[slot]));
+  }
+
+  // ---------------------------------------------- sum the phases, fixed order
+  asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every consumer is done with the ring
+  float* red = reinterpret_cast<float*>(ring);        // [phases][MR][TN]
+  if (active) {
+#pragma unroll
+    for (int m = 0; m < MR; m++) red[((size_t)phase * MR + m) * p.TN + col] = acc[m];
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+  if (*abort_flag) return;
+  for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+    const int m = i / tn, c = i - m * tn;
+    float sum = 0.f;
+    for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
+    p.C[(size_t)m * p.N + col0 + c] = sum;
+  }
+}
+
+struct Plan {
+  Params p;
+  int tiles;
+  size_t smem;
+  bool ok;
+};
+
+Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
+  const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  const int sms = 148;
+  Plan pl{};
+  Params& p = pl.p;
+  const int MR = (int)M;
+  p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)(K / 32);
+  // Tile width: the smallest multiple of 8 that covers N in a whole number of waves of CTAs.
+  int TN = 0;
+  for (int64_t waves = 1;; waves++) {
+    TN = (int)(8 * ((N + 8 * sms * waves - 1) / (8 * sms * waves)));
+    if (TN <= 128) break;
+  }
+  p.TN = TN;
+  pl.tiles = (int)((N + TN - 1) / TN);
+  // Phases: a multiple of 4 (so TN * phases fills whole warps), aiming at ~512 consumer threads.
+  int phases = (kMaxConsumerThreads / TN) & ~3;
+  if (phases < 4) phases = 4;
+  while (phases > 4 && (phases * kRowsPerPhase > p.G * 2)) phases -= 4;  // short K: do not over-split
+  p.phases = phases;
+  p.nthreads = TN * phases;
+  p.row_pitch = TN * BB;
+  p.stage_rows = phases * kRowsPerPhase;
+  p.stage_bytes = ((p.stage_rows * p.row_pitch + 15) / 16) * 16;
+  const int xdig_bytes = MR * p.G * 64, xsc_bytes = MR * p.G * 8;
+  p.xdig_off = kHeader;
+  p.xsc_off = p.xdig_off + xdig_bytes;
+  p.ring_off = ((p.xsc_off + xsc_bytes + 1023) / 1024) * 1024;
+  const int room = kSmemBudget - p.ring_off - 64;
+  int stages = room / p.stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  p.stages = stages;
+  const size_t red = (size_t)phases * MR * TN * 4;
+  const size_t ring = (size_t)stages * p.stage_bytes + 64;
+  pl.smem = p.ring_off + (ring > red ? ring : red);
+  pl.ok = stages >= 2 && p.nthreads <= kMaxConsumerThreads && pl.smem <= 227 * 1024;
+  return pl;
+}
+
+template <int KIND, int MR>
+cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(qgemv_kernel<KIND, MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int threads = ((pl.p.nthreads + 31) / 32) * 32 + 32;
+  qgemv_kernel<KIND, MR><<<pl.tiles, threads, pl.smem, s>>>(pl.p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups) {
+  if (kind != 4 && kind != 8) return false;
+  if (M < 1 || M > kMaxRowsM) return false;
+  if (N < 8 || (N % 8) != 0) return false;  // 16-byte alignment of every group-row span
+  if (K < 32 || (K % 32) != 0 || groups != K / 32) return false;
+  if (N > (1 << 30) || K > (1 << 22)) return false;
+  return make_plan(kind, M, N, K).ok;        // activations' digit form must fit beside the ring
+}
+
+cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
+                         int64_t groups, cudaStream_t s) {
+  (void)groups;
+  if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15)) return cudaErrorMisalignedAddress;
+  Plan pl = make_plan(kind, M, N, K);
+  if (!pl.ok) return cudaErrorInvalidValue;
+  pl.p.A = A, pl.p.B = B, pl.p.C = C;
+  pl.p.status = kernel_status_ptr();
+  if (!pl.p.status) return cudaErrorUnknown;
+#define SMITH_GEMV_CASE(KD, MRV) \
+  if (kind == KD && M == MRV) return launch_one<KD, MRV>(pl, s);
+  SMITH_GEMV_CASE(4, 1) SMITH_GEMV_CASE(4, 2) SMITH_GEMV_CASE(4, 3) SMITH_GEMV_CASE(4, 4)
+  SMITH_GEMV_CASE(8, 1) SMITH_GEMV_CASE(8, 2) SMITH_GEMV_CASE(8, 3) SMITH_GEMV_CASE(8, 4)
+#undef SMITH_GEMV_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace smith

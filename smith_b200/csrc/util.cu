@@ -1,10 +1,34 @@
 // util.cu -- small device utilities of the bridge: synthetic normal data for
 // benchmarks and large-shape tests, and a byte fill used to flush L2.
 #include "kernels.h"
+#include "pipeline.cuh"
 
 namespace smith {
 
 thread_local uint64_t* g_launch_counter = nullptr;
+
+__device__ int g_kernel_status = 0;
+
+// Device address of the status word on the current device (one lookup per device).
+int* kernel_status_ptr() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kernel_status) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+// Reads and clears the "a bounded device-side wait gave up" word of the current device.
+int kernel_take_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_kernel_status, sizeof v) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_kernel_status, &zero, sizeof zero);
+  return v;
+}
 
 namespace {
 

@@ -103,11 +103,13 @@ def test_matmul_auto_path_within_tolerance(kind, M, K, N):
     assert ok, f"worst err/bound = {worst}"
 
 
-@pytest.mark.parametrize("path", [device.PATH_GENERIC, device.PATH_DECODE, device.PATH_TENSOR])
+@pytest.mark.parametrize("path", [device.PATH_GENERIC, device.PATH_DECODE, device.PATH_TENSOR, device.PATH_GEMV])
 @pytest.mark.parametrize("kind", ["q4", "q8"])
 def test_matmul_each_path_where_supported(kind, path):
     shapes = {device.PATH_GENERIC: [(1, 64, 32), (9, 1000, 77)],
               device.PATH_DECODE: [(1, 4096, 1024), (5, 1024, 256), (16, 2048, 640), (8, 4096, 98)],
+              device.PATH_GEMV: [(1, 4096, 1024), (2, 1024, 256), (4, 2048, 640), (3, 4096, 104), (1, 14336, 512),
+                                 (1, 64, 8), (2, 28672, 64)],
               device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384)]}[path]
     for M, K, N in shapes:
         a, w = _data(M + K + N + path, M, K, N)
