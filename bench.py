@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path (quantizeQ4/Q8 -> matmulQ4/Q8) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A "step" is one pass of the hot path over R distinct, device-resident packed
+weight matrices of the workload's shape (R chosen so that R x bytes is at least
+four times the 126 MB L2: consecutive launches never find their weights in
+cache).  The R launches of a step are captured once in a CUDA graph and
+replayed, the way a decode engine replays its layer stack.  Timing is CUDA
+events on the launching stream, max over ranks, between barriers.
+
+`value`  : algorithmic bytes (M <= 16) or FLOPs (M >= 64) of all launches / device time.
+`e2e`    : the same quantity through the operator API (smith_b200.matmulQ4 /
+           matmulQ8 on host-resident activation tensors): every call copies the
+           activations host->device from page-locked memory, runs the kernel,
+           copies the result device->host and waits, exactly what the JS
+           operator does per call.  Packed weights stay resident, as they do in
+           the reference (they are a device buffer returned by quantizeQ4).
+`roofline`: achieved/peak for the dominant kernel, peak from MEASURED_PEAKS.json.
+`cpu_baseline`: the reference's own shader source compiled as C++ (oracle/_ref)
+           or, failing that, this repository's C restatement, on the host cores.
+
+With N > 1 (launched by torch.distributed.run) the weights are sharded along
+the output dimension N, activations are replicated, and each step ends with an
+all-gather of the output row slices (strong scaling of a fixed problem).
+
+Synthetic data: weights ~N(0, 0.02), activations ~N(0, 1), generated on the
+device by the bridge's counter-based generator, packed by the CUDA packers.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: kind, M, K, N, weight std
+    "q4_decode_gemv_4096x14336_m1": dict(kind=4, M=1, K=4096, N=14336, std=0.02),   # configs[2], M=1 (the 70 % target)
+    "q4_decode_4096x14336_m4": dict(kind=4, M=4, K=4096, N=14336, std=0.02),
+    "q4_decode_4096x14336_m16": dict(kind=4, M=16, K=4096, N=14336, std=0.02),
+    "q4_prefill_4096x14336_m64": dict(kind=4, M=64, K=4096, N=14336, std=0.02),
+    "q4_prefill_4096x14336_m256": dict(kind=4, M=256, K=4096, N=14336, std=0.02),
+    "q4_prefill_4096x14336_m512": dict(kind=4, M=512, K=4096, N=14336, std=0.02),   # the 50 % tensor target
+    "q8_prefill_gemm_4096x11008_m512": dict(kind=8, M=512, K=4096, N=11008, std=0.02),  # configs[1]
+    "q4_gemv_4096x4096_m1": dict(kind=4, M=1, K=4096, N=4096, std=0.02),            # configs[0]
+    "q4_lm_head_4096x128256_m1": dict(kind=4, M=1, K=4096, N=128256, std=0.02),
+    "q8_decode_gemv_4096x14336_m1": dict(kind=8, M=1, K=4096, N=14336, std=0.02),
+}
+DEFAULT = "q4_decode_gemv_4096x14336_m1"
+L2_BYTES = 126e6
+
+
+def algorithmic(kind, M, K, N):
+    bb = 24 if kind == 4 else 34
+    nbytes = ((K + 31) // 32) * N * bb + 4 * M * K + 4 * M * N
+    return nbytes, 2 * M * K * N
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tensor=d["bf16_tflops"], source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, source="fallback")
+
+
+def traffic_for(name):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, or None."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get(name)
+    return None
+
+
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 8 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 8 for n, v in zip(names, r[4:8]) if v.lower() == "active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arms
+def cpu_run(kind, M, K, N, seconds, threads=None):
+    """Times the reference's CPU arithmetic on one packed matrix of the workload's shape.
+
+    Uses oracle/_ref (the reference's shader source compiled as C++) when built,
+    else the oracle port.  For shapes whose full run is long, a column window is
+    timed and scaled; `sample` says what ran."""
+    import numpy as np
+    from oracle import oracle as O
+    knd = "q4" if kind == 4 else "q8"
+    threads = threads or O.max_threads()
+    use_ref = O.have_ref()
+    fn = O.ref_matmul if use_ref else O.matmul
+    rng = np.random.default_rng(0)
+    macs = M * K * N
+    cols = N
+    budget = 4e9 * threads / 8          # MACs that finish in a few seconds on these cores
+    if macs > budget:
+        cols = max(64, int(N * budget / macs) // 64 * 64)
+    w = (rng.standard_normal((K, cols)) * 0.02).astype(np.float32)
+    packed = O.quantize_q4(w) if kind == 4 else O.quantize_q8(w)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    fn(a, packed, K, cols, knd, threads=threads)   # warm
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        fn(a, packed, K, cols, knd, threads=threads)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el >= seconds:
+            break
+    per_call = el / reps * (N / cols)
+    sample = (f"{reps} runs of {'all' if cols == N else str(cols) + ' of ' + str(N)} columns"
+              f"{'' if cols == N else ' (time scaled to all columns)'}, {el:.1f} s of CPU work")
+    return per_call, threads, ("reference" if use_ref else "port"), sample
+
+
+def metric_of(kind, M, K, N, seconds_per_call):
+    nbytes, flops = algorithmic(kind, M, K, N)
+    if M <= 16:
+        return nbytes / seconds_per_call / 1e9, "GB/s"
+    return flops / seconds_per_call / 1e12, "TFLOP/s"
+
+
+def metric_name(M):
+    return ("Q4/Q8 matmul HBM GB/s (algorithmic bytes / time)" if M <= 16
+            else "Q4/Q8 matmul TFLOP/s (2*M*K*N / time)")
+
+
+def run_reference_arm(args, wl, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    info = None
+    for i in range(args.warmup + args.steps):
+        per_call, threads, kind, sample = cpu_run(wl["kind"], wl["M"], wl["K"], wl["N"], seconds=1.0)
+        info = (threads, kind, sample)
+        if i >= args.warmup:
+            times.append(per_call)
+    per_call = sum(times) / len(times)
+    value, unit = metric_of(wl["kind"], wl["M"], wl["K"], wl["N"], per_call)
+    threads, kind, sample = info
+    line = {
+        "impl": "reference", "metric": metric_name(wl["M"]), "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_call * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "launches_per_step": 1,
+                   "note": "the reference's own CPU implementation of the path (its matmul shader source compiled "
+                           "as C++ when oracle/_ref is built, else the C restatement), all host threads; "
+                           "the reference's Metal path is unavailable on this box"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference_arm(args, wl, args.workload)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import smith_b200 as smith
+    from smith_b200 import device as D
+    from smith_b200 import parallel as P
+
+    kind, M, K, N = wl["kind"], wl["M"], wl["K"], wl["N"]
+    warm = max(args.warmup, 3)
+    bb = 24 if kind == 4 else 34
+    G = K // 32
+    n0, n1 = P.column_shard(N, world, rank)      # this rank's output columns
+    Nl = n1 - n0
+    wbytes_full = G * N * bb
+    R = max(2, int(-(-4 * L2_BYTES // wbytes_full)))
+    D.ctx()
+    stream = torch.cuda.ExternalStream(D.stream())
+
+    # ---- synthetic weights: generated and packed on the device, shard by shard
+    wtmp = D.alloc(K * Nl * 4, D.PRIVATE)
+    packs = []
+    for i in range(R):
+        D.fillNormal(wtmp, K * Nl, 1000 * (i + 1) + rank, wl["std"])
+        pk = D.alloc(G * Nl * bb, D.PRIVATE)
+        (D.q4Pack if kind == 4 else D.q8Pack)(wtmp, pk, K, Nl)
+        packs.append(pk)
+    D.synchronize()
+    D.releaseBuffer(wtmp)
+    a_dev = D.alloc(M * K * 4, D.PRIVATE)
+    D.fillNormal(a_dev, M * K, 7, 1.0)            # same seed on every rank: replicated activations
+    gather = P.OutputGather(M, N, world, rank) if world > 1 else None
+    c_dev = gather.local_buf if gather else D.alloc(M * Nl * 4, D.PRIVATE)
+
+    def one_pass():
+        for pk in packs:
+            D.qmatmul(kind, a_dev, pk, c_dev, M, Nl, K, G, D.PATH_AUTO)
+            if gather:
+                gather.enqueue()
+
+    one_pass()                                    # sizes scratch before capture
+    D.synchronize()
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up during warm-up")
+    graph = None
+    if not gather or gather.capturable:
+        D.graphBegin()
+        one_pass()
+        graph = D.graphEnd()
+
+    def step():
+        if graph:
+            D.graphLaunch(graph)
+        else:
+            one_pass()
+
+    def barrier():
+        D.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(warm):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = D.launchCount()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches_value = (D.launchCount() - launches0) or (args.steps * R * (2 if gather else 1))
+    if graph:
+        launches_value = args.steps * R * ((1 + gather.kernels_per_call) if gather else 1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- end to end through the operator API, host-resident activations and outputs
+    a_host = smith.tensorFrom(D.download(a_dev, M * K * 4, np.float32), [M, K])
+    wqs = [smith.ops.quantize.Quantized(buffer=pk, K=K, N=Nl, groups=G, totalBytes=G * Nl * bb) for pk in packs]
+    mm = smith.matmulQ4 if kind == 4 else smith.matmulQ8
+
+    sharded = [P.ShardedMatmul(kind, K, N, pk, M, world, rank) for pk in packs] if world > 1 else None
+    a_np = smith.toNumpy(a_host)
+
+    def e2e_pass():
+        if sharded:                       # multi-GPU: upload, shard matmul, all-gather, download full rows
+            for sm in sharded:
+                sm.forward(a_np)
+        else:                             # the reference's operator call
+            for wq in wqs:
+                smith.dispose(mm(a_host, wq))
+
+    for _ in range(2):
+        e2e_pass()
+    barrier()
+    launches1 = D.launchCount()
+    e2e_steps = max(3, min(args.steps, 100))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    launches_e2e = D.launchCount() - launches1
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    status = D.kernelStatus()
+    if status != 0:
+        raise SystemExit("a bounded device-side wait gave up: results invalid")
+
+    if rank == 0:
+        per_launch_s = ms * 1e-3 / (args.steps * R)
+        value, unit = metric_of(kind, M, K, N, per_launch_s)
+        e2e_value, _ = metric_of(kind, M, K, N, e2e_s / (e2e_steps * R))
+        peaks = measured_peaks()
+        nbytes_l, flops_l = algorithmic(kind, M, K, Nl)       # what this rank's kernel moves per launch
+        if M <= 64:
+            ach, peak, runit, bound = nbytes_l / per_launch_s / 1e9, peaks["hbm"], "GB/s", "hbm"
+        else:
+            ach, peak, runit, bound = flops_l / per_launch_s / 1e12, peaks["tensor"], "TFLOP/s", "tensor"
+        path = {0: "auto", 1: "generic", 2: "decode_mma", 3: "tensor_tcgen05", 4: "gemv_dp4a"}[D.qmatmulPath(kind, M, Nl, K)]
+        line = {
+            "metric": metric_name(M), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 accumulate over u4/i8 codes" if kind == 4 else "f32 accumulate over i8 codes",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "kind": f"q{kind}", "M": M, "K": K, "N": N,
+                       "launches_per_step": R, "kernel": path,
+                       "sharding": f"N-sharded over {world} GPU(s), all-gather of outputs" if world > 1 else "single GPU",
+                       "l2": f"defeated by rotating over {R} distinct packed matrices per step "
+                             f"({R * wbytes_full / 1e6:.0f} MB > 4 x 126 MB L2)",
+                       "timing": "CUDA events on the launch stream around a replayed CUDA graph, max over ranks"},
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": R * 4 * M * K * world,
+                    "d2h_bytes_per_step": R * 4 * M * (N if world > 1 else Nl) * world, "steps": e2e_steps,
+                    "note": "operator API per call: H2D activations from page-locked memory, kernel, D2H result, wait"},
+            "gpu_launches": int(launches_value + launches_e2e),
+            "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": runit, "frac": ach / peak,
+                         "traffic": traffic_for(args.workload) if world == 1 else None,
+                         "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
+                         else "fallback (no MEASURED_PEAKS.json)",
+                         "frac_of_nominal": ach / (8000.0 if bound == "hbm" else 2250.0),
+                         "algorithmic_per_launch": nbytes_l if bound == "hbm" else flops_l},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            per_call, threads, ckind, sample = cpu_run(kind, M, K, N, seconds=args.cpu_seconds)
+            cv, cu = metric_of(kind, M, K, N, per_call)
+            line["cpu_baseline"] = {"value": cv, "unit": cu, "cores": threads, "kind": ckind, "sample": sample}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
