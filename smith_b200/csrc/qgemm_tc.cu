@@ -1,7 +1,533 @@
-// placeholder until the tensor-core kernel lands
+// qgemm_tc.cu -- prefill-shaped quantized matmul, M > 16, on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// C[M,N] = A[M,K] (f32) x dequant(B); B in Smith's Q4 (24-byte) or Q8 (34-byte)
+// block layout, block (g, col) at (g*N + col) * block_bytes
+// (shaders/matmul_q4.metal:47-55, shaders/matmul_q8.metal:40-48).
+//
+// Two launches:
+//  1. convert_activations: A f32 -> 16-bit [M,K] in scratch memory.  Q4 uses
+//     bf16 (same exponent range as f32).  Q8 uses f16 -- its block scale is an
+//     f16 number by format, so scale * code is formed exactly in f16 -- with
+//     each activation row pre-multiplied by a power of two that moves its
+//     largest magnitude into [2^13, 2^14); the inverse is applied in the epilogue.
+//  2. qgemm_tc_kernel: one CTA computes MT x 128 rows by BN columns.
+//     warp 0     producer: per 64-wide k-block, TMA-loads the MT activation
+//                tiles (128 x 64, 128-byte swizzle) and bulk-copies the two
+//                packed group-rows of the tile's BN columns into a stage.
+//     warp 1     allocates tensor memory and issues the MMAs: per k-block and
+//                row tile four tcgen05.mma (128 x BN x 16), A and B from
+//                shared memory through K-major 128-byte-swizzle descriptors,
+//                D = f32 in TMEM; tcgen05.commit releases the stage.
+//     warps 2-9  dequantise: each thread takes a (column, group) block of the
+//                stage, forms scale * (code - zero) (Q4, f32 arithmetic, rounded
+//                once to bf16) or code * scale (Q8, f16), and stores 16-byte
+//                chunks into the K-major swizzled B tile, then
+//                fence.proxy.async + mbarrier arrive.
+//     warps 2-5  epilogue: tcgen05.ld their 32-lane quarter of each
+//                accumulator, 32 columns at a time, and store C rows.
+//   Weights of a tile are dequantised once and feed MT row tiles, so for
+//   M >= 256 the CUDA-core dequantisation stays below the tensor time.
+//
+// No multicast, no clusters.  Every mbarrier wait is time-bounded
+// (pipeline.cuh); on a give-up the CTA skips to the end, frees its TMEM and
+// leaves the status word set.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "kernels.h"
+#include "pipeline.cuh"
+
 namespace smith {
-bool qgemm_tc_supports(int, int64_t, int64_t, int64_t, int64_t) { return false; }
-size_t qgemm_tc_workspace_bytes(int, int64_t, int64_t, int64_t) { return 0; }
-cudaError_t launch_qgemm_tc(int, const float*, const uint8_t*, float*, int64_t, int64_t, int64_t, int64_t, Workspace, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+constexpr int kBM = 128;            // rows per MMA / per accumulator
+constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of 16-bit values
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (2 + kDequantWarps) * 32;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 224 * 1024;
+
+struct Params {
+  const uint8_t* B;
+  float* C;
+  const float* row_inv;   // Q8: per-row inverse prescale, else nullptr
+  int M, N, K, G;
+  int BN;                 // columns per CTA, multiple of 16, <= 256
+  int stages;
+  int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;  // per-stage layout
+  int tmem_cols;
+  int* status;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
 }
+__device__ __forceinline__ void bulk_load_plain(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] x B[smem], 128 x N x 16, 16-bit inputs, f32 accumulate.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// mbarrier arrive once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, groups of 8 rows 1024 bytes apart.  Fields (bit positions):
+//   [0,14)  start address >> 4        [16,30) leading byte offset >> 4 (unused here)
+//   [32,46) stride byte offset >> 4   [46,48) descriptor version = 1
+//   [49,52) base offset = 0 (tiles are 1024-byte aligned)   [61,64) layout: 2 = 128-byte swizzle
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: f32 accumulate, A and B both
+// K-major, 16-bit format `fmt` (0 = f16, 1 = bf16), M = 128, N = n.
+//   [4,6) D format: 1 = f32   [7,10) A format   [10,13) B format
+//   [15] A major (0 = K)  [16] B major (0 = K)  [17,23) N >> 3   [24,29) M >> 4
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, int n) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kBM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- activations -> 16 bit
+template <int KIND>
+__global__ void __launch_bounds__(256) convert_activations(const float* __restrict__ A, uint16_t* __restrict__ out,
+                                                            float* __restrict__ row_inv, int M, int K) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const float* src = A + (size_t)row * K;
+  float up = 1.f;
+  if (KIND == 8) {
+    float m = 0.f;
+    for (int k = threadIdx.x; k < K; k += 256) m = fmaxf(m, fabsf(src[k]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) m = fmaxf(m, red[i]);
+    const int ex = (int)(__float_as_uint(m) >> 23) & 0xFF;
+    int e = (ex == 0 || ex == 255) ? 0 : (13 - (ex - 127));
+    e = max(-100, min(100, e));
+    up = __uint_as_float((unsigned)(127 + e) << 23);
+    if (threadIdx.x == 0) row_inv[row] = __uint_as_float((unsigned)(127 - e) << 23);
+  }
+  uint16_t* dst = out + (size_t)row * K;
+  for (int k = threadIdx.x * 2; k < K; k += 512) {
+    const float2 v = *reinterpret_cast<const float2*>(src + k);
+    uint32_t packed;
+    if (KIND == 4) {
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(v.y), "f"(v.x));
+    } else {
+      asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(v.y * up), "f"(v.x * up));
+    }
+    *reinterpret_cast<uint32_t*>(dst + k) = packed;
+  }
+}
+
+// ---------------------------------------------------------------- dequantise one (column, group) block
+// Writes the 32 values k = 32*gl .. 32*gl+31 of B-tile row `col` (K-major,
+// 128-byte swizzle: 16-byte chunk c of row n sits at chunk position c ^ (n & 7)).
+template <int KIND>
+__device__ __forceinline__ void dequant_block(const uint8_t* __restrict__ pk, uint32_t pk_off, uint8_t* __restrict__ bt,
+                                              int col, int gl, bool zero_fill) {
+  uint8_t* row = bt + (size_t)(col >> 3) * 1024 + (col & 7) * 128;
+  const int sw = col & 7;
+  if (zero_fill) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(row + (((4 * gl + i) ^ sw) << 4)) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint8_t* blk = pk + pk_off;
+  if (KIND == 4) {
+    const uint2 n0 = *reinterpret_cast<const uint2*>(blk);
+    const uint2 n1 = *reinterpret_cast<const uint2*>(blk + 8);
+    const float2 sz = *reinterpret_cast<const float2*>(blk + 16);
+    const uint32_t w[4] = {n0.x, n0.y, n1.x, n1.y};
+    const float s = sz.x;
+    const float nb = -(128.f + sz.y) * s;   // value = (128 + code) * s + nb = s * (code - zero), one rounding
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint32_t r[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) r[j] = ((w[i] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16 (128+q_j, 128+q_{j+4})
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        v[j] = fmaf(__uint_as_float(r[j] << 16), s, nb);
+        v[j + 4] = fmaf(__uint_as_float(r[j] & 0xFFFF0000u), s, nb);
+      }
+      uint4 o;
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o.x) : "f"(v[1]), "f"(v[0]));
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o.y) : "f"(v[3]), "f"(v[2]));
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o.z) : "f"(v[5]), "f"(v[4]));
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o.w) : "f"(v[7]), "f"(v[6]));
+      *reinterpret_cast<uint4*>(row + (((4 * gl + i) ^ sw) << 4)) = o;
+    }
+  } else {
+    // 34-byte blocks are 2-byte aligned: read aligned words around the codes and shift
+    const uint32_t off = pk_off + 2;
+    const uint32_t sh = (off & 3u) * 8;
+    const uint32_t* al = reinterpret_cast<const uint32_t*>(blk + 2 - (off & 3u));
+    uint32_t raw[9];
+#pragma unroll
+    for (int i = 0; i < 9; i++) raw[i] = al[i];
+    const uint32_t h = *reinterpret_cast<const unsigned short*>(blk);
+    const uint32_t s2 = h | (h << 16);
+    const uint32_t k1152 = 0x64806480u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const uint32_t u = __funnelshift_r(raw[2 * i + j], raw[2 * i + j + 1], sh) ^ 0x80808080u;
+        uint32_t p0 = __byte_perm(u, 0x64646464u, 0x4140);   // f16 (1024 + u0, 1024 + u1)
+        uint32_t p1 = __byte_perm(u, 0x64646464u, 0x4342);
+        asm("sub.f16x2 %0, %0, %1;" : "+r"(p0) : "r"(k1152));  // exact codes
+        asm("sub.f16x2 %0, %0, %1;" : "+r"(p1) : "r"(k1152));
+        asm("mul.f16x2 %0, %1, %2;" : "=r"(o[2 * j]) : "r"(p0), "r"(s2));
+        asm("mul.f16x2 %0, %1, %2;" : "=r"(o[2 * j + 1]) : "r"(p1), "r"(s2));
+      }
+      *reinterpret_cast<uint4*>(row + (((4 * gl + i) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- main kernel
+template <int KIND, int MT>
+__global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                               const Params p) {
+  constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  // header (first 1024 bytes): barriers, TMEM base, abort flag
+  uint64_t* full_in = reinterpret_cast<uint64_t*>(smem);          // [kMaxStages] TMA landed
+  uint64_t* b_ready = full_in + kMaxStages;                        // [kMaxStages] B tile written
+  uint64_t* empty = b_ready + kMaxStages;                          // [kMaxStages] MMAs of the stage done
+  uint64_t* acc_ready = empty + kMaxStages;                        // [1]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  uint8_t* stages = smem + 1024;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int col0 = blockIdx.x * p.BN;
+  const int row0 = blockIdx.y * (MT * kBM);
+  const int tn = min(p.BN, p.N - col0);
+  const int nkb = (p.K + kBK - 1) / kBK;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; s++) {
+      mbar_init(smem_u32(&full_in[s]), 1);
+      mbar_init(smem_u32(&b_ready[s]), kDequantWarps);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    mbar_init(smem_u32(acc_ready), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_base_slot), (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; kb++) {
+        const int s = kb % p.stages;
+        if (kb >= p.stages) {
+          if (!mbar_wait(smem_u32(&empty[s]), ((kb / p.stages) - 1) & 1, abort_flag, p.status)) break;
+        }
+        uint8_t* st = stages + (size_t)s * p.stage_bytes;
+        const uint32_t bar = smem_u32(&full_in[s]);
+        const int g0 = kb * 2;
+        const int ngr = min(2, p.G - g0);
+        mbar_expect_tx(bar, (uint32_t)(MT * kBM * kBK * 2) + (uint32_t)ngr * (uint32_t)tn * BB);
+#pragma unroll
+        for (int t = 0; t < MT; t++)
+          tma_load_2d(smem_u32(st + t * (kBM * kBK * 2)), &tmap_a, kb * kBK, row0 + t * kBM, bar);
+        for (int gl = 0; gl < ngr; gl++)
+          bulk_load_plain(smem_u32(st + p.a_bytes + gl * p.pk_pitch),
+                          p.B + ((size_t)(g0 + gl) * p.N + col0) * BB, (uint32_t)tn * BB, bar);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(KIND == 4 ? 1 : 0, p.BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; kb++) {
+        const int s = kb % p.stages;
+        const uint32_t par = (kb / p.stages) & 1;
+        ok = mbar_wait(smem_u32(&full_in[s]), par, abort_flag, p.status) &&
+             mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* st = stages + (size_t)s * p.stage_bytes;
+        const uint32_t a_addr = smem_u32(st);
+        const uint32_t b_addr = smem_u32(st + p.a_bytes + p.pk_bytes);
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+#pragma unroll
+          for (int j = 0; j < kBK / 16; j++) {
+            // 16 k = 32 bytes further along the swizzled 128-byte row
+            const uint64_t ad = smem_desc_sw128(a_addr + t * (kBM * kBK * 2) + j * 32);
+            const uint64_t bd = smem_desc_sw128(b_addr + j * 32);
+            umma_f16(tmem_base + (uint32_t)(t * p.BN), ad, bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(&empty[s]));
+      }
+      if (ok) umma_commit(smem_u32(acc_ready));
+    }
+  } else {
+    // ------------------------------------------------------------ dequantise
+    const int dt = tid - 64;  // 0 .. 255
+    bool ok = true;
+    for (int kb = 0; kb < nkb && ok; kb++) {
+      const int s = kb % p.stages;
+      ok = mbar_wait(smem_u32(&full_in[s]), (kb / p.stages) & 1, abort_flag, p.status);
+      if (!ok) break;
+      uint8_t* st = stages + (size_t)s * p.stage_bytes;
+      const uint8_t* pk = st + p.a_bytes;
+      uint8_t* bt = st + p.a_bytes + p.pk_bytes;
+      const int g0 = kb * 2;
+      for (int it = dt; it < 2 * p.BN; it += kDequantWarps * 32) {
+        const int gl = it / p.BN, col = it - gl * p.BN;
+        const bool zero = (col >= tn) || (g0 + gl >= p.G);
+        dequant_block<KIND>(pk, (uint32_t)(gl * p.pk_pitch + col * BB), bt, col, gl, zero);
+      }
+      fence_async_smem();       // make the generic-proxy stores visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&b_ready[s]));
+    }
+    // ---------------------------------------------------------- epilogue (warps 2..5)
+    if (warp < 6) {
+      const bool got = ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status);
+      tc_fence_after();
+      if (got) {
+        const int q = warp & 3;                          // TMEM lane quarter this warp may read
+#pragma unroll 1
+        for (int t = 0; t < MT; t++) {
+          const int row = row0 + t * kBM + q * 32 + lane;
+          const float inv = (KIND == 8 && row < p.M) ? p.row_inv[row] : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < p.BN; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
+            tmem_ld_wait();
+            if (row < p.M) {
+              float* dst = p.C + (size_t)row * p.N + col0 + c;
+              if (c + 32 <= tn && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                  float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                         __uint_as_float(r[i + 3]));
+                  if (KIND == 8) v.x *= inv, v.y *= inv, v.z *= inv, v.w *= inv;
+                  *reinterpret_cast<float4*>(dst + i) = v;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                  if (c + i < tn) dst[i] = __uint_as_float(r[i]) * inv;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+struct Plan {
+  int MT, BN, stages, tmem_cols;
+  int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;
+  size_t smem;
+  dim3 grid;
+};
+
+Plan make_plan(int kind, int64_t M, int64_t N) {
+  const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  Plan pl{};
+  pl.MT = (M > kBM) ? 2 : 1;
+  const int64_t mtiles = (M + pl.MT * kBM - 1) / (pl.MT * kBM);
+  // Column tile: the multiple of 16 in [64, 256] that wastes the least of the
+  // machine (partial last tile x partial last wave); wider wins ties.
+  double best = -1.0;
+  int bestBN = 128;
+  for (int bn = 256; bn >= 64; bn -= 16) {
+    const int64_t nt = (N + bn - 1) / bn;
+    const int64_t ctas = nt * mtiles;
+    const int64_t waves = (ctas + 147) / 148;
+    const double eff = ((double)N / (double)(nt * bn)) * ((double)ctas / (double)(waves * 148));
+    if (eff > best + 1e-9) best = eff, bestBN = bn;
+  }
+  pl.BN = bestBN;
+  pl.a_bytes = pl.MT * kBM * kBK * 2;
+  pl.pk_pitch = ((pl.BN * BB + 15) / 16) * 16;
+  pl.pk_bytes = ((2 * pl.pk_pitch + 16 + 1023) / 1024) * 1024;   // + slack for the Q8 read-ahead
+  pl.b_bytes = pl.BN * kBK * 2;
+  pl.stage_bytes = pl.a_bytes + pl.pk_bytes + pl.b_bytes;        // every part a multiple of 1024
+  pl.stages = (kSmemBudget - 1024) / pl.stage_bytes;
+  if (pl.stages > kMaxStages) pl.stages = kMaxStages;
+  int cols = 32;
+  while (cols < pl.MT * pl.BN) cols <<= 1;
+  pl.tmem_cols = cols;
+  pl.smem = 1024 + (size_t)pl.stages * pl.stage_bytes;
+  pl.grid = dim3((unsigned)((N + pl.BN - 1) / pl.BN), (unsigned)mtiles);
+  return pl;
+}
+
+template <int KIND, int MT>
+cudaError_t launch_main(const CUtensorMap& map, const Params& p, const Plan& pl, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  qgemm_tc_kernel<KIND, MT><<<pl.grid, kThreads, pl.smem, s>>>(map, p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool qgemm_tc_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups) {
+  if (kind != 4 && kind != 8) return false;
+  if (M < 1 || M > (1 << 24)) return false;
+  if (N < 8 || (N % 8) != 0) return false;              // 16-byte alignment of group-row spans
+  if (K < 32 || (K % 32) != 0 || groups != K / 32) return false;
+  if (N > (1 << 30) || K > (1 << 24)) return false;
+  if ((M + 255) / 256 > 65535) return false;
+  return encode_fn() != nullptr;
+}
+
+size_t qgemm_tc_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
+  (void)kind;
+  (void)N;
+  return (size_t)M * K * 2 + 256 + (size_t)M * 4;
+}
+
+cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
+                            int64_t groups, Workspace ws, cudaStream_t s) {
+  if (ws.bytes < qgemm_tc_workspace_bytes(kind, M, N, K) || !ws.ptr) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 7) ||
+      (reinterpret_cast<uintptr_t>(ws.ptr) & 255))
+    return cudaErrorMisalignedAddress;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  uint16_t* a16 = static_cast<uint16_t*>(ws.ptr);
+  const size_t a16_bytes = ((size_t)M * K * 2 + 255) & ~size_t(255);
+  float* row_inv = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + a16_bytes);
+
+  if (kind == 4)
+    convert_activations<4><<<(unsigned)M, 256, 0, s>>>(A, a16, row_inv, (int)M, (int)K);
+  else
+    convert_activations<8><<<(unsigned)M, 256, 0, s>>>(A, a16, row_inv, (int)M, (int)K);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
+  const Plan pl = make_plan(kind, M, N);
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&map, kind == 4 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+
+  Params p{};
+  p.B = B, p.C = C, p.row_inv = (kind == 8) ? row_inv : nullptr;
+  p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
+  p.BN = pl.BN, p.stages = pl.stages;
+  p.a_bytes = pl.a_bytes, p.pk_pitch = pl.pk_pitch, p.pk_bytes = pl.pk_bytes, p.b_bytes = pl.b_bytes;
+  p.stage_bytes = pl.stage_bytes, p.tmem_cols = pl.tmem_cols;
+  p.status = kernel_status_ptr();
+  if (!p.status) return cudaErrorUnknown;
+  if (kind == 4) return pl.MT == 2 ? launch_main<4, 2>(map, p, pl, s) : launch_main<4, 1>(map, p, pl, s);
+  return pl.MT == 2 ? launch_main<8, 2>(map, p, pl, s) : launch_main<8, 1>(map, p, pl, s);
+}
+
+}  // namespace smith
