@@ -110,7 +110,7 @@ def test_matmul_each_path_where_supported(kind, path):
               device.PATH_DECODE: [(1, 4096, 1024), (5, 1024, 256), (16, 2048, 640), (8, 4096, 98)],
               device.PATH_GEMV: [(1, 4096, 1024), (2, 1024, 256), (4, 2048, 640), (3, 4096, 104), (1, 14336, 512),
                                  (1, 64, 8), (2, 28672, 64)],
-              device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384)]}[path]
+              device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384), (300, 1056, 72)]}[path]
     for M, K, N in shapes:
         a, w = _data(M + K + N + path, M, K, N)
         packed = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
