@@ -176,6 +176,33 @@ int32_t smith_kernel_status(void* ctx);
 /* How many kernels this context has launched so far. */
 uint64_t smith_launch_count(void* ctx);
 
+/* No counterpart in the reference.  The same product as smith_qmatmul, for
+ * callers that cannot allocate device memory when they make the call: a
+ * serving process whose memory was all handed to its own arena at start-up, a
+ * latency-critical loop or host callback where cudaMalloc (which synchronises
+ * the device) is off limits, or a runtime that holds raw device pointers and
+ * no smith context.  It takes raw device pointers (a: f32 [M,K], b: packed
+ * blocks, c: f32 [M,N], all on the current device, a and b 16-byte aligned) and
+ * a cudaStream_t (NULL = default stream), always runs the tensor-core kernel,
+ * and keeps that kernel's scratch (a 16-bit copy of the activations) in a
+ * fixed 8 MiB array inside the library image instead of allocating it.
+ *   - Limit: M*K*2 (rounded up to 256) + 256 + M*4 bytes must fit in 8 MiB
+ *     (for example M*K <= 4 Mi elements less a little); larger calls are
+ *     refused with an error, as are shapes the tensor-core kernel does not take
+ *     (N % 8, K % 32, groups == K/32; Q4 needs K >= 1024).
+ *   - Every GPU that loads the library holds the 8 MiB until the process exits.
+ *   - The first call on a device looks up the array's device address (and the
+ *     first call of each kernel variant sets its shared-memory attribute): make
+ *     that first call before any stream capture.
+ *   - All calls on a device share the one array and find in it whatever the
+ *     previous call left; nothing in it needs to start at zero.  Two calls that
+ *     overlap on the GPU (different streams, or graphs replayed concurrently)
+ *     race on it: keep calls on one device ordered.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Asynchronous on `stream`.  Returns 0 on success, non-zero with smith_last_error() set. */
+int32_t smith_qmatmul_static(uint32_t kind, const void* a_dev, const void* b_dev, void* c_dev, uint64_t M,
+                             uint64_t N, uint64_t K, uint64_t groups, void* stream);
+
 /* CUDA-graph capture of a sequence of the asynchronous calls above. */
 int32_t smith_graph_begin(void* ctx);
 void* smith_graph_end(void* ctx); /* executable graph handle, NULL on failure */

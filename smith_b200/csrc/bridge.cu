@@ -804,6 +804,26 @@ uint64_t smith_launch_count(void* p) {
   return c ? c->launches : 0;
 }
 
+// For callers that must not allocate device memory at the time of the call: code
+// running after its memory budget is fixed (a serving process that hands every
+// byte to its own arena at start-up), inside a region where cudaMalloc would
+// synchronise the device or is forbidden (a latency-critical loop, a host
+// callback), or a host runtime that only owns raw device pointers and no
+// smith context.  Takes raw device pointers and a stream; always runs the
+// tensor-core kernel, with its scratch in a fixed array inside the library.
+int32_t smith_qmatmul_static(uint32_t kind, const void* a_dev, const void* b_dev, void* c_dev, uint64_t M,
+                             uint64_t N, uint64_t K, uint64_t groups, void* stream) {
+  if (kind != 4 && kind != 8) return fail("kind must be 4 or 8, got %u", kind);
+  if (!a_dev || !b_dev || !c_dev) return fail("smith_qmatmul_static: null device pointer");
+  if (M == 0 || N == 0) return 0;
+  const char* why = "";
+  cudaError_t e = launch_qgemm_tc_static((int)kind, (const float*)a_dev, (const uint8_t*)b_dev, (float*)c_dev,
+                                         (int64_t)M, (int64_t)N, (int64_t)K, (int64_t)groups, (cudaStream_t)stream, &why);
+  if (e != cudaSuccess)
+    return fail("smith_qmatmul_static: %s%s%s", why, *why ? " -- " : "", cudaGetErrorString(e));
+  return 0;
+}
+
 // ---------------------------------------------------------------- graphs
 int32_t smith_graph_begin(void* p) {
   Context* c = as_ctx(p);

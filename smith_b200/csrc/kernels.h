@@ -50,6 +50,10 @@ bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                          int64_t K, int64_t groups, cudaStream_t s);
 
+// Same computation with the scratch in a fixed array inside the library image (no allocation).
+cudaError_t launch_qgemm_tc_static(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
+                                   int64_t K, int64_t groups, cudaStream_t s, const char** why);
+
 // util.cu
 // 1 if a bounded device-side wait gave up since the last call (then clears it), 0 if not, -1 on error.
 int kernel_take_status();

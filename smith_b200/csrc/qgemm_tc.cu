@@ -554,4 +554,54 @@ cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C
   return pl.MT == 2 ? launch_main<8, 2>(map, p, pl, s) : launch_main<8, 1>(map, p, pl, s);
 }
 
+// ---------------------------------------------------------------- entry point that allocates nothing
+// Scratch for smith_qmatmul_static: the 16-bit copy of the activations
+// (M * K * 2 bytes, rounded up to 256) followed by one f32 per row.  It is part
+// of the library image, so every GPU that loads the library holds these bytes
+// until the process exits.  In host code the name below is only a stand-in for
+// the symbol; the device address comes from cudaGetSymbolAddress.
+constexpr size_t kStaticScratchBytes = (size_t)8 << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of g_static_scratch per device, looked up once per device with that device current.
+void* g_static_scratch_ptr[64] = {nullptr};
+}  // namespace
+
+cudaError_t launch_qgemm_tc_static(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
+                                   int64_t K, int64_t groups, cudaStream_t s, const char** why) {
+  *why = "";
+  if (!qgemm_tc_supports(kind, M, N, K, groups)) {
+    *why = "shape not taken by the tensor-core kernel (needs N % 8 == 0, K % 32 == 0, groups == K / 32; Q4 needs K >= 1024)";
+    return cudaErrorInvalidValue;
+  }
+  const size_t need = qgemm_tc_workspace_bytes(kind, M, N, K);
+  if (need > kStaticScratchBytes) {
+    *why = "M * K exceeds the built-in scratch (8 MiB: M * K * 2 + 256 + M * 4 bytes must fit)";
+    return cudaErrorInvalidValue;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) {
+    *why = "device index out of range";
+    return cudaErrorInvalidDevice;
+  }
+  if (!g_static_scratch_ptr[dev]) {  // set-up, once per device, with that device current
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      *why = "cudaGetSymbolAddress failed for the built-in scratch";
+      return e != cudaSuccess ? e : cudaErrorUnknown;
+    }
+    g_static_scratch_ptr[dev] = p;
+  }
+  Workspace ws;
+  ws.ptr = g_static_scratch_ptr[dev];
+  ws.bytes = kStaticScratchBytes;
+  // Nothing in the scratch has to start at zero: convert_activations rewrites every element the
+  // main kernel reads (all M * K values and, for Q8, all M row factors) before it is read.
+  return launch_qgemm_tc(kind, A, B, C, M, N, K, groups, ws, s);
+}
+
 }  // namespace smith

@@ -84,6 +84,7 @@ SYMBOLS = {
     "smith_q8_pack": (_i32, [_p, _p, _p, _u64, _u64]),
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
+    "smith_qmatmul_static": (_i32, [_u32, _p, _p, _p, _u64, _u64, _u64, _u64, _p]),
     "smith_kernel_status": (_i32, [_p]),
     "smith_launch_count": (_u64, [_p]),
     "smith_graph_begin": (_i32, [_p]),
@@ -370,6 +371,11 @@ def q8Pack(wBuffer, outBuffer, K, N):
 
 def qmatmul(kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path=PATH_AUTO):
     _check(lib.smith_qmatmul(ctx(), kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path), "qmatmul")
+
+
+def qmatmulStatic(kind, aPtr, bPtr, cPtr, M, N, K, groups, streamPtr=None):
+    """smith_qmatmul_static: raw device pointers, scratch inside the library, allocates nothing."""
+    _check(lib.smith_qmatmul_static(kind, aPtr, bPtr, cPtr, M, N, K, groups, streamPtr), "qmatmul_static")
 
 
 def qmatmulPath(kind, M, N, K):
