@@ -456,7 +456,10 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
     const int64_t nt = (N + bn - 1) / bn;
     const int64_t ctas = nt * mtiles;
     const int64_t waves = (ctas + 147) / 148;
-    const double eff = ((double)N / (double)(nt * bn)) * ((double)ctas / (double)(waves * 148));
+    // useful fraction of the tiles x fill of the last wave x a mild preference for wide MMAs
+    // (narrow tiles re-read the activations more often and amortise the dequantised tile less)
+    const double eff = ((double)N / (double)(nt * bn)) * ((double)ctas / (double)(waves * 148)) *
+                       ((double)bn / (double)(bn + 48));
     if (eff > best + 1e-9) best = eff, bestBN = bn;
   }
   pl.BN = bestBN;

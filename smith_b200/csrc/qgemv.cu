@@ -23,13 +23,21 @@
 //    The only rounding beyond the f32 accumulation over groups is the 15-bit
 //    rounding of the activations (relative to the largest value of its group).
 //  * One CTA owns TN adjacent columns and all of K.  Thread t owns column
-//    t % TN and the group-rows of phase t / TN, so any TN that is a multiple of
-//    8 fills whole warps when the phase count is a multiple of 4.  Packed
+//    t % TN and the group-rows of phase t / TN, so the tile width is free to be
+//    whatever spreads N evenly over the SMs (the last warp may be partly idle).  Packed
 //    group-rows (TN * block_bytes contiguous bytes each) arrive through a ring
 //    of shared-memory stages filled by 1-D bulk async copies from a producer
 //    thread (full/empty mbarriers, no multicast); lanes read adjacent blocks.
 //  * The phases of a column are summed through shared memory in fixed order
 //    and each output is written once.  No atomics, no global scratch.
+//  * Tiles are sized so that two CTAs share an SM (more warps in flight, and
+//    one CTA's start-up and tail overlap the other's stream), and the kernel
+//    is launched with programmatic stream serialisation: it lets its successor
+//    start as CTAs retire (griddepcontrol.launch_dependents at entry), and
+//    itself waits for its predecessor (griddepcontrol.wait) only before it
+//    first reads the activations -- the producer warp streams weights, which no
+//    kernel writes, from the first instruction.  Back-to-back launches (a
+//    decode step's layer stack) thus overlap launch gap, ramp-up and tail.
 //
 // Waits are time-bounded as in pipeline.cuh.
 #include <cuda_fp16.h>
@@ -41,11 +49,14 @@ namespace smith {
 namespace {
 
 constexpr int kMaxRowsM = 4;
-constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage
+constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage (fewer, larger stages
+                                           // measured faster than more, smaller ones)
 constexpr int kMaxStages = 8;
 constexpr int kHeader = 256;               // barriers + abort flag
-constexpr int kSmemBudget = 220 * 1024;
-constexpr int kMaxConsumerThreads = 512;
+constexpr int kSmemBudget = 110 * 1024;    // per CTA: two CTAs share an SM
+constexpr int kSmemBudgetSolo = 220 * 1024;  // long K: the activations' digit form needs the room, one CTA per SM
+constexpr int kMaxConsumerThreads = 448;      // per CTA (two CTAs of 480 threads fit an SM at 64 registers)
+constexpr int kCtasPerSm = 2;
 
 struct Params {
   const float* A;
@@ -187,8 +198,9 @@ __device__ __forceinline__ void block_dot(const uint8_t* __restrict__ blk, uint3
 }
 
 template <int KIND, int MR>
-__global__ void __launch_bounds__(kMaxConsumerThreads + 32, 1) qgemv_kernel(const Params p) {
+__global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_kernel(const Params p) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + kMaxStages;
@@ -245,6 +257,8 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, 1) qgemv_kernel(cons
   }
 
   // -------------------------------------------------------------- consumers
+  // The activations (and the output buffer) may belong to the launch before this one.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // Activations -> digit words (overlaps the first weight copies).
   // (row, group) pairs are laid out as [MR][G], which is also the order of A's 32-element chunks.
   for (int i = tid; i < ((MR * p.G * 8 + 31) & ~31); i += nwarps * 32) {
@@ -322,15 +336,26 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   Params& p = pl.p;
   const int MR = (int)M;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)(K / 32);
-  // Tile width: the smallest multiple of 8 that covers N in a whole number of waves of CTAs.
+  const int xdig_bytes = MR * p.G * 64, xsc_bytes = MR * p.G * 8;
+  // One CTA per SM with a deep ring when the whole matrix fits one wave of 128-column tiles
+  // (nothing follows a CTA on its SM, so depth beats overlap); two per SM when tiles come in
+  // several waves (one CTA's start-up and tail then overlap its neighbour's stream) -- unless the
+  // activations' digit form alone takes most of a half SM.
+  const bool solo = (xdig_bytes + xsc_bytes) > 48 * 1024 || N <= (int64_t)sms * 128;
+  const int slots = solo ? sms : sms * kCtasPerSm;
+  const int budget = solo ? kSmemBudgetSolo : kSmemBudget;
+  // Tile width: the smallest width that covers N in a whole number of waves of resident CTAs.
+  // A tile's group-row span must start and end on 16 bytes: any even width for 24-byte blocks,
+  // a multiple of 8 for 34-byte blocks.
+  const int64_t q = (kind == 4) ? 2 : 8;
   int TN = 0;
   for (int64_t waves = 1;; waves++) {
-    TN = (int)(8 * ((N + 8 * sms * waves - 1) / (8 * sms * waves)));
-    if (TN <= 128) break;
+    TN = (int)(q * ((N + q * slots * waves - 1) / (q * slots * waves)));
+    if (TN <= (solo ? 128 : 112)) break;
   }
   p.TN = TN;
   pl.tiles = (int)((N + TN - 1) / TN);
-  // Phases: a multiple of 4 (so TN * phases fills whole warps), aiming at ~512 consumer threads.
+  // Phases: a multiple of 4 (so TN * phases fills whole warps), aiming at kMaxConsumerThreads.
   int phases = (kMaxConsumerThreads / TN) & ~3;
   if (phases < 4) phases = 4;
   while (phases > 4 && (phases * kRowsPerPhase > p.G * 2)) phases -= 4;  // short K: do not over-split
@@ -339,16 +364,15 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   p.row_pitch = TN * BB;
   p.stage_rows = phases * kRowsPerPhase;
   p.stage_bytes = ((p.stage_rows * p.row_pitch + 15) / 16) * 16;
-  const int xdig_bytes = MR * p.G * 64, xsc_bytes = MR * p.G * 8;
   p.xdig_off = kHeader;
   p.xsc_off = p.xdig_off + xdig_bytes;
   p.ring_off = ((p.xsc_off + xsc_bytes + 1023) / 1024) * 1024;
-  const int room = kSmemBudget - p.ring_off - 64;
+  const int room = budget - p.ring_off - 64;
   int stages = room / p.stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   p.stages = stages;
   const size_t red = (size_t)phases * MR * TN * 4;
-  const size_t ring = (size_t)stages * p.stage_bytes + 64;
+  const size_t ring = (size_t)(stages > 0 ? stages : 0) * p.stage_bytes + 64;
   pl.smem = p.ring_off + (ring > red ? ring : red);
   pl.ok = stages >= 2 && p.nthreads <= kMaxConsumerThreads && pl.smem <= 227 * 1024;
   return pl;
@@ -364,9 +388,19 @@ cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
     configured = true;
   }
   const int threads = ((pl.p.nthreads + 31) / 32) * 32 + 32;
-  qgemv_kernel<KIND, MR><<<pl.tiles, threads, pl.smem, s>>>(pl.p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl.tiles);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR>, pl.p);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace
