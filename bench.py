@@ -247,14 +247,22 @@ def main():
     D.releaseBuffer(wtmp)
     a_dev = D.alloc(M * K * 4, D.PRIVATE)
     D.fillNormal(a_dev, M * K, 7, 1.0)            # same seed on every rank: replicated activations
-    gather = P.OutputGather(M, N, world, rank) if world > 1 else None
-    c_dev = gather.local_buf if gather else D.alloc(M * Nl * 4, D.PRIVATE)
+    # N > 1: the GEMV kernel gathers its own output over peer memory (M <= 4); wider M uses NCCL
+    gather, fused = None, False
+    if world > 1:
+        fused = M <= 4 and all(D.qgemvTiles(kind, M, b - a, K) > 0
+                               for a, b in (P.column_shard(N, world, r) for r in range(world)))
+        gather = P.FusedGather(M, N, world, rank) if fused else P.OutputGather(M, N, world, rank)
+    c_dev = D.alloc(M * Nl * 4, D.PRIVATE) if (not gather or fused) else gather.local_buf
 
     def one_pass():
         for pk in packs:
-            D.qmatmul(kind, a_dev, pk, c_dev, M, Nl, K, G, D.PATH_AUTO)
-            if gather:
-                gather.enqueue()
+            if fused:
+                gather.enqueue(kind, a_dev, pk, K)
+            else:
+                D.qmatmul(kind, a_dev, pk, c_dev, M, Nl, K, G, D.PATH_AUTO)
+                if gather:
+                    gather.enqueue()
 
     one_pass()                                    # sizes scratch before capture
     D.synchronize()
@@ -355,7 +363,9 @@ def main():
             "data": "synthetic",
             "config": {"workload": args.workload, "kind": f"q{kind}", "M": M, "K": K, "N": N,
                        "launches_per_step": R, "kernel": path,
-                       "sharding": f"N-sharded over {world} GPU(s), all-gather of outputs" if world > 1 else "single GPU",
+                       "sharding": (f"N-sharded over {world} GPU(s), all-gather of outputs "
+                                    + ("fused into the GEMV kernel (peer stores over NVLink)" if fused else "by NCCL"))
+                       if world > 1 else "single GPU",
                        "l2": f"defeated by rotating over {R} distinct packed matrices per step "
                              f"({R * wbytes_full / 1e6:.0f} MB > 4 x 126 MB L2)",
                        "timing": "CUDA events on the launch stream around a replayed CUDA graph, max over ranks"},

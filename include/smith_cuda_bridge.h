@@ -176,6 +176,27 @@ int32_t smith_kernel_status(void* ctx);
 /* How many kernels this context has launched so far. */
 uint64_t smith_launch_count(void* ctx);
 
+/* Multi-GPU, one process per GPU (no counterpart in the reference, which is single-device).
+ * smith_ipc_export writes a 64-byte handle for a PRIVATE buffer; another process on
+ * the same box turns it into a buffer over the same device memory with smith_ipc_import
+ * (reads and writes then travel over NVLink).  Releasing the imported buffer unmaps it. */
+int32_t smith_ipc_export(void* buffer, void* handle_out64);
+void* smith_ipc_import(void* ctx, const void* handle64, uint64_t bytes);
+/* Fused GEMV + all-gather for weights sharded along N (M <= 4).  This rank multiplies its
+ * column shard b (n_local columns starting at column n0 of a row of n_total) and stores the
+ * result slice into EVERY rank's gathered output through y_bufs[r] (rank r's buffer of
+ * 2*M*n_total floats, local or IPC-imported), then adds its tile arrivals to every rank's
+ * state_bufs[r] (16 bytes, zero-initialised once).  The launch completes when this rank's
+ * own row has received the tiles of all ranks: `target` = sum over ranks of
+ * smith_qgemv_tiles(kind, M, n_local_r, K).  The two halves of y are used alternately:
+ * the k-th call (k = 0, 1, ...) on a state leaves its row in half k % 2.  The wait is
+ * bounded (~0.2 s); if a peer never arrives, smith_kernel_status reports it.
+ * Every rank must make the same sequence of calls.  Asynchronous; may be captured in a graph. */
+int32_t smith_qmatmul_allgather(void* ctx, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total,
+                                uint64_t n0, uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world,
+                                uint32_t rank, void* const* y_bufs, void* const* state_bufs, uint32_t target);
+int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
+
 /* No counterpart in the reference.  The same product as smith_qmatmul, for
  * callers that cannot allocate device memory when they make the call: a
  * serving process whose memory was all handed to its own arena at start-up, a

@@ -80,6 +80,7 @@ struct Buffer {
   bool owns_dev = false;
   bool wrapped = false;
   bool resident = false;
+  bool ipc_mapped = false;  // dev is another process's allocation opened through an IPC handle
   std::atomic<int64_t> refs{1};
 };
 
@@ -461,6 +462,7 @@ void smith_release_buffer(void* p) {
     cudaFree(b->dev);
     freed += b->bytes;
   }
+  if (b->dev && b->ipc_mapped) cudaIpcCloseMemHandle(b->dev);
   if (c && c->magic == kCtxMagic) c->held -= freed;
   b->magic = 0;
   delete b;
@@ -822,6 +824,81 @@ int32_t smith_qmatmul_static(uint32_t kind, const void* a_dev, const void* b_dev
   if (e != cudaSuccess)
     return fail("smith_qmatmul_static: %s%s%s", why, *why ? " -- " : "", cudaGetErrorString(e));
   return 0;
+}
+
+// ---------------------------------------------------------------- multi-GPU: peer memory and the fused all-gather
+int32_t smith_ipc_export(void* buffer, void* handle_out) {
+  Buffer* b = as_buf(buffer);
+  if (!b || !handle_out) return fail("smith_ipc_export: bad arguments");
+  if (!b->dev || !b->owns_dev) return fail("smith_ipc_export needs a buffer whose device memory this library allocated");
+  Context* c = as_ctx(b->ctx);
+  if (!c) return 1;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  CU_TRY(cudaIpcGetMemHandle(&h, b->dev));
+  memcpy(handle_out, &h, sizeof h);
+  return 0;
+}
+
+void* smith_ipc_import(void* p, const void* handle, uint64_t bytes) {
+  Context* c = as_ctx(p);
+  if (!c || !handle) {
+    fail("smith_ipc_import: bad arguments");
+    return nullptr;
+  }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  void* dev = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&dev, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    fail("cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return nullptr;
+  }
+  Buffer* b = new Buffer();
+  b->ctx = c;
+  b->bytes = bytes;
+  b->mode = SMITH_PRIVATE;
+  b->dev = dev;
+  b->wrapped = true;
+  b->ipc_mapped = true;
+  return b;
+}
+
+int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
+  return qgemv_tiles((int)kind, (int64_t)M, (int64_t)N, (int64_t)K);
+}
+
+int32_t smith_qmatmul_allgather(void* p, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total, uint64_t n0,
+                                uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world, uint32_t rank,
+                                void* const* y_bufs, void* const* state_bufs, uint32_t target) {
+  Context* c = as_ctx(p);
+  Buffer *ba = as_buf(a), *bb = as_buf(b);
+  if (!c || !ba || !bb) return 1;
+  if (kind != 4 && kind != 8) return fail("kind must be 4 or 8, got %u", kind);
+  if (world < 1 || world > 8 || rank >= world) return fail("smith_qmatmul_allgather: world %u / rank %u out of range", world, rank);
+  if (!y_bufs || !state_bufs) return fail("smith_qmatmul_allgather: null buffer lists");
+  if (n0 + n_local > n_total) return fail("smith_qmatmul_allgather: slice [%llu, %llu) outside a row of %llu",
+                                          (unsigned long long)n0, (unsigned long long)(n0 + n_local),
+                                          (unsigned long long)n_total);
+  if (!ba->dev || !bb->dev) return fail("smith_qmatmul_allgather needs buffers with a device side");
+  const uint64_t blk = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  if (ba->bytes < M * K * 4 || bb->bytes < groups * n_local * blk) return fail("smith_qmatmul_allgather: input buffer too small");
+  if (!qgemv_supports((int)kind, M, n_local, K, groups))
+    return fail("fused all-gather is built into the GEMV kernel only (M <= 4, N %% 8 == 0, K %% 32 == 0); M=%llu N=%llu K=%llu",
+                (unsigned long long)M, (unsigned long long)n_local, (unsigned long long)K);
+  GemvGather g{};
+  g.world = (int)world, g.rank = (int)rank, g.n0 = (int64_t)n0, g.n_total = (int64_t)n_total, g.target = target;
+  for (uint32_t r = 0; r < world; r++) {
+    Buffer *by = as_buf(y_bufs[r]), *bs = as_buf(state_bufs[r]);
+    if (!by || !bs || !by->dev || !bs->dev) return fail("smith_qmatmul_allgather: rank %u buffers have no device side", r);
+    if (by->bytes < 2 * M * n_total * 4 || bs->bytes < 16) return fail("smith_qmatmul_allgather: rank %u buffers too small", r);
+    g.y[r] = (float*)by->dev;
+    g.state[r] = (unsigned*)bs->dev;
+  }
+  cudaError_t e = launch_qgemv_gather((int)kind, (const float*)ba->dev, (const uint8_t*)bb->dev, nullptr, M, n_local, K,
+                                      groups, &g, c->stream);
+  return e == cudaSuccess ? 0 : fail("fused GEMV + all-gather launch failed: %s", cudaGetErrorString(e));
 }
 
 // ---------------------------------------------------------------- graphs

@@ -49,6 +49,19 @@ cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C
 bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                          int64_t K, int64_t groups, cudaStream_t s);
+// Same launch ending in a fused all-gather: the N columns computed here are this rank's slice
+// [n0, n0 + N) of a row of n_total columns, stored into every rank's gathered buffers.
+struct GemvGather {
+  float* y[8];          // per rank: gathered output, two buffers [2][M][n_total]
+  unsigned* state[8];   // per rank: control words {step, ticket, arrivals[0], arrivals[1]}
+  int world, rank;
+  int64_t n0, n_total;
+  unsigned target;      // CTAs (tiles) arriving per step, summed over ranks
+};
+cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
+                                int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s);
+// Grid size the GEMV uses for a shape (-1 if it does not take it).
+int qgemv_tiles(int kind, int64_t M, int64_t N, int64_t K);
 
 // Same computation with the scratch in a fixed array inside the library image (no allocation).
 cudaError_t launch_qgemm_tc_static(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,

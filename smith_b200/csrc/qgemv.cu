@@ -39,6 +39,17 @@
 //    kernel writes, from the first instruction.  Back-to-back launches (a
 //    decode step's layer stack) thus overlap launch gap, ramp-up and tail.
 //
+//  * Multi-GPU (weights sharded along N): the same kernel can end in a fused
+//    all-gather.  Instead of writing its columns to a local C, each CTA stores
+//    them into every rank's gathered row through peer-mapped pointers (plain
+//    stores over NVLink), fences, and adds one arrival to every rank's counter.
+//    The last CTA of the grid to finish then waits -- bounded -- until its own
+//    counter shows the tiles of all ranks, so the launch completes only when
+//    this rank's gathered row is whole.  Two output buffers and two counters
+//    are used alternately (a rank can run at most one step ahead of another,
+//    because its step cannot complete without the other's arrivals), and the
+//    step number lives in device memory so that a captured graph can be replayed.
+//
 // Waits are time-bounded as in pipeline.cuh.
 #include <cuda_fp16.h>
 
@@ -49,6 +60,7 @@ namespace smith {
 namespace {
 
 constexpr int kMaxRowsM = 4;
+constexpr int kMaxPeers = 8;
 constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage (fewer, larger stages
                                            // measured faster than more, smaller ones)
 constexpr int kMaxStages = 8;
@@ -67,6 +79,13 @@ struct Params {
   int row_pitch, stage_rows, stage_bytes, stages;
   int xdig_off, xsc_off, ring_off;  // byte offsets in dynamic shared memory
   int* status;
+  // Fused all-gather of the output slice over peer memory (world == 0: plain store to C).
+  // y[r]: rank r's gathered output, two buffers [2][M][n_total] used alternately;
+  // state[r]: rank r's four control words {step, finished-CTA ticket, arrivals[0], arrivals[1]}.
+  float* y[kMaxPeers];
+  unsigned* state[kMaxPeers];
+  int world, rank, n0, n_total;
+  unsigned target;  // tiles that arrive per step, summed over all ranks
 };
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) {
@@ -259,6 +278,8 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   // -------------------------------------------------------------- consumers
   // The activations (and the output buffer) may belong to the launch before this one.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  unsigned step = 0;
+  if (p.world > 0) step = *reinterpret_cast<volatile unsigned*>(p.state[p.rank]);  // advanced by the previous launch
   // Activations -> digit words (overlaps the first weight copies).
   // (row, group) pairs are laid out as [MR][G], which is also the order of A's 32-element chunks.
   for (int i = tid; i < ((MR * p.G * 8 + 31) & ~31); i += nwarps * 32) {
@@ -314,11 +335,48 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   }
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
   if (*abort_flag) return;
+  if (p.world == 0) {
+    for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+      const int m = i / tn, c = i - m * tn;
+      float sum = 0.f;
+      for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
+      p.C[(size_t)m * p.N + col0 + c] = sum;
+    }
+    return;
+  }
+  // ---------------------------------------------- fused all-gather over peer memory
+  const unsigned par = step & 1u;
   for (int i = tid; i < p.M * tn; i += nwarps * 32) {
     const int m = i / tn, c = i - m * tn;
     float sum = 0.f;
     for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
-    p.C[(size_t)m * p.N + col0 + c] = sum;
+    const size_t at = ((size_t)par * p.M + m) * p.n_total + p.n0 + col0 + c;
+    for (int r = 0; r < p.world; r++) p.y[r][at] = sum;
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every store of this CTA is issued
+  if (tid == 0) {
+    __threadfence_system();                             // ... and ordered before the arrivals
+    for (int r = 0; r < p.world; r++) atomicAdd_system(p.state[r] + 2 + par, 1u);
+    unsigned* mine = p.state[p.rank];
+    const unsigned ticket = atomicAdd(mine + 1, 1u);
+    if (ticket == gridDim.x - 1) {                      // last CTA of this rank's grid
+      const unsigned expected = (step / 2u + 1u) * p.target;
+      const long long t0 = clock64();
+      bool whole = false;
+      for (unsigned spin = 0;; spin++) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + 2 + par) : "memory");
+        if (seen >= expected) {
+          whole = true;
+          break;
+        }
+        if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) break;
+      }
+      if (!whole) atomicExch(p.status, 1);              // a peer never arrived: the row is not valid
+      mine[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned*>(mine) = step + 1u;
+    }
   }
 }
 
@@ -405,6 +463,11 @@ cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
 
 }  // namespace
 
+int qgemv_tiles(int kind, int64_t M, int64_t N, int64_t K) {
+  const Plan pl = make_plan(kind, M, N, K);
+  return pl.ok ? pl.tiles : -1;
+}
+
 bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups) {
   if (kind != 4 && kind != 8) return false;
   if (M < 1 || M > kMaxRowsM) return false;
@@ -416,6 +479,11 @@ bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups) {
 
 cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
                          int64_t groups, cudaStream_t s) {
+  return launch_qgemv_gather(kind, A, B, C, M, N, K, groups, nullptr, s);
+}
+
+cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
+                                int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s) {
   (void)groups;
   if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15)) return cudaErrorMisalignedAddress;
   Plan pl = make_plan(kind, M, N, K);
@@ -423,6 +491,17 @@ cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, i
   pl.p.A = A, pl.p.B = B, pl.p.C = C;
   pl.p.status = kernel_status_ptr();
   if (!pl.p.status) return cudaErrorUnknown;
+  pl.p.world = 0;
+  if (g) {
+    if (g->world < 1 || g->world > kMaxPeers || g->rank < 0 || g->rank >= g->world) return cudaErrorInvalidValue;
+    pl.p.world = g->world, pl.p.rank = g->rank, pl.p.n0 = (int)g->n0, pl.p.n_total = (int)g->n_total;
+    pl.p.target = g->target;
+    for (int r = 0; r < g->world; r++) {
+      pl.p.y[r] = g->y[r];
+      pl.p.state[r] = g->state[r];
+      if (!pl.p.y[r] || !pl.p.state[r]) return cudaErrorInvalidValue;
+    }
+  }
 #define SMITH_GEMV_CASE(KD, MRV) \
   if (kind == KD && M == MRV) return launch_one<KD, MRV>(pl, s);
   SMITH_GEMV_CASE(4, 1) SMITH_GEMV_CASE(4, 2) SMITH_GEMV_CASE(4, 3) SMITH_GEMV_CASE(4, 4)

@@ -85,6 +85,11 @@ SYMBOLS = {
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_qmatmul_static": (_i32, [_u32, _p, _p, _p, _u64, _u64, _u64, _u64, _p]),
+    "smith_ipc_export": (_i32, [_p, _p]),
+    "smith_ipc_import": (_p, [_p, _p, _u64]),
+    "smith_qmatmul_allgather": (_i32, [_p, _u32, _p, _p, _u64, _u64, _u64, _u64, _u64, _u64, _u32, _u32,
+                                        C.POINTER(_p), C.POINTER(_p), _u32]),
+    "smith_qgemv_tiles": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_kernel_status": (_i32, [_p]),
     "smith_launch_count": (_u64, [_p]),
     "smith_graph_begin": (_i32, [_p]),
@@ -380,6 +385,32 @@ def qmatmulStatic(kind, aPtr, bPtr, cPtr, M, N, K, groups, streamPtr=None):
 
 def qmatmulPath(kind, M, N, K):
     return int(lib.smith_qmatmul_path(kind, M, N, K))
+
+
+def ipcExport(buffer):
+    """64-byte handle another process on this box can import."""
+    out = C.create_string_buffer(64)
+    _check(lib.smith_ipc_export(buffer, out), "ipc_export")
+    return out.raw
+
+
+def ipcImport(handle, nbytes):
+    buf = lib.smith_ipc_import(ctx(), handle, int(nbytes))
+    if not buf:
+        _raise("ipc_import")
+    return buf
+
+
+def qgemvTiles(kind, M, N, K):
+    return int(lib.smith_qgemv_tiles(kind, M, N, K))
+
+
+def qmatmulAllGather(kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank, yBuffers, stateBuffers,
+                     target):
+    ys = (_p * world)(*yBuffers)
+    ss = (_p * world)(*stateBuffers)
+    _check(lib.smith_qmatmul_allgather(ctx(), kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank,
+                                       ys, ss, target), "qmatmul_allgather")
 
 
 def kernelStatus():

@@ -96,6 +96,76 @@ class OutputGather:
         return self.full
 
 
+class FusedGather:
+    """Output row gathered by the GEMV kernel itself (M <= 4): every rank's kernel stores its
+    column slice into every rank's row through peer-mapped memory and the launch completes
+    when the local row is whole.  No NCCL call on the data path; capturable in a CUDA graph.
+
+    Owns this rank's row buffer (two halves used alternately) and its 16-byte control block,
+    and holds IPC mappings of the other ranks' buffers."""
+    capturable = True
+    kernels_per_call = 0    # the gather is part of the matmul launch
+
+    def __init__(self, M, N, world, rank, group=None):
+        from . import device as D
+        self.M, self.N, self.world, self.rank = M, N, world, rank
+        self.spans = [column_shard(N, world, r) for r in range(world)]
+        self.y = D.alloc(2 * M * N * 4, D.PRIVATE)
+        self.state = D.alloc(256, D.PRIVATE)
+        D.upload(self.state, np.zeros(64, np.uint32))
+        D.upload(self.y, np.zeros(2 * M * N, np.float32))
+        self.ys, self.states = [None] * world, [None] * world
+        self.ys[rank], self.states[rank] = self.y, self.state
+        if world > 1:
+            import torch.distributed as dist
+            mine = (D.ipcExport(self.y), D.ipcExport(self.state))
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+            for r in range(world):
+                if r != rank:
+                    self.ys[r] = D.ipcImport(handles[r][0], 2 * M * N * 4)
+                    self.states[r] = D.ipcImport(handles[r][1], 256)
+            dist.barrier(group=group)     # everyone has mapped everyone before the first store
+        self.calls = 0
+        self._targets = {}
+
+    def target(self, kind, K):
+        from . import device as D
+        key = (kind, K)
+        if key not in self._targets:
+            tiles = [D.qgemvTiles(kind, self.M, b - a, K) for a, b in self.spans]
+            if min(tiles) < 0:
+                raise D.SmithError("smith: the GEMV kernel does not take this shard shape")
+            self._targets[key] = sum(tiles)
+        return self._targets[key]
+
+    def enqueue(self, kind, a_buf, packed_shard_buf, K):
+        """Asynchronous fused matmul + all-gather; returns which half of the row buffer it fills."""
+        from . import device as D
+        n0, n1 = self.spans[self.rank]
+        D.qmatmulAllGather(kind, a_buf, packed_shard_buf, self.M, self.N, n0, n1 - n0, K, K // 32, self.world,
+                           self.rank, self.ys, self.states, self.target(kind, K))
+        half = self.calls & 1
+        self.calls += 1
+        return half
+
+    def read(self, half):
+        """The gathered rows [M, N] of one half (after a synchronize)."""
+        from . import device as D
+        n = self.M * self.N
+        return D.download(self.y, n * 4, np.float32, offset=half * n * 4).reshape(self.M, self.N)
+
+    def close(self):
+        from . import device as D
+        for r in range(self.world):
+            if r != self.rank and self.ys[r]:
+                D.releaseBuffer(self.ys[r])
+                D.releaseBuffer(self.states[r])
+        D.releaseBuffer(self.y)
+        D.releaseBuffer(self.state)
+        self.ys = self.states = []
+
+
 class ShardedMatmul:
     """y = a @ dequant(W) with W N-sharded over the process group: the multi-GPU
     counterpart of matmulQ4 / matmulQ8 for one weight matrix."""
@@ -107,12 +177,17 @@ class ShardedMatmul:
         self.packed = packed_shard_buffer
         n0, n1 = column_shard(N, world, rank)
         self.Nl = n1 - n0
-        self.gather = OutputGather(M, N, world, rank)
+        self.fused = M <= 4 and all(D.qgemvTiles(kind, M, b - a, K) > 0
+                                    for a, b in (column_shard(N, world, r) for r in range(world)))
+        self.gather = FusedGather(M, N, world, rank) if self.fused else OutputGather(M, N, world, rank)
         self.a_dev = D.alloc(M * K * 4, D.PRIVATE)
 
     def enqueue(self, a_dev=None):
-        """Asynchronous: matmul on this rank's shard, then the all-gather."""
+        """Asynchronous: matmul on this rank's shard and the all-gather (fused into the kernel for
+        M <= 4, NCCL otherwise).  Returns the half index (fused) or the gathered torch tensor."""
         from . import device as D
+        if self.fused:
+            return self.gather.enqueue(self.kind, a_dev or self.a_dev, self.packed, self.K)
         D.qmatmul(self.kind, a_dev or self.a_dev, self.packed, self.gather.local_buf, self.M, self.Nl, self.K,
                   self.K // 32, D.PATH_AUTO)
         return self.gather.enqueue()
@@ -121,6 +196,8 @@ class ShardedMatmul:
         """End to end from host memory: upload activations, compute, gather, download the full rows."""
         from . import device as D
         D.upload(self.a_dev, np.ascontiguousarray(a_host, dtype=np.float32))
-        full = self.enqueue()
+        out = self.enqueue()
         D.synchronize()
-        return full.cpu().numpy()
+        if self.fused:
+            return self.gather.read(out)
+        return out.cpu().numpy()

@@ -307,3 +307,60 @@ def test_async_submit_and_graph_replay():
     device.dispatch(enc, N, M, 1, 16, 1, 1)
     device.wait(device.endAsync(enc))
     assert np.array_equal(cb.get(np.float32), first)
+
+
+# ------------------------------------------------------------------ fused all-gather epilogue (one GPU)
+def test_fused_gather_world_of_one_and_alternating_halves():
+    from smith_b200.parallel import FusedGather
+    K, N, M = 2048, 1024, 2
+    rng = np.random.default_rng(21)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    packed = O.quantize_q4(w)
+    pb = DevBuf.of(packed)
+    fg = FusedGather(M, N, 1, 0)
+    for call in range(3):                                   # halves 0, 1, 0: the counters keep counting
+        a = rng.standard_normal((M, K)).astype(np.float32)
+        ab = DevBuf.of(a)
+        half = fg.enqueue(4, ab.handle, pb.handle, K)
+        device.synchronize()
+        assert half == call % 2 and device.kernelStatus() == 0
+        want = matmul_on_device(a, packed, K, N, "q4", device.PATH_GEMV)
+        assert bits_equal(fg.read(half), want)
+        ab.free()
+    fg.close()
+    pb.free()
+
+
+def test_fused_gather_two_shards_emulated_on_one_gpu():
+    # Two ranks' launches run one after the other on this GPU, each storing its column slice into
+    # both ranks' rows.  The first launch is told to expect only its own tiles (its peer has not run
+    # yet and two kernels that wait on each other must never share a GPU); the second expects both.
+    K, N, M, world = 1024, 512, 3, 2
+    rng = np.random.default_rng(22)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    packed = O.quantize_q8(w)
+    from smith_b200 import parallel as P
+    ys = [DevBuf.of(np.zeros(2 * M * N, np.float32)) for _ in range(world)]
+    states = [DevBuf.of(np.zeros(64, np.uint32)) for _ in range(world)]
+    ab = DevBuf.of(a)
+    tiles = []
+    for r in range(world):
+        n0, n1 = P.column_shard(N, world, r)
+        tiles.append(device.qgemvTiles(8, M, n1 - n0, K))
+        shard = DevBuf.of(P.slice_packed_columns(packed, K // 32, N, 34, n0, n1))
+        device.qmatmulAllGather(8, ab.handle, shard.handle, M, N, n0, n1 - n0, K, K // 32, world, r,
+                                [y.handle for y in ys], [s.handle for s in states], sum(tiles))
+        device.synchronize()
+        assert device.kernelStatus() == 0
+        shard.free()
+    want = matmul_on_device(a, packed, K, N, "q8", device.PATH_GENERIC)
+    for r in range(world):
+        got = ys[r].get(np.float32)[:M * N].reshape(M, N)
+        ok, worst = within_tolerance(got, want, a, packed, K, N, "q8", REL)
+        assert ok, (r, worst)
+        st = states[r].get(np.uint32)[:4]
+        assert st[2] == sum(tiles) and st[3] == 0 and st[1] == 0      # all arrivals counted, ticket reset
+    assert states[0].get(np.uint32)[0] == 1 and states[1].get(np.uint32)[0] == 1  # each rank advanced one step
+    for b in ys + states + [ab]:
+        b.free()
