@@ -34,10 +34,11 @@ cudaError_t launch_pack_q8(const float* w, uint8_t* out, int64_t K, int64_t N, c
 cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                                    int64_t N, int64_t K, int64_t groups, cudaStream_t s);
 
-// qdecode.cu : M <= 16, streams packed rows through shared memory, f32 accumulate.
+// qdecode.cu : M <= 16, activations as int8 digit pairs in scratch, integer mma.sync against the codes.
 bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
+size_t qdecode_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
-                           int64_t N, int64_t K, int64_t groups, cudaStream_t s);
+                           int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
 
 // qgemm_tc.cu : M > 16, dequantise to bf16 tiles in shared memory, tcgen05 MMA, TMEM accumulators.
 bool qgemm_tc_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);

@@ -1,42 +1,37 @@
-// qdecode.cu -- decode-shaped quantized matmul, M <= 16 rows of activations.
+// qdecode.cu -- decode-shaped quantized matmul, M <= 16 rows of activations,
+// on the integer tensor-core path (mma.sync m16n8k32, s8 x s8 -> s32).
 //
 // C[M,N] = A[M,K] (f32) x dequant(B); B in Smith's Q4 (24-byte) or Q8 (34-byte)
 // block layout, block (g, col) at (g*N + col) * block_bytes
 // (shaders/matmul_q4.metal:47-55, shaders/matmul_q8.metal:40-48).
 //
-// The work is bound by reading the packed weights from HBM exactly once, so
-// the kernel is organised around that stream:
+// Like the GEMV kernel this is bound by streaming the packed weights once, and
+// like it the activations are first turned into block fixed point: per group of
+// 32, a power-of-two scale that moves the largest magnitude under 2^14, an
+// integer x_int, and two int8 digits (x_int = hi * 128 + lo).  Here that is
+// done once per launch by a small kernel (quantise_rows) into scratch memory,
+// laid out [group][row][64 bytes] so that the digits of a pipeline stage are
+// one contiguous span that is bulk-copied next to the stage's weights.
 //
-//  * One CTA owns a tile of TN adjacent output columns and the whole K range.
-//    For one group g the TN blocks of the tile are contiguous in memory
-//    (TN * block_bytes, a multiple of 16 bytes because TN % 8 == 0), so a
-//    single thread moves them with one 1-D bulk async copy
-//    (cp.async.bulk.shared::cluster.global, no multicast) per group-row into
-//    a ring of shared-memory stages guarded by full/empty mbarriers.  One
-//    stage holds kWarps group-rows; up to kMaxStages stages are in flight.
-//  * kWarps consumer warps each take one group-row of a stage and sweep the
-//    tile's columns eight at a time with warp-level mma.sync m16n8k16.  The
-//    B fragment is built in registers straight from the packed codes
-//    (exact small integers in bf16 / f16, via an exponent-bias trick), the A
-//    fragment is the activations split into a high and a low 16-bit part
-//    (bf16 for Q4; f16 of the row-prescaled activation for Q8) so that
-//    activations keep ~16-17 bits of mantissa, and accumulation is f32.
-//    With M <= 8 the high parts sit in MMA rows 0-7 and the low parts in rows
-//    8-15 of the same instruction; with 8 < M <= 16 two instructions are used.
-//  * The per-group scale (and Q4 zero point) is applied to the group's f32
-//    partial sum in registers:
-//        Q4: acc += scale * (sum_k x_k (128 + q_k)  -  (128 + zero) * sum_k x_k)
-//        Q8: acc += scale * sum_k x_k q_k
-//    (128 is the exponent bias that makes 0x4300 | q a valid bf16 number).
-//  * Each consumer warp covers a different subset of the groups; the kWarps
-//    partial tiles are summed through shared memory at the end and written
-//    once.  No atomics, no scratch in global memory; summation order is fixed,
-//    so results are reproducible run to run.
-//
-// Every mbarrier wait is bounded by wall-clock time; a wait that gives up
-// raises a flag in shared and global memory, the CTA stops consuming, and the
-// host reads the flag (qdecode_take_status).  The result is then invalid.
-#include <cuda_bf16.h>
+// Main kernel: one CTA owns TN = 8 * NS adjacent columns and all of K.  A
+// consumer warp owns one 8-column slice and one K-phase (warp = phase * NS +
+// slice), keeps that slice's f32 accumulators in registers for the whole
+// launch, and walks the group-rows of its phase.  Per 32-weight group and slice:
+//   * B fragment: lane (n = lane/4, j = lane%4) reads the j-th 8 codes of
+//     column n's block; Q4 nibbles become bytes with two masks (even codes,
+//     odd codes), Q8 codes are bytes already.  No arithmetic on the codes.
+//   * A fragment: one 16-byte load of the digit words {hi, lo} x {first four,
+//     second four} codes in the same order.  With M <= 8 the MMA's rows 0-7
+//     carry the high digits and rows 8-15 the low digits of the same
+//     activation rows (one MMA per group); with 8 < M <= 16 two MMAs.
+//   * The s32 results are exact; dot = 128 * hi + lo is converted to f32 once
+//     and scaled:  acc += (scale * 2^-e) * (dot - zero * sum_k x_int)  (Q4),
+//     acc += (scale * 2^-e) * dot  (Q8).
+// Phases are summed through shared memory in fixed order; every output is
+// written once.  Producer warp, bulk-async ring, full/empty mbarriers and
+// bounded waits as in the GEMV kernel; both kernels are launched with
+// programmatic stream serialisation, and the producer streams weights before
+// it waits for the digits of quantise_rows.
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -45,336 +40,247 @@
 namespace smith {
 namespace {
 
-constexpr int kWarps = 16;                       // consumer warps = group-rows per stage
-constexpr int kThreads = (kWarps + 1) * 32;      // + one producer warp
-constexpr int kMaxSlices = 16;                   // TN <= 128 columns
-constexpr int kMaxStages = 6;
-constexpr int kRingBudget = 196 * 1024;          // bytes of shared memory for the ring
-constexpr int kHeaderBytes = 1024;               // barriers + per-row scales
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 200 * 1024;
+constexpr int kMaxConsumerWarps = 16;
+constexpr int kStageRows = 16;         // group-rows per pipeline stage (rounded up to a multiple of the phases)
 
 struct Params {
-  const float* A;
   const uint8_t* B;
+  const uint8_t* xdig;     // [G][M][64] digit words
+  const float2* xsc;       // [G][M] {2^-e, float(sum_k x_int)}
   float* C;
   int M, N, K, G;
-  int TN;          // columns per CTA (multiple of 8)
-  int row_pitch;   // bytes between group-rows inside a stage
-  int stages;      // ring depth
-  int stage_bytes;
-  int* status;     // device-wide "a wait gave up" word
+  int NS, phases;          // slices per CTA (TN = 8 * NS), K-phases; consumer warps = NS * phases
+  int row_pitch, stage_rows, w_bytes, d_bytes, s_bytes, stage_bytes, stages;
+  int* status;
 };
 
-// Plain shared-memory loads: the compiler may schedule them freely among
-// themselves, but not above the barrier wait (whose asm clobbers memory).
-__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
-__device__ __forceinline__ uint32_t lds16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
-__device__ __forceinline__ float2 lds_f2(const uint8_t* p) { return *reinterpret_cast<const float2*>(p); }
-
-// {upper 16 bits = cvt(hi_slot), lower 16 bits = cvt(lo_slot)}
-__device__ __forceinline__ uint32_t pack_bf16(float lo_slot, float hi_slot) {
-  uint32_t d;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi_slot), "f"(lo_slot));
-  return d;
-}
-__device__ __forceinline__ uint32_t pack_f16(float lo_slot, float hi_slot) {
-  uint32_t d;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi_slot), "f"(lo_slot));
-  return d;
+__device__ __forceinline__ void imma(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// ---------------------------------------------------------------- activations -> digits (global scratch)
+// Eight threads per (group, row), four consecutive k each.  Digit layout of a (group, row): 16 words.
+//   Q4: word j*4 + {0,1,2,3} = {even-k hi, even-k lo, odd-k hi, odd-k lo} of k = 8j .. 8j+7
+//       (byte b of an even word is k = 8j + 2b) -- the order in which two masks pull the codes out of a word.
+//   Q8: word j*4 + {0,1,2,3} = {hi, lo of k = 8j .. 8j+3, hi, lo of k = 8j+4 .. 8j+7}.
 template <int KIND>
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__global__ void __launch_bounds__(256) quantise_rows(const float* __restrict__ A, uint8_t* __restrict__ xdig,
+                                                     float2* __restrict__ xsc, int M, int K, int G) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // A may be the output of the launch before
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane8 = t & 7;
+  int pair = t >> 3;                       // (row, group), row-major like A's 32-element chunks
+  const bool live = pair < M * G;
+  if (!live) pair = M * G - 1;             // keep whole warps in the shuffles
+  const int m = pair / G, g = pair - m * G;
+  const float4 v4 = __ldg(reinterpret_cast<const float4*>(A + (size_t)m * K + (size_t)g * 32) + lane8);
+  const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  int bad = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) bad |= !(fabsf(v[i]) <= 3.4028234e38f);
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+  }
+  const int ex = (int)(__float_as_uint(amax) >> 23) & 0xFF;
+  int e = (ex == 0) ? 0 : (13 - (ex - 127));
+  e = max(-126, min(126, e));
+  const float up = __uint_as_float((unsigned)(127 + e) << 23);
+  float down = __uint_as_float((unsigned)(127 - e) << 23);
+  if (bad) down = __int_as_float(0x7FC00000);  // inf / NaN activations reach every output of the row
+  int q[4], sum = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    q[i] = max(-16383, min(16383, __float2int_rn(v[i] * up)));
+    sum += q[i];
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (!live) return;
+  uint8_t* d = xdig + ((size_t)g * M + m) * 64;
   if (KIND == 4) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  } else {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-}
-
-// Split a (possibly prescaled) activation pair into 16-bit high and low parts.
-// hi = round16(x); lo = round16(x - hi).  `sum` accumulates hi + lo as the MMA sees them.
-template <int KIND>
-__device__ __forceinline__ void split_pair(float xa, float xb, uint32_t& hi, uint32_t& lo, float& sum) {
-  if (KIND == 4) {
-    hi = pack_bf16(xa, xb);
-    const float ha = __uint_as_float(hi << 16), hb = __uint_as_float(hi & 0xFFFF0000u);
-    const float la = xa - ha, lb = xb - hb;
-    lo = pack_bf16(la, lb);
-    sum += (ha + __uint_as_float(lo << 16)) + (hb + __uint_as_float(lo & 0xFFFF0000u));
-  } else {
-    hi = pack_f16(xa, xb);
-    const __half2 h2 = *reinterpret_cast<const __half2*>(&hi);
-    const float ha = __low2float(h2), hb = __high2float(h2);
-    lo = pack_f16(xa - ha, xb - hb);
-  }
-}
-
-// Activations of one group for this thread: 8 consecutive k (k = 8j .. 8j+7) of
-// row `r` (and r + 8 when WIDE).  Rows >= M read as zero.
-template <bool WIDE>
-struct XRegs {
-  float4 v[WIDE ? 4 : 2];
-};
-
-template <bool WIDE>
-__device__ __forceinline__ void load_x(XRegs<WIDE>& x, const float* __restrict__ A, int M, int K, int g, int r,
-                                       int j) {
-  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4* p0 = reinterpret_cast<const float4*>(A + (size_t)r * K + g * 32 + j * 8);
-  x.v[0] = (r < M) ? __ldg(p0) : z;
-  x.v[1] = (r < M) ? __ldg(p0 + 1) : z;
-  if (WIDE) {
-    const float4* p1 = reinterpret_cast<const float4*>(A + (size_t)(r + 8) * K + g * 32 + j * 8);
-    x.v[2] = (r + 8 < M) ? __ldg(p1) : z;
-    x.v[3] = (r + 8 < M) ? __ldg(p1 + 1) : z;
-  }
-}
-
-// A fragments of the two MMAs that cover one 32-element group.
-//   !WIDE: f[m] = {hi(row r; pair a), lo(row r; pair a), hi(row r; pair b), lo(row r; pair b)}
-//    WIDE: hi[m] = {hi(r;a), hi(r+8;a), hi(r;b), hi(r+8;b)}, lo[m] likewise
-// Pair layout (which of the thread's 8 k values share a register) follows the
-// code unpacking: Q4 pairs nibble i with nibble i+4, Q8 pairs adjacent bytes.
-template <int KIND, bool WIDE>
-struct AFrag {
-  uint32_t hi[2][4];
-  uint32_t lo[2][4];  // only used when WIDE
-  float sx0, sx1;     // sum_k (hi + lo) of row r / row r + 8 over the whole group (Q4 only)
-};
-
-template <int KIND, bool WIDE>
-__device__ __forceinline__ void build_a(AFrag<KIND, WIDE>& f, const XRegs<WIDE>& x, float rs0, float rs1) {
-  float e[8], o[8];
-  e[0] = x.v[0].x, e[1] = x.v[0].y, e[2] = x.v[0].z, e[3] = x.v[0].w;
-  e[4] = x.v[1].x, e[5] = x.v[1].y, e[6] = x.v[1].z, e[7] = x.v[1].w;
-  if (KIND == 8) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) e[i] *= rs0;
-  }
-  // index pairs: [mma][a|b] -> (first, second)
-  constexpr int P4[2][2][2] = {{{0, 4}, {1, 5}}, {{2, 6}, {3, 7}}};
-  constexpr int P8[2][2][2] = {{{0, 1}, {2, 3}}, {{4, 5}, {6, 7}}};
-  float s0 = 0.f, s1 = 0.f;
-  if (!WIDE) {
-#pragma unroll
-    for (int m = 0; m < 2; m++)
-#pragma unroll
-      for (int ab = 0; ab < 2; ab++) {
-        const int i0 = (KIND == 4) ? P4[m][ab][0] : P8[m][ab][0];
-        const int i1 = (KIND == 4) ? P4[m][ab][1] : P8[m][ab][1];
-        split_pair<KIND>(e[i0], e[i1], f.hi[m][2 * ab], f.hi[m][2 * ab + 1], s0);
-      }
-  } else {
-    o[0] = x.v[2].x, o[1] = x.v[2].y, o[2] = x.v[2].z, o[3] = x.v[2].w;
-    o[4] = x.v[3].x, o[5] = x.v[3].y, o[6] = x.v[3].z, o[7] = x.v[3].w;
-    if (KIND == 8) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) o[i] *= rs1;
+    for (int i = 0; i < 4; i++) {
+      const int word = lane8 >> 1, byte = ((lane8 & 1) << 1) | (i >> 1), odd = i & 1;
+      uint8_t* w = d + word * 16 + odd * 8 + byte;
+      w[0] = (uint8_t)(q[i] >> 7);
+      w[4] = (uint8_t)(q[i] & 127);
     }
+  } else {
+    uint32_t hi = 0, lo = 0;
 #pragma unroll
-    for (int m = 0; m < 2; m++)
-#pragma unroll
-      for (int ab = 0; ab < 2; ab++) {
-        const int i0 = (KIND == 4) ? P4[m][ab][0] : P8[m][ab][0];
-        const int i1 = (KIND == 4) ? P4[m][ab][1] : P8[m][ab][1];
-        split_pair<KIND>(e[i0], e[i1], f.hi[m][2 * ab], f.lo[m][2 * ab], s0);
-        split_pair<KIND>(o[i0], o[i1], f.hi[m][2 * ab + 1], f.lo[m][2 * ab + 1], s1);
-      }
-  }
-  if (KIND == 4) {  // the four threads of a quad hold the four quarters of the group
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-    if (WIDE) {
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    for (int i = 0; i < 4; i++) {
+      hi |= (uint32_t)((q[i] >> 7) & 0xFF) << (8 * i);
+      lo |= (uint32_t)(q[i] & 127) << (8 * i);
     }
+    reinterpret_cast<uint2*>(d)[lane8] = make_uint2(hi, lo);
   }
-  f.sx0 = s0;
-  f.sx1 = s1;
+  if (lane8 == 0) xsc[(size_t)g * M + m] = make_float2(down, (float)sum);
 }
 
+// ---------------------------------------------------------------- main kernel
 template <int KIND, bool WIDE>
-__global__ void __launch_bounds__(kThreads, 1) qdecode_kernel(const Params p) {
+__global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kernel(const Params p) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   constexpr int NACC = WIDE ? 4 : 2;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);            // [kMaxStages]
-  uint64_t* empty = full + kMaxStages;                            // [kMaxStages]
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 128);
-  float* row_scale = reinterpret_cast<float*>(smem + 256);        // [16] Q8 prescale 2^e
-  float* row_inv = row_scale + 16;                                // [16] 2^-e
-  unsigned* row_max = reinterpret_cast<unsigned*>(row_inv + 16);  // [16] bits of max |x|
-  uint8_t* ring = smem + kHeaderBytes;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+  uint8_t* ring = smem + 1024;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int col0 = blockIdx.x * p.TN;
-  const int tn = min(p.TN, p.N - col0);
-  const int ns = tn >> 3;
-  const int nst = (p.G + kWarps - 1) / kWarps;
+  const int TN = p.NS * 8;
+  const int col0 = blockIdx.x * TN;
+  const int tn = min(TN, p.N - col0);
+  const int nwarps = p.NS * p.phases;
+  const int nst = (p.G + p.stage_rows - 1) / p.stage_rows;
   const uint32_t row_bytes = (uint32_t)tn * BB;
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; s++) {
-      mbar_init(smem_u32(&full[s]), 1);
-      mbar_init(smem_u32(&empty[s]), kWarps);
+      mbar_init(smem_u32(&full[s]), 2);            // weights armed first, digits once they exist
+      mbar_init(smem_u32(&empty[s]), nwarps);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (tid < 16) row_max[tid] = 0u;
   __syncthreads();
 
-  if (warp == kWarps) {
-    // ------------------------------------------------------------ producer
-    // One lane per group-row: the rows of a stage are issued by the warp in
-    // parallel (a single thread issuing them one by one is too slow to keep
-    // the stream busy).  Lane 0 arms the barrier before any copy can complete.
+  if (warp >= nwarps) {
+    // ------------------------------------------------------------ producer warp
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    bool live = true;
-    for (int st = 0; st < nst && live; st++) {
+    auto issue_weights = [&](int st) {
       const int slot = st % p.stages;
-      if (st >= p.stages) {
-        int okw = 1;
-        if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag, p.status);
-        live = __shfl_sync(0xffffffffu, okw, 0) != 0;
-        if (!live) break;
-      }
-      const int rows = min(kWarps, p.G - st * kWarps);
+      const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
       const uint32_t bar = smem_u32(&full[slot]);
       if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
       __syncwarp();
       const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
-      const uint8_t* src = p.B + ((size_t)(st * kWarps) * p.N + col0) * BB;
-      if (lane < rows) bulk_load(dst + lane * p.row_pitch, src + (size_t)lane * p.N * BB, row_bytes, bar, policy);
+      const uint8_t* src = p.B + ((size_t)st * p.stage_rows * p.N + col0) * BB;
+      for (int rr = lane; rr < rows; rr += 32)
+        bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * p.N * BB, row_bytes, bar, policy);
+    };
+    auto issue_digits = [&](int st) {
+      const int slot = st % p.stages;
+      const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
+      const uint32_t bar = smem_u32(&full[slot]);
+      // bulk copies move multiples of 16 bytes: the scale span is rounded up (the scratch has slack)
+      const uint32_t db = (uint32_t)rows * p.M * 64, sb = (((uint32_t)rows * p.M * 8) + 15u) & ~15u;
+      if (lane == 0) {
+        mbar_expect_tx(bar, db + sb);
+        uint8_t* base = ring + (size_t)slot * p.stage_bytes + p.w_bytes;
+        bulk_load_default(smem_u32(base), p.xdig + (size_t)st * p.stage_rows * p.M * 64, db, bar);
+        bulk_load_default(smem_u32(base + p.d_bytes), p.xsc + (size_t)st * p.stage_rows * p.M, sb, bar);
+      }
+      __syncwarp();
+    };
+    // weights of the first ring-full go out before anything waits on the previous launch
+    const int first = min(nst, p.stages);
+    for (int st = 0; st < first; st++) issue_weights(st);
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // quantise_rows has finished: the digits exist
+    for (int st = 0; st < first; st++) issue_digits(st);
+    bool live = true;
+    for (int st = first; st < nst && live; st++) {
+      const int slot = st % p.stages;
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag, p.status);
+      live = __shfl_sync(0xffffffffu, okw, 0) != 0;
+      if (!live) break;
+      issue_weights(st);
+      issue_digits(st);
     }
     return;  // consumers observe every full barrier, so the copies land before the CTA ends
   }
 
   // -------------------------------------------------------------- consumers
+  const int slice = warp % p.NS, phase = warp / p.NS;
+  const bool has_cols = slice * 8 < tn;
   const int r = lane >> 2, j = lane & 3;
-  float rs0 = 1.f, rs1 = 1.f;
-  if (KIND == 8) {
-    // Per-row power-of-two prescale so that f16 can carry the activations:
-    // max |x_row| is moved into [2^13, 2^14).
-    for (int row = 0; row < p.M; row++) {
-      float m = 0.f;
-      for (int k = tid; k < p.K; k += kWarps * 32) m = fmaxf(m, fabsf(__ldg(p.A + (size_t)row * p.K + k)));
+  const int m0 = min(r, p.M - 1), m1 = min(r + 8, p.M - 1);   // rows past M repeat the last one (never stored)
+  float acc[NACC];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      if (lane == 0) atomicMax(&row_max[row], __float_as_uint(m));
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32));
-    if (tid < 16) {
-      const unsigned bits = row_max[tid];
-      int e = 0;
-      const int ex = (int)(bits >> 23);
-      if (ex > 0 && ex < 255) e = 13 - (ex - 127);
-      e = max(-100, min(100, e));
-      row_scale[tid] = __uint_as_float((unsigned)(127 + e) << 23);
-      row_inv[tid] = __uint_as_float((unsigned)(127 - e) << 23);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32));
-    rs0 = row_scale[r];
-    rs1 = row_scale[r + 8];
-  }
+  for (int i = 0; i < NACC; i++) acc[i] = 0.f;
 
-  float acc[kMaxSlices][NACC];
-#pragma unroll
-  for (int s = 0; s < kMaxSlices; s++)
-#pragma unroll
-    for (int i = 0; i < NACC; i++) acc[s][i] = 0.f;
-
-  XRegs<WIDE> xr;
-  if (warp < p.G) load_x<WIDE>(xr, p.A, p.M, p.K, warp, r, j);
   bool ok = true;
-
   for (int st = 0; st < nst && ok; st++) {
     const int slot = st % p.stages;
-    const int g = st * kWarps + warp;
-    AFrag<KIND, WIDE> af;
-    if (g < p.G) {
-      build_a<KIND, WIDE>(af, xr, rs0, rs1);
-      if (g + kWarps < p.G) load_x<WIDE>(xr, p.A, p.M, p.K, g + kWarps, r, j);
-    }
     ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag, p.status);
-    if (ok && g < p.G) {
-      const uint8_t* row_base = ring + (size_t)slot * p.stage_bytes + (size_t)warp * p.row_pitch;
-#pragma unroll
-      for (int s = 0; s < kMaxSlices; s++) {
-        if (s < ns) {
-          uint32_t b[4];
-          float sc0, sc1, zz0 = 0.f, zz1 = 0.f;
+    if (ok && has_cols) {
+      const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+      const uint8_t* dig = stage + p.w_bytes;
+      const float2* sc = reinterpret_cast<const float2*>(stage + p.w_bytes + p.d_bytes);
+      const int rows_here = min(p.stage_rows, p.G - st * p.stage_rows);
+#pragma unroll 4
+      for (int row = phase; row < rows_here; row += p.phases) {   // this phase's group-rows inside the stage
+        {
+          const uint8_t* wrow = stage + (size_t)row * p.row_pitch;
+          // ---- B fragment: the j-th eight codes of column slice*8 + r
+          uint32_t b0, b1;
+          float sc0, sc1, z0 = 0.f, z1 = 0.f;
           if (KIND == 4) {
-            const uint32_t w = lds32(row_base + (uint32_t)(s * 8 + r) * BB + 4 * j);
-            const float2 q0 = lds_f2(row_base + (uint32_t)(s * 8 + 2 * j) * BB + 16);
-            const float2 q1 = lds_f2(row_base + (uint32_t)(s * 8 + 2 * j + 1) * BB + 16);
-            sc0 = q0.x, sc1 = q1.x;
-            zz0 = 128.f + q0.y, zz1 = 128.f + q1.y;
-            // nibble i in the low half, nibble i+4 in the high half, each OR-ed into bf16 128.0
-            b[0] = (w & 0x000F000Fu) | 0x43004300u;
-            b[1] = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
-            b[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
-            b[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(wrow + (slice * 8 + r) * BB + 4 * j);
+            b0 = w & 0x0F0F0F0Fu;          // codes of k = 8j + 0, 2, 4, 6
+            b1 = (w >> 4) & 0x0F0F0F0Fu;   // codes of k = 8j + 1, 3, 5, 7
+            const float2 q0 = *reinterpret_cast<const float2*>(wrow + (slice * 8 + 2 * j) * BB + 16);
+            const float2 q1 = *reinterpret_cast<const float2*>(wrow + (slice * 8 + 2 * j + 1) * BB + 16);
+            sc0 = q0.x, z0 = q0.y, sc1 = q1.x, z1 = q1.y;
           } else {
-            // the stage base is 1024-byte aligned and row pitches are multiples of 16,
-            // so the byte offset inside the stage decides the word alignment
-            const uint32_t off = (uint32_t)(s * 8 + r) * BB + 2 + 8 * j;
-            const uint8_t* al = row_base + (off & ~3u);
+            const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)(slice * 8 + r) * BB + 2 + 8 * j;
+            const uint32_t* al = reinterpret_cast<const uint32_t*>(stage + (off & ~3u));
             const uint32_t sh = (off & 3u) * 8;
-            const uint32_t w0 = lds32(al), w1 = lds32(al + 4), w2 = lds32(al + 8);
-            const uint32_t lo = __funnelshift_r(w0, w1, sh) ^ 0x80808080u;
-            const uint32_t hi = __funnelshift_r(w1, w2, sh) ^ 0x80808080u;
-            const uint32_t h0 = lds16(row_base + (uint32_t)(s * 8 + 2 * j) * BB);
-            const uint32_t h1 = lds16(row_base + (uint32_t)(s * 8 + 2 * j + 1) * BB);
-            sc0 = __half2float(__ushort_as_half((unsigned short)h0));
-            sc1 = __half2float(__ushort_as_half((unsigned short)h1));
-            // bytes u = q + 128 become f16 (1024 + u); subtracting 1152 leaves q exactly
-            const uint32_t k1152 = 0x64806480u;
-            uint32_t t;
-            t = __byte_perm(lo, 0x64646464u, 0x4140);
-            asm("sub.f16x2 %0, %1, %2;" : "=r"(b[0]) : "r"(t), "r"(k1152));
-            t = __byte_perm(lo, 0x64646464u, 0x4342);
-            asm("sub.f16x2 %0, %1, %2;" : "=r"(b[1]) : "r"(t), "r"(k1152));
-            t = __byte_perm(hi, 0x64646464u, 0x4140);
-            asm("sub.f16x2 %0, %1, %2;" : "=r"(b[2]) : "r"(t), "r"(k1152));
-            t = __byte_perm(hi, 0x64646464u, 0x4342);
-            asm("sub.f16x2 %0, %1, %2;" : "=r"(b[3]) : "r"(t), "r"(k1152));
+            const uint32_t w0 = al[0], w1 = al[1], w2 = al[2];
+            b0 = __funnelshift_r(w0, w1, sh);   // codes of k = 8j .. 8j+3
+            b1 = __funnelshift_r(w1, w2, sh);   // codes of k = 8j+4 .. 8j+7
+            sc0 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(wrow + (slice * 8 + 2 * j) * BB)));
+            sc1 = __half2float(
+                __ushort_as_half(*reinterpret_cast<const unsigned short*>(wrow + (slice * 8 + 2 * j + 1) * BB)));
           }
-          float c[4] = {0.f, 0.f, 0.f, 0.f};
-          mma16816<KIND>(c, af.hi[0], b[0], b[1]);
-          mma16816<KIND>(c, af.hi[1], b[2], b[3]);
-          if (WIDE) {
-            mma16816<KIND>(c, af.lo[0], b[0], b[1]);
-            mma16816<KIND>(c, af.lo[1], b[2], b[3]);
-          }
+          // ---- A fragment(s): digit words of activation row r (and r + 8)
+          const uint4 d0 = *reinterpret_cast<const uint4*>(dig + ((size_t)row * p.M + m0) * 64 + 16 * j);
+          const float2 x0 = sc[(size_t)row * p.M + m0];
           if (!WIDE) {
-            // rows 0-7 carry the high parts, rows 8-15 the low parts of the same activations
-            const float t0 = c[0] + c[2], t1 = c[1] + c[3];
+            // rows 0-7: high digits, rows 8-15: low digits of the same activation rows
+            const uint32_t a[4] = {d0.x, d0.y, d0.z, d0.w};
+            int c[4] = {0, 0, 0, 0};
+            imma(c, a, b0, b1);
+            const float f0 = (float)(c[0] * 128 + c[2]), f1 = (float)(c[1] * 128 + c[3]);
             if (KIND == 4) {
-              acc[s][0] = fmaf(sc0, fmaf(-zz0, af.sx0, t0), acc[s][0]);
-              acc[s][1] = fmaf(sc1, fmaf(-zz1, af.sx0, t1), acc[s][1]);
+              acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f0), acc[0]);
+              acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f1), acc[1]);
             } else {
-              acc[s][0] = fmaf(sc0, t0, acc[s][0]);
-              acc[s][1] = fmaf(sc1, t1, acc[s][1]);
+              acc[0] = fmaf(sc0 * x0.x, f0, acc[0]);
+              acc[1] = fmaf(sc1 * x0.x, f1, acc[1]);
             }
           } else {
+            const uint4 d1 = *reinterpret_cast<const uint4*>(dig + ((size_t)row * p.M + m1) * 64 + 16 * j);
+            const float2 x1 = sc[(size_t)row * p.M + m1];
+            const uint32_t ah[4] = {d0.x, d1.x, d0.z, d1.z};   // high digits of rows r, r + 8
+            const uint32_t al4[4] = {d0.y, d1.y, d0.w, d1.w};  // low digits
+            int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+            imma(ch, ah, b0, b1);
+            imma(cl, al4, b0, b1);
+            const float f00 = (float)(ch[0] * 128 + cl[0]), f01 = (float)(ch[1] * 128 + cl[1]);
+            const float f10 = (float)(ch[2] * 128 + cl[2]), f11 = (float)(ch[3] * 128 + cl[3]);
             if (KIND == 4) {
-              acc[s][0] = fmaf(sc0, fmaf(-zz0, af.sx0, c[0]), acc[s][0]);
-              acc[s][1] = fmaf(sc1, fmaf(-zz1, af.sx0, c[1]), acc[s][1]);
-              acc[s][2] = fmaf(sc0, fmaf(-zz0, af.sx1, c[2]), acc[s][2]);
-              acc[s][3] = fmaf(sc1, fmaf(-zz1, af.sx1, c[3]), acc[s][3]);
+              acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f00), acc[0]);
+              acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f01), acc[1]);
+              acc[2] = fmaf(sc0 * x1.x, fmaf(-z0, x1.y, f10), acc[2]);
+              acc[3] = fmaf(sc1 * x1.x, fmaf(-z1, x1.y, f11), acc[3]);
             } else {
-              acc[s][0] = fmaf(sc0, c[0], acc[s][0]);
-              acc[s][1] = fmaf(sc1, c[1], acc[s][1]);
-              acc[s][2] = fmaf(sc0, c[2], acc[s][2]);
-              acc[s][3] = fmaf(sc1, c[3], acc[s][3]);
+              acc[0] = fmaf(sc0 * x0.x, f00, acc[0]);
+              acc[1] = fmaf(sc1 * x0.x, f01, acc[1]);
+              acc[2] = fmaf(sc0 * x1.x, f10, acc[2]);
+              acc[3] = fmaf(sc1 * x1.x, f11, acc[3]);
             }
           }
         }
@@ -384,63 +290,81 @@ __global__ void __launch_bounds__(kThreads, 1) qdecode_kernel(const Params p) {
     if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
   }
 
-  // ---------------------------------------------- cross-warp sum, fixed order
-  asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32));  // every consumer is done with the ring
+  // ---------------------------------------------- sum the phases, fixed order
+  asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every consumer is done with the ring
   constexpr int ROWS = WIDE ? 16 : 8;
-  float* red = reinterpret_cast<float*>(ring);  // [kWarps][ROWS][TN]
-  const int TNp = p.TN;
-#pragma unroll
-  for (int s = 0; s < kMaxSlices; s++) {
-    if (s < ns) {
-      float* dst = red + ((size_t)warp * ROWS + r) * TNp + s * 8 + 2 * j;
-      *reinterpret_cast<float2*>(dst) = make_float2(acc[s][0], acc[s][1]);
-      if (WIDE) *reinterpret_cast<float2*>(dst + 8 * TNp) = make_float2(acc[s][2], acc[s][3]);
-    }
+  float* red = reinterpret_cast<float*>(ring);        // [phases][ROWS][TN]
+  {
+    float* dst = red + ((size_t)phase * ROWS + r) * TN + slice * 8 + 2 * j;
+    *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
+    if (WIDE) *reinterpret_cast<float2*>(dst + 8 * TN) = make_float2(acc[2], acc[3]);
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32));
+  asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
   if (*abort_flag) return;
-  for (int idx = tid; idx < p.M * tn; idx += kWarps * 32) {
-    const int row = idx / tn, col = idx - row * tn;
+  for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+    const int m = i / tn, c = i - m * tn;
     float sum = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; w++) sum += red[((size_t)w * ROWS + row) * TNp + col];
-    if (KIND == 8) sum *= row_inv[row];
-    p.C[(size_t)row * p.N + col0 + col] = sum;
+    for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * ROWS + m) * TN + c];
+    p.C[(size_t)m * p.N + col0 + c] = sum;
   }
 }
 
 struct Plan {
-  int TN, tiles, row_pitch, stage_bytes, stages;
+  Params p;
+  int tiles;
   size_t smem;
+  bool ok;
 };
 
-Plan make_plan(int kind, int64_t M, int64_t N) {
+Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
   const int sms = 148;
-  // Smallest multiple-of-8 tile width that covers N with a whole number of
-  // waves of CTAs, capped at kMaxSlices * 8 columns.
-  int64_t waves = 1;
-  int TN;
-  for (;; waves++) {
-    TN = (int)(8 * ((N + 8 * sms * waves - 1) / (8 * sms * waves)));
-    if (TN <= kMaxSlices * 8) break;
+  Plan pl{};
+  Params& p = pl.p;
+  p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)(K / 32);
+  // Slices per CTA: the fewest that cover N in a whole number of waves, at most 16 (128 columns).
+  int NS = 0;
+  for (int64_t waves = 1;; waves++) {
+    NS = (int)((N + 8 * sms * waves - 1) / (8 * sms * waves));
+    if (NS <= kMaxConsumerWarps) break;
   }
-  Plan pl;
-  pl.TN = TN;
+  p.NS = NS;
+  const int TN = NS * 8;
   pl.tiles = (int)((N + TN - 1) / TN);
-  pl.row_pitch = TN * BB;  // multiple of 16 since TN % 8 == 0
-  pl.stage_bytes = ((kWarps * pl.row_pitch + 1023) / 1024) * 1024;
-  pl.stages = kRingBudget / pl.stage_bytes;
-  if (pl.stages > kMaxStages) pl.stages = kMaxStages;
-  if (pl.stages < 2) pl.stages = 2;
-  const size_t ring = (size_t)pl.stages * pl.stage_bytes + 16;
-  const size_t red = (size_t)kWarps * (M > 8 ? 16 : 8) * TN * 4;
-  pl.smem = kHeaderBytes + (ring > red ? ring : red);
+  int phases = kMaxConsumerWarps / NS;
+  if (phases < 1) phases = 1;
+  while (phases > 1 && phases * 4 > p.G) phases--;   // short K: do not over-split
+  p.phases = phases;
+  p.row_pitch = TN * BB;
+  p.stage_rows = phases * ((kStageRows + phases - 1) / phases);
+  p.w_bytes = ((p.stage_rows * p.row_pitch + 16 + 127) / 128) * 128;   // + slack for the Q8 read-ahead
+  p.d_bytes = p.stage_rows * p.M * 64;
+  p.s_bytes = ((p.stage_rows * p.M * 8 + 127) / 128) * 128;
+  p.stage_bytes = ((p.w_bytes + p.d_bytes + p.s_bytes + 1023) / 1024) * 1024;
+  int stages = (kSmemBudget - 1024) / p.stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  p.stages = stages;
+  const size_t red = (size_t)phases * (M > 8 ? 16 : 8) * TN * 4;
+  const size_t ring = (size_t)(stages > 0 ? stages : 0) * p.stage_bytes;
+  pl.smem = 1024 + (ring > red ? ring : red);
+  pl.ok = stages >= 2 && pl.smem <= 227 * 1024;
   return pl;
 }
 
+template <typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int KIND, bool WIDE>
-cudaError_t launch_one(const Params& p, const Plan& pl, cudaStream_t s) {
+cudaError_t launch_main(const Plan& pl, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(qdecode_kernel<KIND, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -448,9 +372,11 @@ cudaError_t launch_one(const Params& p, const Plan& pl, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  qdecode_kernel<KIND, WIDE><<<pl.tiles, kThreads, pl.smem, s>>>(p);
+  const int threads = (pl.p.NS * pl.p.phases + 1) * 32;
+  const cudaError_t e = launch_pdl(qdecode_kernel<KIND, WIDE>, dim3((unsigned)pl.tiles), dim3((unsigned)threads),
+                                   pl.smem, s, pl.p);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace
@@ -460,22 +386,44 @@ bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups)
   if (M < 1 || M > 16) return false;
   if (N < 8 || (N % 8) != 0) return false;       // 16-byte alignment of every group-row span
   if (K < 32 || (K % 32) != 0 || groups != K / 32) return false;
-  if (N > (1 << 30) || K > (1 << 24)) return false;
-  return true;
+  if (N > (1 << 30) || K > (1 << 22)) return false;
+  return make_plan(kind, M, N, K).ok;
 }
 
-cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
-                           int64_t K, int64_t groups, cudaStream_t s) {
-  if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15)) return cudaErrorMisalignedAddress;
-  const Plan pl = make_plan(kind, M, N);
-  Params p;
-  p.A = A, p.B = B, p.C = C;
-  p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
-  p.status = kernel_status_ptr();
-  if (!p.status) return cudaErrorUnknown;
-  p.TN = pl.TN, p.row_pitch = pl.row_pitch, p.stages = pl.stages, p.stage_bytes = pl.stage_bytes;
-  if (kind == 4) return (M > 8) ? launch_one<4, true>(p, pl, s) : launch_one<4, false>(p, pl, s);
-  return (M > 8) ? launch_one<8, true>(p, pl, s) : launch_one<8, false>(p, pl, s);
+size_t qdecode_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
+  (void)kind;
+  (void)N;
+  const size_t G = (size_t)(K / 32);
+  return ((G * (size_t)M * 64 + 255) & ~size_t(255)) + G * (size_t)M * 8 + 64;
+}
+
+cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
+                           int64_t groups, Workspace ws, cudaStream_t s) {
+  (void)groups;
+  if (!ws.ptr || ws.bytes < qdecode_workspace_bytes(kind, M, N, K)) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(ws.ptr) & 255))
+    return cudaErrorMisalignedAddress;
+  Plan pl = make_plan(kind, M, N, K);
+  if (!pl.ok) return cudaErrorInvalidValue;
+  const size_t G = (size_t)(K / 32);
+  uint8_t* xdig = static_cast<uint8_t*>(ws.ptr);
+  float2* xsc = reinterpret_cast<float2*>(xdig + ((G * (size_t)M * 64 + 255) & ~size_t(255)));
+  const int qthreads = (int)(M * G * 8);
+  cudaError_t e;
+  if (kind == 4)
+    e = launch_pdl(quantise_rows<4>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig, xsc,
+                   (int)M, (int)K, (int)G);
+  else
+    e = launch_pdl(quantise_rows<8>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig, xsc,
+                   (int)M, (int)K, (int)G);
+  count_launch();
+  if (e != cudaSuccess) return e;
+  pl.p.B = B, pl.p.C = C, pl.p.xdig = xdig, pl.p.xsc = xsc;
+  pl.p.status = kernel_status_ptr();
+  if (!pl.p.status) return cudaErrorUnknown;
+  if (kind == 4) return (M > 8) ? launch_main<4, true>(pl, s) : launch_main<4, false>(pl, s);
+  return (M > 8) ? launch_main<8, true>(pl, s) : launch_main<8, false>(pl, s);
 }
 
 }  // namespace smith
