@@ -42,7 +42,7 @@ namespace {
 
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr int kMaxConsumerWarps = 16;
+constexpr int kMaxConsumerWarps = 28;
 constexpr int kStageRows = 16;         // group-rows per pipeline stage (rounded up to a multiple of the phases)
 
 struct Params {
@@ -60,6 +60,28 @@ __device__ __forceinline__ void imma(int (&c)[4], const uint32_t (&a)[4], uint32
   asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Shared-memory loads by 32-bit address (keeps the hot loop's address arithmetic to single adds).
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float2 lds_f32x2(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_u32x4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
 }
 
 // ---------------------------------------------------------------- activations -> digits (global scratch)
@@ -210,80 +232,88 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; i++) acc[i] = 0.f;
+  const uint32_t ring_s = smem_u32(ring);
+  // Q4: word j of the block of column slice*8 + r.  Q8: its codes 8j .. 8j+7 start at byte 2 + 8j.
+  const uint32_t off_w = (uint32_t)(slice * 8 + r) * BB + (KIND == 4 ? 4u * j : 2u + 8u * j);
+  const uint32_t sh8 = (off_w & 3u) * 8;
+  const uint32_t off_q = (uint32_t)(slice * 8 + 2 * j) * BB + (KIND == 4 ? 16u : 0u);   // scale (and zero)
+  const uint32_t off_d0 = (uint32_t)m0 * 64 + 16u * j, off_d1 = (uint32_t)m1 * 64 + 16u * j;
+  const uint32_t off_x0 = (uint32_t)m0 * 8, off_x1 = (uint32_t)m1 * 8;
+  const uint32_t w_step = (uint32_t)p.phases * (uint32_t)p.row_pitch;
+  const uint32_t d_step = (uint32_t)p.phases * (uint32_t)(p.M * 64), s_step = (uint32_t)p.phases * (uint32_t)(p.M * 8);
 
   bool ok = true;
   for (int st = 0; st < nst && ok; st++) {
     const int slot = st % p.stages;
     ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag, p.status);
     if (ok && has_cols) {
-      const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-      const uint8_t* dig = stage + p.w_bytes;
-      const float2* sc = reinterpret_cast<const float2*>(stage + p.w_bytes + p.d_bytes);
+      // 32-bit shared addresses: a per-thread constant part plus a per-row base that advances by a stride
+      const uint32_t stage = ring_s + (uint32_t)slot * (uint32_t)p.stage_bytes;
       const int rows_here = min(p.stage_rows, p.G - st * p.stage_rows);
+      uint32_t wrow = stage + (uint32_t)phase * (uint32_t)p.row_pitch;
+      uint32_t drow = stage + (uint32_t)p.w_bytes + (uint32_t)phase * (uint32_t)(p.M * 64);
+      uint32_t srow = stage + (uint32_t)(p.w_bytes + p.d_bytes) + (uint32_t)phase * (uint32_t)(p.M * 8);
 #pragma unroll 4
       for (int row = phase; row < rows_here; row += p.phases) {   // this phase's group-rows inside the stage
-        {
-          const uint8_t* wrow = stage + (size_t)row * p.row_pitch;
-          // ---- B fragment: the j-th eight codes of column slice*8 + r
-          uint32_t b0, b1;
-          float sc0, sc1, z0 = 0.f, z1 = 0.f;
+        // ---- B fragment: the j-th eight codes of column slice*8 + r
+        uint32_t b0, b1;
+        float sc0, sc1, z0 = 0.f, z1 = 0.f;
+        if (KIND == 4) {
+          const uint32_t w = lds_u32(wrow + off_w);
+          b0 = w & 0x0F0F0F0Fu;          // codes of k = 8j + 0, 2, 4, 6
+          b1 = (w >> 4) & 0x0F0F0F0Fu;   // codes of k = 8j + 1, 3, 5, 7
+          const float2 q0 = lds_f32x2(wrow + off_q);
+          const float2 q1 = lds_f32x2(wrow + off_q + BB);
+          sc0 = q0.x, z0 = q0.y, sc1 = q1.x, z1 = q1.y;
+        } else {
+          // 34-byte blocks are 2-byte aligned: aligned words around the codes, then a funnel shift.
+          // Stage bases and row pitches are multiples of 16, so the constant part decides the shift.
+          const uint32_t a = wrow + (off_w & ~3u);
+          const uint32_t w0 = lds_u32(a), w1 = lds_u32(a + 4), w2 = lds_u32(a + 8);
+          b0 = __funnelshift_r(w0, w1, sh8);   // codes of k = 8j .. 8j+3
+          b1 = __funnelshift_r(w1, w2, sh8);   // codes of k = 8j+4 .. 8j+7
+          sc0 = __half2float(__ushort_as_half((unsigned short)lds_u16(wrow + off_q)));
+          sc1 = __half2float(__ushort_as_half((unsigned short)lds_u16(wrow + off_q + BB)));
+        }
+        // ---- A fragment(s): digit words of activation row r (and r + 8)
+        const uint4 d0 = lds_u32x4(drow + off_d0);
+        const float2 x0 = lds_f32x2(srow + off_x0);
+        if (!WIDE) {
+          // rows 0-7: high digits, rows 8-15: low digits of the same activation rows
+          const uint32_t a4[4] = {d0.x, d0.y, d0.z, d0.w};
+          int c[4] = {0, 0, 0, 0};
+          imma(c, a4, b0, b1);
+          const float f0 = (float)(c[0] * 128 + c[2]), f1 = (float)(c[1] * 128 + c[3]);
           if (KIND == 4) {
-            const uint32_t w = *reinterpret_cast<const uint32_t*>(wrow + (slice * 8 + r) * BB + 4 * j);
-            b0 = w & 0x0F0F0F0Fu;          // codes of k = 8j + 0, 2, 4, 6
-            b1 = (w >> 4) & 0x0F0F0F0Fu;   // codes of k = 8j + 1, 3, 5, 7
-            const float2 q0 = *reinterpret_cast<const float2*>(wrow + (slice * 8 + 2 * j) * BB + 16);
-            const float2 q1 = *reinterpret_cast<const float2*>(wrow + (slice * 8 + 2 * j + 1) * BB + 16);
-            sc0 = q0.x, z0 = q0.y, sc1 = q1.x, z1 = q1.y;
+            acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f0), acc[0]);
+            acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f1), acc[1]);
           } else {
-            const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)(slice * 8 + r) * BB + 2 + 8 * j;
-            const uint32_t* al = reinterpret_cast<const uint32_t*>(stage + (off & ~3u));
-            const uint32_t sh = (off & 3u) * 8;
-            const uint32_t w0 = al[0], w1 = al[1], w2 = al[2];
-            b0 = __funnelshift_r(w0, w1, sh);   // codes of k = 8j .. 8j+3
-            b1 = __funnelshift_r(w1, w2, sh);   // codes of k = 8j+4 .. 8j+7
-            sc0 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(wrow + (slice * 8 + 2 * j) * BB)));
-            sc1 = __half2float(
-                __ushort_as_half(*reinterpret_cast<const unsigned short*>(wrow + (slice * 8 + 2 * j + 1) * BB)));
+            acc[0] = fmaf(sc0 * x0.x, f0, acc[0]);
+            acc[1] = fmaf(sc1 * x0.x, f1, acc[1]);
           }
-          // ---- A fragment(s): digit words of activation row r (and r + 8)
-          const uint4 d0 = *reinterpret_cast<const uint4*>(dig + ((size_t)row * p.M + m0) * 64 + 16 * j);
-          const float2 x0 = sc[(size_t)row * p.M + m0];
-          if (!WIDE) {
-            // rows 0-7: high digits, rows 8-15: low digits of the same activation rows
-            const uint32_t a[4] = {d0.x, d0.y, d0.z, d0.w};
-            int c[4] = {0, 0, 0, 0};
-            imma(c, a, b0, b1);
-            const float f0 = (float)(c[0] * 128 + c[2]), f1 = (float)(c[1] * 128 + c[3]);
-            if (KIND == 4) {
-              acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f0), acc[0]);
-              acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f1), acc[1]);
-            } else {
-              acc[0] = fmaf(sc0 * x0.x, f0, acc[0]);
-              acc[1] = fmaf(sc1 * x0.x, f1, acc[1]);
-            }
+        } else {
+          const uint4 d1 = lds_u32x4(drow + off_d1);
+          const float2 x1 = lds_f32x2(srow + off_x1);
+          const uint32_t ah[4] = {d0.x, d1.x, d0.z, d1.z};   // high digits of rows r, r + 8
+          const uint32_t al4[4] = {d0.y, d1.y, d0.w, d1.w};  // low digits
+          int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+          imma(ch, ah, b0, b1);
+          imma(cl, al4, b0, b1);
+          const float f00 = (float)(ch[0] * 128 + cl[0]), f01 = (float)(ch[1] * 128 + cl[1]);
+          const float f10 = (float)(ch[2] * 128 + cl[2]), f11 = (float)(ch[3] * 128 + cl[3]);
+          if (KIND == 4) {
+            acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f00), acc[0]);
+            acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f01), acc[1]);
+            acc[2] = fmaf(sc0 * x1.x, fmaf(-z0, x1.y, f10), acc[2]);
+            acc[3] = fmaf(sc1 * x1.x, fmaf(-z1, x1.y, f11), acc[3]);
           } else {
-            const uint4 d1 = *reinterpret_cast<const uint4*>(dig + ((size_t)row * p.M + m1) * 64 + 16 * j);
-            const float2 x1 = sc[(size_t)row * p.M + m1];
-            const uint32_t ah[4] = {d0.x, d1.x, d0.z, d1.z};   // high digits of rows r, r + 8
-            const uint32_t al4[4] = {d0.y, d1.y, d0.w, d1.w};  // low digits
-            int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
-            imma(ch, ah, b0, b1);
-            imma(cl, al4, b0, b1);
-            const float f00 = (float)(ch[0] * 128 + cl[0]), f01 = (float)(ch[1] * 128 + cl[1]);
-            const float f10 = (float)(ch[2] * 128 + cl[2]), f11 = (float)(ch[3] * 128 + cl[3]);
-            if (KIND == 4) {
-              acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f00), acc[0]);
-              acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f01), acc[1]);
-              acc[2] = fmaf(sc0 * x1.x, fmaf(-z0, x1.y, f10), acc[2]);
-              acc[3] = fmaf(sc1 * x1.x, fmaf(-z1, x1.y, f11), acc[3]);
-            } else {
-              acc[0] = fmaf(sc0 * x0.x, f00, acc[0]);
-              acc[1] = fmaf(sc1 * x0.x, f01, acc[1]);
-              acc[2] = fmaf(sc0 * x1.x, f10, acc[2]);
-              acc[3] = fmaf(sc1 * x1.x, f11, acc[3]);
-            }
+            acc[0] = fmaf(sc0 * x0.x, f00, acc[0]);
+            acc[1] = fmaf(sc1 * x0.x, f01, acc[1]);
+            acc[2] = fmaf(sc0 * x1.x, f10, acc[2]);
+            acc[3] = fmaf(sc1 * x1.x, f11, acc[3]);
           }
         }
+        wrow += w_step, drow += d_step, srow += s_step;
       }
     }
     __syncwarp();
@@ -326,7 +356,7 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   int NS = 0;
   for (int64_t waves = 1;; waves++) {
     NS = (int)((N + 8 * sms * waves - 1) / (8 * sms * waves));
-    if (NS <= kMaxConsumerWarps) break;
+    if (NS <= 16) break;   // at most 128 columns per CTA
   }
   p.NS = NS;
   const int TN = NS * 8;
