@@ -365,3 +365,62 @@ def test_fused_gather_two_shards_emulated_on_one_gpu():
     assert states[0].get(np.uint32)[0] == 1 and states[1].get(np.uint32)[0] == 1  # each rank advanced one step
     for b in ys + states + [ab]:
         b.free()
+
+
+# ------------------------------------------------------------------ full-size projection shapes, sampled columns
+# BASELINE configs 4 and 5: every Q4 linear projection of a Llama-3-8B-shaped and a 70B-shaped decode
+# step.  Weights are generated and packed on the device at full size; a window of columns is
+# downloaded and checked against the oracle (packed bytes bit-exact, outputs within tolerance).
+LLAMA_8B = [("wq", 4096, 4096), ("wk", 4096, 1024), ("wo", 4096, 4096), ("gate", 4096, 14336), ("down", 14336, 4096),
+            ("lm_head", 4096, 128256)]
+LLAMA_70B = [("wq", 8192, 8192), ("wk", 8192, 1024), ("gate", 8192, 28672), ("down", 28672, 8192)]
+
+
+def _check_projection(K, N, Ms, std, seed):
+    G = K // 32
+    wb = DevBuf(K * N * 4)
+    device.fillNormal(wb.handle, K * N, seed, std)
+    pb = DevBuf(G * N * 24)
+    device.q4Pack(wb.handle, pb.handle, K, N)
+    device.synchronize()
+    c0 = (N // 2) // 8 * 8
+    c1 = min(N, c0 + 48)
+    # packed bytes of the window: bit-exact against the CPU packer on the same f32 columns
+    w_cols = np.empty((K, c1 - c0), np.float32)
+    full_rows = wb.get(np.float32).reshape(K, N) if K * N <= (1 << 26) else None
+    if full_rows is not None:
+        w_cols[:] = full_rows[:, c0:c1]
+    else:                                               # too large to bring back whole: row by row
+        for k in range(K):
+            w_cols[k] = device.download(wb.handle, (c1 - c0) * 4, np.float32, offset=(k * N + c0) * 4)
+    wb.free()
+    packed_cols = np.empty((G, (c1 - c0) * 24), np.uint8)
+    for g in range(G):
+        packed_cols[g] = device.download(pb.handle, (c1 - c0) * 24, np.uint8, offset=(g * N + c0) * 24)
+    packed_cols = packed_cols.reshape(-1)
+    assert np.array_equal(packed_cols, O.quantize_q4(w_cols))
+    rng = np.random.default_rng(seed)
+    for M in Ms:
+        a = rng.standard_normal((M, K)).astype(np.float32)
+        ab, cb = DevBuf.of(a), DevBuf(M * N * 4)
+        device.qmatmul(4, ab.handle, pb.handle, cb.handle, M, N, K, G, device.PATH_AUTO)
+        device.synchronize()
+        assert device.kernelStatus() == 0
+        got = cb.get(np.float32).reshape(M, N)[:, c0:c1]
+        want = O.matmul(a, packed_cols, K, c1 - c0, "q4", threads=O.max_threads())
+        ok, worst = within_tolerance(got, want, a, packed_cols, K, c1 - c0, "q4", REL)
+        assert ok, f"K={K} N={N} M={M}: worst err/bound = {worst}"
+        assert np.all(np.isfinite(cb.get(np.float32)))
+        ab.free()
+        cb.free()
+    pb.free()
+
+
+@pytest.mark.parametrize("name,K,N", LLAMA_8B)
+def test_llama_8b_shaped_projections(name, K, N):
+    _check_projection(K, N, (1, 16), 0.02, 40 + len(name))
+
+
+@pytest.mark.parametrize("name,K,N", LLAMA_70B)
+def test_llama_70b_shaped_projections(name, K, N):
+    _check_projection(K, N, (1, 32, 256), 0.015, 70 + len(name))
