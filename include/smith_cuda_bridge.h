@@ -157,7 +157,7 @@ int32_t smith_q8_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
 
 /* Direct, asynchronous C[M,N] = A[M,K] * dequant(B) on device-side buffers.
  * kind: 4 or 8.  path: 0 = choose by shape, 1 = any-shape CUDA-core kernel,
- * 2 = decode kernel (M <= 16, mma.sync), 3 = tensor-core (tcgen05) kernel,
+ * 2 = decode kernel (M <= 32, integer mma.sync), 3 = tensor-core (tcgen05) kernel,
  * 4 = GEMV kernel (M <= 4, dp4a).  A forced path that does not take the shape fails. */
 #define SMITH_PATH_AUTO 0
 #define SMITH_PATH_GENERIC 1

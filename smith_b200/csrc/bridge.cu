@@ -237,7 +237,7 @@ int do_qmatmul(Context* c, int kind, const float* A, const uint8_t* B, float* C,
       if (!qdecode_supports(kind, M, N, K, groups))
         return fail("decode kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,
                     (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
-      if (ensure_workspace(c, qdecode_workspace_bytes(kind, M, N, K))) return 1;
+      if (qdecode_workspace_bytes(kind, M, N, K) && ensure_workspace(c, qdecode_workspace_bytes(kind, M, N, K))) return 1;
       e = launch_qdecode(kind, A, B, C, M, N, K, groups, c->ws, c->stream);
       break;
     case kGemv:

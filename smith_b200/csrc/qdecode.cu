@@ -13,6 +13,11 @@
 // laid out [group][row][64 bytes] so that the digits of a pipeline stage are
 // one contiguous span that is bulk-copied next to the stage's weights.
 //
+// When all digits of the launch fit beside the weight ring (short K or few rows) the main
+// kernel does the conversion itself, into shared memory, and there is no separate kernel.
+// Rows are padded to 8 (M <= 8) or to a multiple of 16 with zero digits, so fragments never
+// need a row check.
+//
 // Main kernel: one CTA owns TN = 8 * NS adjacent columns and all of K.  A
 // consumer warp owns one 8-column slice and one K-phase (warp = phase * NS +
 // slice), keeps that slice's f32 accumulators in registers for the whole
@@ -23,7 +28,7 @@
 //   * A fragment: one 16-byte load of the digit words {hi, lo} x {first four,
 //     second four} codes in the same order.  With M <= 8 the MMA's rows 0-7
 //     carry the high digits and rows 8-15 the low digits of the same
-//     activation rows (one MMA per group); with 8 < M <= 16 two MMAs.
+//     activation rows (one MMA per group); wider M runs tiles of 16 rows, two MMAs each.
 //   * The s32 results are exact; dot = 128 * hi + lo is converted to f32 once
 //     and scaled:  acc += (scale * 2^-e) * (dot - zero * sum_k x_int)  (Q4),
 //     acc += (scale * 2^-e) * dot  (Q8).
@@ -50,7 +55,9 @@ struct Params {
   const uint8_t* xdig;     // [G][M][64] digit words
   const float2* xsc;       // [G][M] {2^-e, float(sum_k x_int)}
   float* C;
-  int M, N, K, G;
+  const float* A;          // activations, read directly when the digits are resident
+  int M, Mp, N, K, G;      // Mp: rows padded to 8 or a multiple of 16
+  int res_off;             // resident digits: byte offset in shared memory (0 = streamed from scratch)
   int NS, phases;          // slices per CTA (TN = 8 * NS), K-phases; consumer warps = NS * phases
   int row_pitch, stage_rows, w_bytes, d_bytes, s_bytes, stage_bytes, stages;
   int* status;
@@ -89,18 +96,12 @@ __device__ __forceinline__ uint4 lds_u32x4(uint32_t a) {
 //   Q4: word j*4 + {0,1,2,3} = {even-k hi, even-k lo, odd-k hi, odd-k lo} of k = 8j .. 8j+7
 //       (byte b of an even word is k = 8j + 2b) -- the order in which two masks pull the codes out of a word.
 //   Q8: word j*4 + {0,1,2,3} = {hi, lo of k = 8j .. 8j+3, hi, lo of k = 8j+4 .. 8j+7}.
+// One (group, padded row): 8 lanes (lane8 = 0..7), four consecutive k each.  Rows >= M get zero digits.
 template <int KIND>
-__global__ void __launch_bounds__(256) quantise_rows(const float* __restrict__ A, uint8_t* __restrict__ xdig,
-                                                     float2* __restrict__ xsc, int M, int K, int G) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // A may be the output of the launch before
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int lane8 = t & 7;
-  int pair = t >> 3;                       // (row, group), row-major like A's 32-element chunks
-  const bool live = pair < M * G;
-  if (!live) pair = M * G - 1;             // keep whole warps in the shuffles
-  const int m = pair / G, g = pair - m * G;
-  const float4 v4 = __ldg(reinterpret_cast<const float4*>(A + (size_t)m * K + (size_t)g * 32) + lane8);
+__device__ __forceinline__ void quantise_pair(const float* __restrict__ A, int M, int K, int g, int m, int lane8,
+                                              uint8_t* d, float2* sc_out) {
+  float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (m < M) v4 = __ldg(reinterpret_cast<const float4*>(A + (size_t)m * K + (size_t)g * 32) + lane8);
   const float v[4] = {v4.x, v4.y, v4.z, v4.w};
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
   int bad = 0;
@@ -125,8 +126,7 @@ __global__ void __launch_bounds__(256) quantise_rows(const float* __restrict__ A
   }
 #pragma unroll
   for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if (!live) return;
-  uint8_t* d = xdig + ((size_t)g * M + m) * 64;
+  if (d == nullptr) return;
   if (KIND == 4) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -144,14 +144,30 @@ __global__ void __launch_bounds__(256) quantise_rows(const float* __restrict__ A
     }
     reinterpret_cast<uint2*>(d)[lane8] = make_uint2(hi, lo);
   }
-  if (lane8 == 0) xsc[(size_t)g * M + m] = make_float2(down, (float)sum);
+  if (lane8 == 0) *sc_out = make_float2(down, (float)sum);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256) quantise_rows(const float* __restrict__ A, uint8_t* __restrict__ xdig,
+                                                     float2* __restrict__ xsc, int M, int Mp, int K, int G) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // A may be the output of the launch before
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  int pair = t >> 3;                       // (group, padded row)
+  const bool live = pair < Mp * G;
+  if (!live) pair = Mp * G - 1;            // keep whole warps in the shuffles
+  const int g = pair / Mp, m = pair - g * Mp;
+  quantise_pair<KIND>(A, M, K, g, m, t & 7, live ? xdig + (size_t)pair * 64 : nullptr, xsc + pair);
 }
 
 // ---------------------------------------------------------------- main kernel
-template <int KIND, bool WIDE>
+// NT = 0: M <= 8, one MMA per group (high digits in MMA rows 0-7, low digits in rows 8-15).
+// NT >= 1: NT tiles of 16 activation rows, two MMAs (high, low digits) per tile and group.
+template <int KIND, int NT>
 __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kernel(const Params p) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
-  constexpr int NACC = WIDE ? 4 : 2;
+  constexpr int NACC = (NT == 0) ? 2 : 4 * NT;
+  const bool resident = p.res_off != 0;
   extern __shared__ __align__(1024) uint8_t smem[];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -169,7 +185,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; s++) {
-      mbar_init(smem_u32(&full[s]), 2);            // weights armed first, digits once they exist
+      mbar_init(smem_u32(&full[s]), resident ? 1 : 2);   // weights armed first, streamed digits once they exist
       mbar_init(smem_u32(&empty[s]), nwarps);
     }
     *abort_flag = 0;
@@ -197,20 +213,22 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
       const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
       const uint32_t bar = smem_u32(&full[slot]);
       // bulk copies move multiples of 16 bytes: the scale span is rounded up (the scratch has slack)
-      const uint32_t db = (uint32_t)rows * p.M * 64, sb = (((uint32_t)rows * p.M * 8) + 15u) & ~15u;
+      const uint32_t db = (uint32_t)rows * p.Mp * 64, sb = (((uint32_t)rows * p.Mp * 8) + 15u) & ~15u;
       if (lane == 0) {
         mbar_expect_tx(bar, db + sb);
         uint8_t* base = ring + (size_t)slot * p.stage_bytes + p.w_bytes;
-        bulk_load_default(smem_u32(base), p.xdig + (size_t)st * p.stage_rows * p.M * 64, db, bar);
-        bulk_load_default(smem_u32(base + p.d_bytes), p.xsc + (size_t)st * p.stage_rows * p.M, sb, bar);
+        bulk_load_default(smem_u32(base), p.xdig + (size_t)st * p.stage_rows * p.Mp * 64, db, bar);
+        bulk_load_default(smem_u32(base + p.d_bytes), p.xsc + (size_t)st * p.stage_rows * p.Mp, sb, bar);
       }
       __syncwarp();
     };
     // weights of the first ring-full go out before anything waits on the previous launch
     const int first = min(nst, p.stages);
     for (int st = 0; st < first; st++) issue_weights(st);
-    asm volatile("griddepcontrol.wait;" ::: "memory");   // quantise_rows has finished: the digits exist
-    for (int st = 0; st < first; st++) issue_digits(st);
+    if (!resident) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");   // quantise_rows has finished: the digits exist
+      for (int st = 0; st < first; st++) issue_digits(st);
+    }
     bool live = true;
     for (int st = first; st < nst && live; st++) {
       const int slot = st % p.stages;
@@ -219,7 +237,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
       live = __shfl_sync(0xffffffffu, okw, 0) != 0;
       if (!live) break;
       issue_weights(st);
-      issue_digits(st);
+      if (!resident) issue_digits(st);
     }
     return;  // consumers observe every full barrier, so the copies land before the CTA ends
   }
@@ -228,7 +246,18 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
   const int slice = warp % p.NS, phase = warp / p.NS;
   const bool has_cols = slice * 8 < tn;
   const int r = lane >> 2, j = lane & 3;
-  const int m0 = min(r, p.M - 1), m1 = min(r + 8, p.M - 1);   // rows past M repeat the last one (never stored)
+  uint8_t* res_dig = smem + p.res_off;                                   // [G][Mp][64]
+  float2* res_sc = reinterpret_cast<float2*>(res_dig + (size_t)p.G * p.Mp * 64);  // [G][Mp]
+  if (resident) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations may belong to the launch before
+    const int pairs = p.G * p.Mp;
+    for (int i = tid; i < ((pairs * 8 + 31) & ~31); i += nwarps * 32) {
+      const int pair = min(i >> 3, pairs - 1);           // duplicates rewrite equal bytes; keeps warps whole
+      const int g = pair / p.Mp, m = pair - g * p.Mp;
+      quantise_pair<KIND>(p.A, p.M, p.K, g, m, i & 7, res_dig + (size_t)pair * 64, res_sc + pair);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+  }
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; i++) acc[i] = 0.f;
@@ -237,10 +266,11 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
   const uint32_t off_w = (uint32_t)(slice * 8 + r) * BB + (KIND == 4 ? 4u * j : 2u + 8u * j);
   const uint32_t sh8 = (off_w & 3u) * 8;
   const uint32_t off_q = (uint32_t)(slice * 8 + 2 * j) * BB + (KIND == 4 ? 16u : 0u);   // scale (and zero)
-  const uint32_t off_d0 = (uint32_t)m0 * 64 + 16u * j, off_d1 = (uint32_t)m1 * 64 + 16u * j;
-  const uint32_t off_x0 = (uint32_t)m0 * 8, off_x1 = (uint32_t)m1 * 8;
+  const uint32_t off_d = (uint32_t)r * 64 + 16u * j;   // digit words of row r of a tile (+512 for row r + 8)
+  const uint32_t off_x = (uint32_t)r * 8;              // its {2^-e, sum} pair (+64 for row r + 8)
   const uint32_t w_step = (uint32_t)p.phases * (uint32_t)p.row_pitch;
-  const uint32_t d_step = (uint32_t)p.phases * (uint32_t)(p.M * 64), s_step = (uint32_t)p.phases * (uint32_t)(p.M * 8);
+  const uint32_t d_step = (uint32_t)p.phases * (uint32_t)(p.Mp * 64), s_step = (uint32_t)p.phases * (uint32_t)(p.Mp * 8);
+  const uint32_t res_dig_s = smem_u32(res_dig), res_sc_s = smem_u32(res_sc);
 
   bool ok = true;
   for (int st = 0; st < nst && ok; st++) {
@@ -251,8 +281,11 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
       const uint32_t stage = ring_s + (uint32_t)slot * (uint32_t)p.stage_bytes;
       const int rows_here = min(p.stage_rows, p.G - st * p.stage_rows);
       uint32_t wrow = stage + (uint32_t)phase * (uint32_t)p.row_pitch;
-      uint32_t drow = stage + (uint32_t)p.w_bytes + (uint32_t)phase * (uint32_t)(p.M * 64);
-      uint32_t srow = stage + (uint32_t)(p.w_bytes + p.d_bytes) + (uint32_t)phase * (uint32_t)(p.M * 8);
+      const uint32_t first_row = (uint32_t)(st * p.stage_rows + phase);   // group index of this phase's first row
+      uint32_t drow = resident ? res_dig_s + first_row * (uint32_t)(p.Mp * 64)
+                               : stage + (uint32_t)p.w_bytes + (uint32_t)phase * (uint32_t)(p.Mp * 64);
+      uint32_t srow = resident ? res_sc_s + first_row * (uint32_t)(p.Mp * 8)
+                               : stage + (uint32_t)(p.w_bytes + p.d_bytes) + (uint32_t)phase * (uint32_t)(p.Mp * 8);
 #pragma unroll 4
       for (int row = phase; row < rows_here; row += p.phases) {   // this phase's group-rows inside the stage
         // ---- B fragment: the j-th eight codes of column slice*8 + r
@@ -275,11 +308,11 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
           sc0 = __half2float(__ushort_as_half((unsigned short)lds_u16(wrow + off_q)));
           sc1 = __half2float(__ushort_as_half((unsigned short)lds_u16(wrow + off_q + BB)));
         }
-        // ---- A fragment(s): digit words of activation row r (and r + 8)
-        const uint4 d0 = lds_u32x4(drow + off_d0);
-        const float2 x0 = lds_f32x2(srow + off_x0);
-        if (!WIDE) {
+        // ---- A fragment(s) and the scaled accumulation
+        if (NT == 0) {
           // rows 0-7: high digits, rows 8-15: low digits of the same activation rows
+          const uint4 d0 = lds_u32x4(drow + off_d);
+          const float2 x0 = lds_f32x2(srow + off_x);
           const uint32_t a4[4] = {d0.x, d0.y, d0.z, d0.w};
           int c[4] = {0, 0, 0, 0};
           imma(c, a4, b0, b1);
@@ -292,25 +325,31 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
             acc[1] = fmaf(sc1 * x0.x, f1, acc[1]);
           }
         } else {
-          const uint4 d1 = lds_u32x4(drow + off_d1);
-          const float2 x1 = lds_f32x2(srow + off_x1);
-          const uint32_t ah[4] = {d0.x, d1.x, d0.z, d1.z};   // high digits of rows r, r + 8
-          const uint32_t al4[4] = {d0.y, d1.y, d0.w, d1.w};  // low digits
-          int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
-          imma(ch, ah, b0, b1);
-          imma(cl, al4, b0, b1);
-          const float f00 = (float)(ch[0] * 128 + cl[0]), f01 = (float)(ch[1] * 128 + cl[1]);
-          const float f10 = (float)(ch[2] * 128 + cl[2]), f11 = (float)(ch[3] * 128 + cl[3]);
-          if (KIND == 4) {
-            acc[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f00), acc[0]);
-            acc[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f01), acc[1]);
-            acc[2] = fmaf(sc0 * x1.x, fmaf(-z0, x1.y, f10), acc[2]);
-            acc[3] = fmaf(sc1 * x1.x, fmaf(-z1, x1.y, f11), acc[3]);
-          } else {
-            acc[0] = fmaf(sc0 * x0.x, f00, acc[0]);
-            acc[1] = fmaf(sc1 * x0.x, f01, acc[1]);
-            acc[2] = fmaf(sc0 * x1.x, f10, acc[2]);
-            acc[3] = fmaf(sc1 * x1.x, f11, acc[3]);
+#pragma unroll
+          for (int t = 0; t < (NT == 0 ? 1 : NT); t++) {
+            const uint4 d0 = lds_u32x4(drow + off_d + (uint32_t)t * 1024u);
+            const uint4 d1 = lds_u32x4(drow + off_d + (uint32_t)t * 1024u + 512u);
+            const float2 x0 = lds_f32x2(srow + off_x + (uint32_t)t * 128u);
+            const float2 x1 = lds_f32x2(srow + off_x + (uint32_t)t * 128u + 64u);
+            const uint32_t ah[4] = {d0.x, d1.x, d0.z, d1.z};   // high digits of rows r, r + 8 of the tile
+            const uint32_t al4[4] = {d0.y, d1.y, d0.w, d1.w};  // low digits
+            int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+            imma(ch, ah, b0, b1);
+            imma(cl, al4, b0, b1);
+            const float f00 = (float)(ch[0] * 128 + cl[0]), f01 = (float)(ch[1] * 128 + cl[1]);
+            const float f10 = (float)(ch[2] * 128 + cl[2]), f11 = (float)(ch[3] * 128 + cl[3]);
+            float* a = acc + 4 * t;
+            if (KIND == 4) {
+              a[0] = fmaf(sc0 * x0.x, fmaf(-z0, x0.y, f00), a[0]);
+              a[1] = fmaf(sc1 * x0.x, fmaf(-z1, x0.y, f01), a[1]);
+              a[2] = fmaf(sc0 * x1.x, fmaf(-z0, x1.y, f10), a[2]);
+              a[3] = fmaf(sc1 * x1.x, fmaf(-z1, x1.y, f11), a[3]);
+            } else {
+              a[0] = fmaf(sc0 * x0.x, f00, a[0]);
+              a[1] = fmaf(sc1 * x0.x, f01, a[1]);
+              a[2] = fmaf(sc0 * x1.x, f10, a[2]);
+              a[3] = fmaf(sc1 * x1.x, f11, a[3]);
+            }
           }
         }
         wrow += w_step, drow += d_step, srow += s_step;
@@ -322,12 +361,18 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
 
   // ---------------------------------------------- sum the phases, fixed order
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every consumer is done with the ring
-  constexpr int ROWS = WIDE ? 16 : 8;
+  constexpr int ROWS = (NT == 0) ? 8 : 16 * NT;
   float* red = reinterpret_cast<float*>(ring);        // [phases][ROWS][TN]
-  {
+  if (NT == 0) {
     float* dst = red + ((size_t)phase * ROWS + r) * TN + slice * 8 + 2 * j;
     *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
-    if (WIDE) *reinterpret_cast<float2*>(dst + 8 * TN) = make_float2(acc[2], acc[3]);
+  } else {
+#pragma unroll
+    for (int t = 0; t < (NT == 0 ? 1 : NT); t++) {
+      float* dst = red + ((size_t)phase * ROWS + 16 * t + r) * TN + slice * 8 + 2 * j;
+      *reinterpret_cast<float2*>(dst) = make_float2(acc[4 * t], acc[4 * t + 1]);
+      *reinterpret_cast<float2*>(dst + 8 * TN) = make_float2(acc[4 * t + 2], acc[4 * t + 3]);
+    }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
   if (*abort_flag) return;
@@ -341,10 +386,12 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
 
 struct Plan {
   Params p;
-  int tiles;
+  int tiles, NT;
   size_t smem;
   bool ok;
 };
+
+constexpr int kMaxRows = 32;   // rows beyond this go to the tensor-core kernel
 
 Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
@@ -352,11 +399,13 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   Plan pl{};
   Params& p = pl.p;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)(K / 32);
+  pl.NT = (M <= 8) ? 0 : (int)((M + 15) / 16);
+  p.Mp = (M <= 8) ? 8 : 16 * pl.NT;
   // Slices per CTA: the fewest that cover N in a whole number of waves, at most 16 (128 columns).
   int NS = 0;
   for (int64_t waves = 1;; waves++) {
     NS = (int)((N + 8 * sms * waves - 1) / (8 * sms * waves));
-    if (NS <= 16) break;   // at most 128 columns per CTA
+    if (NS <= 16) break;
   }
   p.NS = NS;
   const int TN = NS * 8;
@@ -366,18 +415,27 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   while (phases > 1 && phases * 4 > p.G) phases--;   // short K: do not over-split
   p.phases = phases;
   p.row_pitch = TN * BB;
-  p.stage_rows = phases * ((kStageRows + phases - 1) / phases);
+  // Digits resident in shared memory (converted by the kernel itself) only for short reductions, where a
+  // second launch would cost more than every CTA redoing the conversion; measured at K = 4096, M = 8 the
+  // streamed form is faster (17.4 us against 21.8 us).
+  const size_t res_bytes = (size_t)p.G * p.Mp * 72;
+  const bool resident = res_bytes <= 24 * 1024;
+  const int target_rows = (p.Mp >= 32 && !resident) ? 8 : kStageRows;
+  p.stage_rows = phases * ((target_rows + phases - 1) / phases);
   p.w_bytes = ((p.stage_rows * p.row_pitch + 16 + 127) / 128) * 128;   // + slack for the Q8 read-ahead
-  p.d_bytes = p.stage_rows * p.M * 64;
-  p.s_bytes = ((p.stage_rows * p.M * 8 + 127) / 128) * 128;
+  p.d_bytes = resident ? 0 : p.stage_rows * p.Mp * 64;
+  p.s_bytes = resident ? 0 : ((p.stage_rows * p.Mp * 8 + 127) / 128) * 128;
   p.stage_bytes = ((p.w_bytes + p.d_bytes + p.s_bytes + 1023) / 1024) * 1024;
-  int stages = (kSmemBudget - 1024) / p.stage_bytes;
+  const int res_room = resident ? (int)((res_bytes + 1023) / 1024) * 1024 : 0;
+  int stages = (kSmemBudget + 20 * 1024 - 1024 - res_room) / p.stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   p.stages = stages;
-  const size_t red = (size_t)phases * (M > 8 ? 16 : 8) * TN * 4;
+  const size_t red = (size_t)phases * (size_t)p.Mp * TN * 4;
   const size_t ring = (size_t)(stages > 0 ? stages : 0) * p.stage_bytes;
-  pl.smem = 1024 + (ring > red ? ring : red);
-  pl.ok = stages >= 2 && pl.smem <= 227 * 1024;
+  const size_t ring_room = (((ring > red ? ring : red) + 1023) / 1024) * 1024;
+  p.res_off = resident ? (int)(1024 + ring_room) : 0;
+  pl.smem = 1024 + ring_room + res_room;
+  pl.ok = stages >= 2 && pl.smem <= 227 * 1024 && M <= kMaxRows;
   return pl;
 }
 
@@ -393,17 +451,17 @@ cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t sm
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int KIND, bool WIDE>
+template <int KIND, int NT>
 cudaError_t launch_main(const Plan& pl, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(qdecode_kernel<KIND, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(qdecode_kernel<KIND, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int threads = (pl.p.NS * pl.p.phases + 1) * 32;
-  const cudaError_t e = launch_pdl(qdecode_kernel<KIND, WIDE>, dim3((unsigned)pl.tiles), dim3((unsigned)threads),
+  const cudaError_t e = launch_pdl(qdecode_kernel<KIND, NT>, dim3((unsigned)pl.tiles), dim3((unsigned)threads),
                                    pl.smem, s, pl.p);
   count_launch();
   return e;
@@ -413,7 +471,7 @@ cudaError_t launch_main(const Plan& pl, cudaStream_t s) {
 
 bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups) {
   if (kind != 4 && kind != 8) return false;
-  if (M < 1 || M > 16) return false;
+  if (M < 1 || M > kMaxRows) return false;
   if (N < 8 || (N % 8) != 0) return false;       // 16-byte alignment of every group-row span
   if (K < 32 || (K % 32) != 0 || groups != K / 32) return false;
   if (N > (1 << 30) || K > (1 << 22)) return false;
@@ -421,39 +479,45 @@ bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups)
 }
 
 size_t qdecode_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
-  (void)kind;
-  (void)N;
-  const size_t G = (size_t)(K / 32);
-  return ((G * (size_t)M * 64 + 255) & ~size_t(255)) + G * (size_t)M * 8 + 64;
+  const Plan pl = make_plan(kind, M, N, K);
+  if (pl.p.res_off != 0) return 0;               // digits live in shared memory
+  const size_t G = (size_t)(K / 32), Mp = (size_t)pl.p.Mp;
+  return ((G * Mp * 64 + 255) & ~size_t(255)) + G * Mp * 8 + 64;
 }
 
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
                            int64_t groups, Workspace ws, cudaStream_t s) {
   (void)groups;
-  if (!ws.ptr || ws.bytes < qdecode_workspace_bytes(kind, M, N, K)) return cudaErrorInvalidValue;
-  if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15) ||
-      (reinterpret_cast<uintptr_t>(ws.ptr) & 255))
-    return cudaErrorMisalignedAddress;
   Plan pl = make_plan(kind, M, N, K);
   if (!pl.ok) return cudaErrorInvalidValue;
-  const size_t G = (size_t)(K / 32);
-  uint8_t* xdig = static_cast<uint8_t*>(ws.ptr);
-  float2* xsc = reinterpret_cast<float2*>(xdig + ((G * (size_t)M * 64 + 255) & ~size_t(255)));
-  const int qthreads = (int)(M * G * 8);
-  cudaError_t e;
-  if (kind == 4)
-    e = launch_pdl(quantise_rows<4>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig, xsc,
-                   (int)M, (int)K, (int)G);
-  else
-    e = launch_pdl(quantise_rows<8>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig, xsc,
-                   (int)M, (int)K, (int)G);
-  count_launch();
-  if (e != cudaSuccess) return e;
-  pl.p.B = B, pl.p.C = C, pl.p.xdig = xdig, pl.p.xsc = xsc;
+  if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15)) return cudaErrorMisalignedAddress;
+  pl.p.A = A, pl.p.B = B, pl.p.C = C, pl.p.xdig = nullptr, pl.p.xsc = nullptr;
+  if (pl.p.res_off == 0) {
+    const size_t need = qdecode_workspace_bytes(kind, M, N, K);
+    if (!ws.ptr || ws.bytes < need || (reinterpret_cast<uintptr_t>(ws.ptr) & 255)) return cudaErrorInvalidValue;
+    const size_t G = (size_t)(K / 32), Mp = (size_t)pl.p.Mp;
+    uint8_t* xdig = static_cast<uint8_t*>(ws.ptr);
+    float2* xsc = reinterpret_cast<float2*>(xdig + ((G * Mp * 64 + 255) & ~size_t(255)));
+    const int qthreads = (int)(Mp * G * 8);
+    cudaError_t e;
+    if (kind == 4)
+      e = launch_pdl(quantise_rows<4>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig,
+                     xsc, (int)M, (int)Mp, (int)K, (int)G);
+    else
+      e = launch_pdl(quantise_rows<8>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig,
+                     xsc, (int)M, (int)Mp, (int)K, (int)G);
+    count_launch();
+    if (e != cudaSuccess) return e;
+    pl.p.xdig = xdig, pl.p.xsc = xsc;
+  }
   pl.p.status = kernel_status_ptr();
   if (!pl.p.status) return cudaErrorUnknown;
-  if (kind == 4) return (M > 8) ? launch_main<4, true>(pl, s) : launch_main<4, false>(pl, s);
-  return (M > 8) ? launch_main<8, true>(pl, s) : launch_main<8, false>(pl, s);
+#define SMITH_DECODE_CASE(KD, NTV) \
+  if (kind == KD && pl.NT == NTV) return launch_main<KD, NTV>(pl, s);
+  SMITH_DECODE_CASE(4, 0) SMITH_DECODE_CASE(4, 1) SMITH_DECODE_CASE(4, 2)
+  SMITH_DECODE_CASE(8, 0) SMITH_DECODE_CASE(8, 1) SMITH_DECODE_CASE(8, 2)
+#undef SMITH_DECODE_CASE
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace smith

@@ -108,7 +108,7 @@ def test_matmul_auto_path_within_tolerance(kind, M, K, N):
 def test_matmul_each_path_where_supported(kind, path):
     shapes = {device.PATH_GENERIC: [(1, 64, 32), (9, 1000, 77)],
               device.PATH_DECODE: [(1, 4096, 1024), (5, 1024, 256), (16, 2048, 640), (8, 4096, 104), (7, 4128, 136), (13, 96, 8),
-                                   (9, 14336, 256)],
+                                   (9, 14336, 256), (24, 4096, 512), (32, 1024, 264), (20, 2048, 96), (17, 8192, 128)],
               device.PATH_GEMV: [(1, 4096, 1024), (2, 1024, 256), (4, 2048, 640), (3, 4096, 104), (1, 14336, 512),
                                  (1, 64, 8), (2, 28672, 64)],
               device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384), (300, 1056, 72)]}[path]
