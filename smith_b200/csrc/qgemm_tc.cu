@@ -15,11 +15,14 @@
 //     warp 0     producer: per 64-wide k-block, TMA-loads the MT activation
 //                tiles (128 x 64, 128-byte swizzle) and bulk-copies the two
 //                packed group-rows of the tile's BN columns into a stage.
-//     warp 1     allocates tensor memory and issues the MMAs: per k-block and
-//                row tile four tcgen05.mma (128 x BN x 16), A and B from
-//                shared memory through K-major 128-byte-swizzle descriptors,
-//                D = f32 in TMEM; tcgen05.commit releases the stage.
-//     warps 2-17 dequantise: each thread takes half of a (column, group) block
+//     warps 1-2  MMA issuers, one per row tile (warp 1 also allocates tensor
+//                memory): per k-block four tcgen05.mma (128 x BN x 16), A and B
+//                from shared memory through K-major 128-byte-swizzle
+//                descriptors, D = f32 in TMEM; tcgen05.commit releases the stage.
+//     warps 3-30 dequantise, in `groups` teams that own alternate k-blocks (team =
+//                warp % groups works on k-blocks team, team + groups, ...), so that
+//                a team has several k-block periods for its latency-bound work
+//                and its barrier round trip: each thread takes half of a (column, group) block
 //                of the stage (16 weights), forms scale * (code - zero) (Q4,
 //                packed bf16: exact code - round(zero), then one fused
 //                multiply-add with the scale and the zero point's fraction) or
@@ -30,7 +33,7 @@
 //                nibbles pair up in a 32-bit word); convert_activations stores
 //                the activations' k in the same order, so the dot products
 //                are unchanged and no byte shuffles are needed.
-//     warps 2-5  epilogue: tcgen05.ld their 32-lane quarter of each
+//     warps 3-6  epilogue: tcgen05.ld their 32-lane quarter of each
 //                accumulator, 32 columns at a time, and store C rows.
 //   Weights of a tile are dequantised once and feed MT row tiles, so for
 //   M >= 256 the CUDA-core dequantisation stays below the tensor time.
@@ -50,8 +53,9 @@ namespace {
 
 constexpr int kBM = 128;            // rows per MMA / per accumulator
 constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of 16-bit values
-constexpr int kDequantWarps = 16;
-constexpr int kThreads = (2 + kDequantWarps) * 32;
+constexpr int kDequantWarps = 28;
+constexpr int kFirstDequantWarp = 3;   // warp 0: producer, warps 1-2: MMA issuers (one per row tile)
+constexpr int kThreads = (kFirstDequantWarp + kDequantWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 224 * 1024;
 
@@ -62,6 +66,7 @@ struct Params {
   int M, N, K, G;
   int BN;                 // columns per CTA, multiple of 16, <= 256
   int stages;
+  int groups;             // dequant teams (1, 2 or 4); team size = kDequantWarps / groups
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;  // per-stage layout
   int tmem_cols;
   int* status;
@@ -286,10 +291,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < p.stages; s++) {
       mbar_init(smem_u32(&full_in[s]), 1);
-      mbar_init(smem_u32(&b_ready[s]), kDequantWarps);
-      mbar_init(smem_u32(&empty[s]), 1);
+      mbar_init(smem_u32(&b_ready[s]), kDequantWarps / p.groups);   // the team that owns the stage's k-block
+      mbar_init(smem_u32(&empty[s]), MT);                             // one commit per MMA issuer
     }
-    mbar_init(smem_u32(acc_ready), 1);
+    mbar_init(smem_u32(acc_ready), MT);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -304,68 +309,84 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
+    // Loops of the single-thread roles carry the stage index and parity along: an integer
+    // division by the (run-time) ring depth costs a lone thread hundreds of cycles per k-block.
     if (lane == 0) {
+      int s = 0;
+      uint32_t par = 0;                       // parity of this pass over the ring
+      const uint8_t* bsrc = p.B + (size_t)col0 * BB;
+      const size_t brow = (size_t)p.N * BB;
+      const uint32_t a_tx = (uint32_t)(MT * kBM * kBK * 2), b_tx = (uint32_t)tn * BB;
+      uint32_t st = smem_u32(stages);
       for (int kb = 0; kb < nkb; kb++) {
-        const int s = kb % p.stages;
         if (kb >= p.stages) {
-          if (!mbar_wait(smem_u32(&empty[s]), ((kb / p.stages) - 1) & 1, abort_flag, p.status)) break;
+          if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status)) break;
         }
-        uint8_t* st = stages + (size_t)s * p.stage_bytes;
         const uint32_t bar = smem_u32(&full_in[s]);
-        const int g0 = kb * 2;
-        const int ngr = min(2, p.G - g0);
-        mbar_expect_tx(bar, (uint32_t)(MT * kBM * kBK * 2) + (uint32_t)ngr * (uint32_t)tn * BB);
+        const int ngr = min(2, p.G - kb * 2);
+        mbar_expect_tx(bar, a_tx + (uint32_t)ngr * b_tx);
 #pragma unroll
-        for (int t = 0; t < MT; t++)
-          tma_load_2d(smem_u32(st + t * (kBM * kBK * 2)), &tmap_a, kb * kBK, row0 + t * kBM, bar);
+        for (int t = 0; t < MT; t++) tma_load_2d(st + t * (kBM * kBK * 2), &tmap_a, kb * kBK, row0 + t * kBM, bar);
         for (int gl = 0; gl < ngr; gl++)
-          bulk_load_plain(smem_u32(st + p.a_bytes + gl * p.pk_pitch),
-                          p.B + ((size_t)(g0 + gl) * p.N + col0) * BB, (uint32_t)tn * BB, bar);
+          bulk_load_plain(st + p.a_bytes + gl * p.pk_pitch, bsrc + gl * brow, b_tx, bar);
+        bsrc += 2 * brow;
+        st += p.stage_bytes;
+        if (++s == p.stages) s = 0, par ^= 1u, st = smem_u32(stages);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp < kFirstDequantWarp) {
+    // ------------------------------------------------------------ MMA issuers (warp 1: row tile 0, warp 2: row tile 1)
+    const int t = warp - 1;
+    if (lane == 0 && t < MT) {
       const uint32_t idesc = instr_desc(KIND == 4 ? 1 : 0, p.BN);
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; kb++) {
-        const int s = kb % p.stages;
-        const uint32_t par = (kb / p.stages) & 1;
+      int s = 0;
+      uint32_t par = 0;
+      // descriptors differ between stages and k-steps only in the start-address field
+      // (bytes >> 4, the low 14 bits): add, do not rebuild
+      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(stages + t * (kBM * kBK * 2)));
+      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(stages + p.a_bytes + p.pk_bytes));
+      const uint32_t stage_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t d_tmem = tmem_base + (uint32_t)(t * p.BN);
+      uint32_t soff = 0;
+      for (int kb = 0; kb < nkb; kb++) {
         // b_ready implies full_in: the dequant warps waited on it (TMA tiles included) before arriving
         ok = mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        uint8_t* st = stages + (size_t)s * p.stage_bytes;
-        const uint32_t a_addr = smem_u32(st);
-        const uint32_t b_addr = smem_u32(st + p.a_bytes + p.pk_bytes);
+        const uint64_t a_desc = a_desc0 + soff, b_desc = b_desc0 + soff;
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-#pragma unroll
-          for (int j = 0; j < kBK / 16; j++) {
-            // 16 k = 32 bytes further along the swizzled 128-byte row
-            const uint64_t ad = smem_desc_sw128(a_addr + t * (kBM * kBK * 2) + j * 32);
-            const uint64_t bd = smem_desc_sw128(b_addr + j * 32);
-            umma_f16(tmem_base + (uint32_t)(t * p.BN), ad, bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          }
+        for (int j = 0; j < kBK / 16; j++) {
+          // 16 k = 32 bytes further along the swizzled 128-byte row
+          umma_f16(d_tmem, a_desc + (uint64_t)((j * 32) >> 4), b_desc + (uint64_t)((j * 32) >> 4), idesc,
+                   (kb > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(smem_u32(&empty[s]));
+        soff += stage_step;
+        if (++s == p.stages) s = 0, par ^= 1u, soff = 0;
       }
       if (ok) umma_commit(smem_u32(acc_ready));
     }
   } else {
     // ------------------------------------------------------------ dequantise
-    const int dt = tid - 64;  // 0 .. kDequantWarps * 32 - 1
+    const int dw = warp - kFirstDequantWarp;            // 0 .. kDequantWarps - 1
+    const int team = dw % p.groups;                      // this warp's team
+    const int team_threads = (kDequantWarps / p.groups) * 32;
+    const int dt = (dw / p.groups) * 32 + lane;          // thread index inside the team
     bool ok = true;
-    for (int kb = 0; kb < nkb && ok; kb++) {
-      const int s = kb % p.stages;
-      ok = mbar_wait(smem_u32(&full_in[s]), (kb / p.stages) & 1, abort_flag, p.status);
+    int s = team;                                        // groups < stages
+    uint32_t par = 0;
+    const int bn2 = 2 * p.BN, bn3 = 3 * p.BN, items = 4 * p.BN;
+    for (int kb = team; kb < nkb; kb += p.groups) {
+      ok = mbar_wait(smem_u32(&full_in[s]), par, abort_flag, p.status);
       if (!ok) break;
       uint8_t* st = stages + (size_t)s * p.stage_bytes;
       const uint8_t* pk = st + p.a_bytes;
       uint8_t* bt = st + p.a_bytes + p.pk_bytes;
       const int g0 = kb * 2;
-      for (int it = dt; it < 4 * p.BN; it += kDequantWarps * 32) {
-        const int part = it / p.BN, col = it - part * p.BN;   // part = 2 * group + half
+      for (int it = dt; it < items; it += team_threads) {
+        const int part = (it >= p.BN) + (it >= bn2) + (it >= bn3);   // part = 2 * group + half
+        const int col = it - part * p.BN;
         const int gl = part >> 1;
         const bool zero = (col >= tn) || (g0 + gl >= p.G);
         dequant_half<KIND>(pk, (uint32_t)(gl * p.pk_pitch + col * BB), bt, col, gl, part & 1, zero);
@@ -373,9 +394,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       fence_async_smem();       // make the generic-proxy stores visible to the tensor core's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&b_ready[s]));
+      s += p.groups;
+      if (s >= p.stages) s -= p.stages, par ^= 1u;
     }
-    // ---------------------------------------------------------- epilogue (warps 2..5)
-    if (warp < 6) {
+    // ---------------------------------------------------------- epilogue (first four dequant warps)
+    if (warp < kFirstDequantWarp + 4) {
       const bool got = ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status);
       tc_fence_after();
       if (got) {
@@ -437,7 +460,7 @@ EncodeTiledFn encode_fn() {
 }
 
 struct Plan {
-  int MT, BN, stages, tmem_cols;
+  int MT, BN, stages, tmem_cols, groups;
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;
   size_t smem;
   dim3 grid;
@@ -470,6 +493,8 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
   pl.stage_bytes = pl.a_bytes + pl.pk_bytes + pl.b_bytes;        // every part a multiple of 1024
   pl.stages = (kSmemBudget - 1024) / pl.stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
+  // dequant teams: as many k-blocks in flight as the ring allows beside the one being multiplied
+  pl.groups = pl.stages >= 5 ? 4 : (pl.stages >= 3 ? 2 : 1);
   int cols = 32;
   while (cols < pl.MT * pl.BN) cols <<= 1;
   pl.tmem_cols = cols;
@@ -548,7 +573,7 @@ cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C
   Params p{};
   p.B = B, p.C = C, p.row_inv = (kind == 8) ? row_inv : nullptr;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
-  p.BN = pl.BN, p.stages = pl.stages;
+  p.BN = pl.BN, p.stages = pl.stages, p.groups = pl.groups;
   p.a_bytes = pl.a_bytes, p.pk_pitch = pl.pk_pitch, p.pk_bytes = pl.pk_bytes, p.b_bytes = pl.b_bytes;
   p.stage_bytes = pl.stage_bytes, p.tmem_cols = pl.tmem_cols;
   p.status = kernel_status_ptr();
