@@ -11,19 +11,22 @@
 //     f16 number by format, so scale * code is formed exactly in f16 -- with
 //     each activation row pre-multiplied by a power of two that moves its
 //     largest magnitude into [2^13, 2^14); the inverse is applied in the epilogue.
-//  2. qgemm_tc_kernel: one CTA computes MT x 128 rows by BN columns.
-//     warp 0     producer: per 64-wide k-block, TMA-loads the MT activation
-//                tiles (128 x 64, 128-byte swizzle) and bulk-copies the two
-//                packed group-rows of the tile's BN columns into a stage.
+//  2. qgemm_tc_kernel: one CTA computes MT x 128 rows by BN columns, 64 k at a
+//     time, through two shared-memory rings: a deep one of packed group-rows
+//     (a few KB per k-block, loaded from HBM far ahead) and a shallow one of
+//     {activation tile, dequantised B tile} slots.
+//     warp 0     activation producer: lane t TMA-loads row tile t's 128 x 64
+//                tile (128-byte swizzle) of each k-block into a tile slot.
 //     warps 1-2  MMA issuers, one per row tile (warp 1 also allocates tensor
 //                memory): per k-block four tcgen05.mma (128 x BN x 16), A and B
 //                from shared memory through K-major 128-byte-swizzle
-//                descriptors, D = f32 in TMEM; tcgen05.commit releases the stage.
-//     warps 3-30 dequantise, in `groups` teams that own alternate k-blocks (team =
-//                warp % groups works on k-blocks team, team + groups, ...), so that
-//                a team has several k-block periods for its latency-bound work
-//                and its barrier round trip: each thread takes half of a (column, group) block
-//                of the stage (16 weights), forms scale * (code - zero) (Q4,
+//                descriptors, D = f32 in TMEM; tcgen05.commit frees the slot.
+//     warp 3     weight producer: lanes 0-1 bulk-copy the k-block's two packed
+//                group-rows of the tile's BN columns into a packed-ring slot.
+//     warps 4-31 dequantise, in `groups` teams that own alternate k-blocks (team =
+//                warp % groups works on k-blocks team, team + groups, ...): each
+//                thread takes half of a (column, group) block (16 weights),
+//                forms scale * (code - zero) (Q4,
 //                packed bf16: exact code - round(zero), then one fused
 //                multiply-add with the scale and the zero point's fraction) or
 //                code * scale (Q8, packed f16, exact product of two f16-exact
@@ -33,7 +36,7 @@
 //                nibbles pair up in a 32-bit word); convert_activations stores
 //                the activations' k in the same order, so the dot products
 //                are unchanged and no byte shuffles are needed.
-//     warps 3-6  epilogue: tcgen05.ld their 32-lane quarter of each
+//     warps 4-7  epilogue: tcgen05.ld their 32-lane quarter of each
 //                accumulator, 32 columns at a time, and store C rows.
 //   Weights of a tile are dequantised once and feed MT row tiles, so for
 //   M >= 256 the CUDA-core dequantisation stays below the tensor time.
@@ -54,7 +57,8 @@ namespace {
 constexpr int kBM = 128;            // rows per MMA / per accumulator
 constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of 16-bit values
 constexpr int kDequantWarps = 28;
-constexpr int kFirstDequantWarp = 3;   // warp 0: producer, warps 1-2: MMA issuers (one per row tile)
+constexpr int kWeightProducerWarp = 3;
+constexpr int kFirstDequantWarp = 4;   // warp 0: activation producer, 1-2: MMA issuers (one per row tile), 3: weight producer
 constexpr int kThreads = (kFirstDequantWarp + kDequantWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 224 * 1024;
@@ -65,9 +69,10 @@ struct Params {
   const float* row_inv;   // Q8: per-row inverse prescale, else nullptr
   int M, N, K, G;
   int BN;                 // columns per CTA, multiple of 16, <= 256
-  int stages;
+  int stages;             // tile ring depth
+  int pk_stages;          // packed ring depth
   int groups;             // dequant teams (1, 2 or 4); team size = kDequantWarps / groups
-  int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;  // per-stage layout
+  int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;  // stage_bytes = a_bytes + b_bytes: one tile slot
   int tmem_cols;
   int* status;
 };
@@ -267,19 +272,28 @@ __device__ __forceinline__ void dequant_half(const uint8_t* __restrict__ pk, uin
 }
 
 // ---------------------------------------------------------------- main kernel
+// Two rings in shared memory, so that each resource is only as deep as its latency needs:
+//   packed ring   `pk_stages` slots of two packed group-rows (the k-block's weights as they lie in
+//                 HBM, a few KB): deep, because these loads come from HBM;
+//   tile ring     `stages` slots of {activation tile (TMA), dequantised B tile}: the large ones.
+// A k-block's critical cycle is then  B slot free -> dequantise -> MMAs -> B slot free ;
+// the weight loads run far ahead of it and the activation load overlaps the dequantisation.
 template <int KIND, int MT>
 __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                const Params p) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   extern __shared__ __align__(1024) uint8_t smem[];
   // header (first 1024 bytes): barriers, TMEM base, abort flag
-  uint64_t* full_in = reinterpret_cast<uint64_t*>(smem);          // [kMaxStages] TMA landed
-  uint64_t* b_ready = full_in + kMaxStages;                        // [kMaxStages] B tile written
-  uint64_t* empty = b_ready + kMaxStages;                          // [kMaxStages] MMAs of the stage done
+  uint64_t* pk_full = reinterpret_cast<uint64_t*>(smem);          // [kMaxStages] packed group-rows landed
+  uint64_t* pk_empty = pk_full + kMaxStages;                       // [kMaxStages] ... and read by their team
+  uint64_t* a_full = pk_empty + kMaxStages;                        // [kMaxStages] activation tile landed
+  uint64_t* b_ready = a_full + kMaxStages;                         // [kMaxStages] B tile written
+  uint64_t* empty = b_ready + kMaxStages;                          // [kMaxStages] MMAs of the tile slot done
   uint64_t* acc_ready = empty + kMaxStages;                        // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  uint8_t* stages = smem + 1024;
+  uint8_t* tiles = smem + 1024;                                    // [stages][a_bytes + b_bytes]
+  uint8_t* packed = tiles + (size_t)p.stages * p.stage_bytes;      // [pk_stages][pk_bytes]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // row tiles vary fastest, so the CTAs that share a weight tile run at the same time
@@ -287,12 +301,15 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   const int row0 = blockIdx.x * (MT * kBM);
   const int tn = min(p.BN, p.N - col0);
   const int nkb = (p.K + kBK - 1) / kBK;
+  const int team_warps = kDequantWarps / p.groups;
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; s++) {
-      mbar_init(smem_u32(&full_in[s]), 1);
-      mbar_init(smem_u32(&b_ready[s]), kDequantWarps / p.groups);   // the team that owns the stage's k-block
-      mbar_init(smem_u32(&empty[s]), MT);                             // one commit per MMA issuer
+    for (int s = 0; s < kMaxStages; s++) {
+      mbar_init(smem_u32(&pk_full[s]), 1);
+      mbar_init(smem_u32(&pk_empty[s]), team_warps);   // the team that owns the slot's k-block
+      mbar_init(smem_u32(&a_full[s]), 1);
+      mbar_init(smem_u32(&b_ready[s]), team_warps);
+      mbar_init(smem_u32(&empty[s]), MT);              // one commit per MMA issuer
     }
     mbar_init(smem_u32(acc_ready), MT);
     *abort_flag = 0;
@@ -307,31 +324,47 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
+  // The loops of the single-thread roles carry slot index and parity along: an integer division
+  // by a run-time ring depth costs a lone thread hundreds of cycles per k-block.
   if (warp == 0) {
-    // ------------------------------------------------------------ producer
-    // Loops of the single-thread roles carry the stage index and parity along: an integer
-    // division by the (run-time) ring depth costs a lone thread hundreds of cycles per k-block.
-    if (lane == 0) {
+    // ------------------------------------------------------------ activation producer (lane t: row tile t)
+    if (lane < MT) {
       int s = 0;
-      uint32_t par = 0;                       // parity of this pass over the ring
-      const uint8_t* bsrc = p.B + (size_t)col0 * BB;
-      const size_t brow = (size_t)p.N * BB;
-      const uint32_t a_tx = (uint32_t)(MT * kBM * kBK * 2), b_tx = (uint32_t)tn * BB;
-      uint32_t st = smem_u32(stages);
+      uint32_t par = 0;
+      uint32_t dst = smem_u32(tiles) + lane * (kBM * kBK * 2);
       for (int kb = 0; kb < nkb; kb++) {
         if (kb >= p.stages) {
           if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status)) break;
         }
-        const uint32_t bar = smem_u32(&full_in[s]);
+        const uint32_t bar = smem_u32(&a_full[s]);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(MT * kBM * kBK * 2));
+        tma_load_2d(dst, &tmap_a, kb * kBK, row0 + lane * kBM, bar);
+        dst += p.stage_bytes;
+        if (++s == p.stages) s = 0, par ^= 1u, dst = smem_u32(tiles) + lane * (kBM * kBK * 2);
+      }
+    }
+  } else if (warp == kWeightProducerWarp) {
+    // ------------------------------------------------------------ weight producer (lane g: group-row g of the k-block)
+    if (lane < 2) {
+      int s = 0;
+      uint32_t par = 0;
+      const size_t brow = (size_t)p.N * BB;
+      const uint8_t* src = p.B + (size_t)col0 * BB + lane * brow;
+      const uint32_t b_tx = (uint32_t)tn * BB;
+      uint32_t dst = smem_u32(packed) + lane * p.pk_pitch;
+      for (int kb = 0; kb < nkb; kb++) {
+        if (kb >= p.pk_stages) {
+          if (!mbar_wait(smem_u32(&pk_empty[s]), par ^ 1u, abort_flag, p.status)) break;
+        }
+        const uint32_t bar = smem_u32(&pk_full[s]);
         const int ngr = min(2, p.G - kb * 2);
-        mbar_expect_tx(bar, a_tx + (uint32_t)ngr * b_tx);
-#pragma unroll
-        for (int t = 0; t < MT; t++) tma_load_2d(st + t * (kBM * kBK * 2), &tmap_a, kb * kBK, row0 + t * kBM, bar);
-        for (int gl = 0; gl < ngr; gl++)
-          bulk_load_plain(st + p.a_bytes + gl * p.pk_pitch, bsrc + gl * brow, b_tx, bar);
-        bsrc += 2 * brow;
-        st += p.stage_bytes;
-        if (++s == p.stages) s = 0, par ^= 1u, st = smem_u32(stages);
+        // the copy's complete_tx may reach the barrier before lane 0's expect_tx: the phase cannot
+        // complete before that arrival, and the transaction count may run negative meanwhile
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)ngr * b_tx);
+        if (lane < ngr) bulk_load_plain(dst, src, b_tx, bar);
+        src += 2 * brow;
+        dst += p.pk_bytes;
+        if (++s == p.pk_stages) s = 0, par ^= 1u, dst = smem_u32(packed) + lane * p.pk_pitch;
       }
     }
   } else if (warp < kFirstDequantWarp) {
@@ -342,16 +375,16 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       bool ok = true;
       int s = 0;
       uint32_t par = 0;
-      // descriptors differ between stages and k-steps only in the start-address field
+      // descriptors differ between slots and k-steps only in the start-address field
       // (bytes >> 4, the low 14 bits): add, do not rebuild
-      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(stages + t * (kBM * kBK * 2)));
-      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(stages + p.a_bytes + p.pk_bytes));
-      const uint32_t stage_step = (uint32_t)p.stage_bytes >> 4;
+      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(tiles + t * (kBM * kBK * 2)));
+      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(tiles + p.a_bytes));
+      const uint32_t slot_step = (uint32_t)p.stage_bytes >> 4;
       const uint32_t d_tmem = tmem_base + (uint32_t)(t * p.BN);
       uint32_t soff = 0;
       for (int kb = 0; kb < nkb; kb++) {
-        // b_ready implies full_in: the dequant warps waited on it (TMA tiles included) before arriving
-        ok = mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
+        ok = mbar_wait(smem_u32(&a_full[s]), par, abort_flag, p.status) &&
+             mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         const uint64_t a_desc = a_desc0 + soff, b_desc = b_desc0 + soff;
@@ -362,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
                    (kb > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(smem_u32(&empty[s]));
-        soff += stage_step;
+        soff += slot_step;
         if (++s == p.stages) s = 0, par ^= 1u, soff = 0;
       }
       if (ok) umma_commit(smem_u32(acc_ready));
@@ -371,18 +404,21 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     // ------------------------------------------------------------ dequantise
     const int dw = warp - kFirstDequantWarp;            // 0 .. kDequantWarps - 1
     const int team = dw % p.groups;                      // this warp's team
-    const int team_threads = (kDequantWarps / p.groups) * 32;
+    const int team_threads = team_warps * 32;
     const int dt = (dw / p.groups) * 32 + lane;          // thread index inside the team
     bool ok = true;
-    int s = team;                                        // groups < stages
-    uint32_t par = 0;
+    int s = team, sp = team;                             // groups <= stages, pk_stages
+    uint32_t par = 0, parp = 0;
     const int bn2 = 2 * p.BN, bn3 = 3 * p.BN, items = 4 * p.BN;
     for (int kb = team; kb < nkb; kb += p.groups) {
-      ok = mbar_wait(smem_u32(&full_in[s]), par, abort_flag, p.status);
+      ok = mbar_wait(smem_u32(&pk_full[sp]), parp, abort_flag, p.status);
+      if (ok && kb >= p.stages) {
+        ok = mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status);   // the slot's last MMAs have read it
+        tc_fence_after();
+      }
       if (!ok) break;
-      uint8_t* st = stages + (size_t)s * p.stage_bytes;
-      const uint8_t* pk = st + p.a_bytes;
-      uint8_t* bt = st + p.a_bytes + p.pk_bytes;
+      const uint8_t* pk = packed + (size_t)sp * p.pk_bytes;
+      uint8_t* bt = tiles + (size_t)s * p.stage_bytes + p.a_bytes;
       const int g0 = kb * 2;
       for (int it = dt; it < items; it += team_threads) {
         const int part = (it >= p.BN) + (it >= bn2) + (it >= bn3);   // part = 2 * group + half
@@ -393,12 +429,17 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       }
       fence_async_smem();       // make the generic-proxy stores visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&b_ready[s]));
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&b_ready[s]));
+        mbar_arrive(smem_u32(&pk_empty[sp]));
+      }
       s += p.groups;
       if (s >= p.stages) s -= p.stages, par ^= 1u;
+      sp += p.groups;
+      if (sp >= p.pk_stages) sp -= p.pk_stages, parp ^= 1u;
     }
     // ---------------------------------------------------------- epilogue (first four dequant warps)
-    if (warp < kFirstDequantWarp + 4) {
+    if (dw < 4) {
       const bool got = ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status);
       tc_fence_after();
       if (got) {
@@ -460,7 +501,7 @@ EncodeTiledFn encode_fn() {
 }
 
 struct Plan {
-  int MT, BN, stages, tmem_cols, groups;
+  int MT, BN, stages, pk_stages, tmem_cols, groups;
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;
   size_t smem;
   dim3 grid;
@@ -490,15 +531,19 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
   pl.pk_pitch = ((pl.BN * BB + 15) / 16) * 16;
   pl.pk_bytes = ((2 * pl.pk_pitch + 16 + 1023) / 1024) * 1024;   // + slack for the Q8 read-ahead
   pl.b_bytes = pl.BN * kBK * 2;
-  pl.stage_bytes = pl.a_bytes + pl.pk_bytes + pl.b_bytes;        // every part a multiple of 1024
-  pl.stages = (kSmemBudget - 1024) / pl.stage_bytes;
+  pl.stage_bytes = pl.a_bytes + pl.b_bytes;                      // one tile slot; every part a multiple of 1024
+  // tile ring as deep as fits beside four packed slots, the packed ring takes what is left
+  const int budget = kSmemBudget - 1024;
+  pl.stages = (budget - 4 * pl.pk_bytes) / pl.stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
-  // dequant teams: as many k-blocks in flight as the ring allows beside the one being multiplied
+  pl.pk_stages = (budget - pl.stages * pl.stage_bytes) / pl.pk_bytes;
+  if (pl.pk_stages > kMaxStages) pl.pk_stages = kMaxStages;
+  // dequant teams: k-blocks dequantised side by side; each needs a tile slot beside the one being multiplied
   pl.groups = pl.stages >= 5 ? 4 : (pl.stages >= 3 ? 2 : 1);
   int cols = 32;
   while (cols < pl.MT * pl.BN) cols <<= 1;
   pl.tmem_cols = cols;
-  pl.smem = 1024 + (size_t)pl.stages * pl.stage_bytes;
+  pl.smem = 1024 + (size_t)pl.stages * pl.stage_bytes + (size_t)pl.pk_stages * pl.pk_bytes;
   pl.grid = dim3((unsigned)mtiles, (unsigned)((N + pl.BN - 1) / pl.BN));
   return pl;
 }
@@ -573,7 +618,7 @@ cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C
   Params p{};
   p.B = B, p.C = C, p.row_inv = (kind == 8) ? row_inv : nullptr;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
-  p.BN = pl.BN, p.stages = pl.stages, p.groups = pl.groups;
+  p.BN = pl.BN, p.stages = pl.stages, p.pk_stages = pl.pk_stages, p.groups = pl.groups;
   p.a_bytes = pl.a_bytes, p.pk_pitch = pl.pk_pitch, p.pk_bytes = pl.pk_bytes, p.b_bytes = pl.b_bytes;
   p.stage_bytes = pl.stage_bytes, p.tmem_cols = pl.tmem_cols;
   p.status = kernel_status_ptr();
