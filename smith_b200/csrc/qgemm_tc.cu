@@ -17,14 +17,14 @@
 //     {activation tile, dequantised B tile} slots.
 //     warp 0     activation producer: lane t TMA-loads row tile t's 128 x 64
 //                tile (128-byte swizzle) of each k-block into a tile slot.
-//     warps 1-2  MMA issuers, one per row tile (warp 1 also allocates tensor
+//     warps 4,8  MMA issuers, one per row tile (warp 4 also allocates tensor
 //                memory): per k-block four tcgen05.mma (128 x BN x 16), A and B
 //                from shared memory through K-major 128-byte-swizzle
 //                descriptors, D = f32 in TMEM; tcgen05.commit frees the slot.
-//     warp 3     weight producer: lanes 0-1 bulk-copy the k-block's two packed
+//     warp 12    weight producer: lanes 0-1 bulk-copy the k-block's two packed
 //                group-rows of the tile's BN columns into a packed-ring slot.
-//     warps 4-31 dequantise, in `groups` teams that own alternate k-blocks (team =
-//                warp % groups works on k-blocks team, team + groups, ...): each
+//     the 24 warps that are not multiples of four dequantise, in `groups` teams that own
+//                alternate k-blocks (team t works on k-blocks t, t + groups, ...): each
 //                thread takes half of a (column, group) block (16 weights),
 //                forms scale * (code - zero) (Q4,
 //                packed bf16: exact code - round(zero), then one fused
@@ -36,7 +36,7 @@
 //                nibbles pair up in a 32-bit word); convert_activations stores
 //                the activations' k in the same order, so the dot products
 //                are unchanged and no byte shuffles are needed.
-//     warps 4-7  epilogue: tcgen05.ld their 32-lane quarter of each
+//     warps 1-3, 16  epilogue: tcgen05.ld their 32-lane quarter of each
 //                accumulator, 32 columns at a time, and store C rows.
 //   Weights of a tile are dequantised once and feed MT row tiles, so for
 //   M >= 256 the CUDA-core dequantisation stays below the tensor time.
@@ -56,10 +56,17 @@ namespace {
 
 constexpr int kBM = 128;            // rows per MMA / per accumulator
 constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of 16-bit values
-constexpr int kDequantWarps = 28;
-constexpr int kWeightProducerWarp = 3;
-constexpr int kFirstDequantWarp = 4;   // warp 0: activation producer, 1-2: MMA issuers (one per row tile), 3: weight producer
-constexpr int kThreads = (kFirstDequantWarp + kDequantWarps) * 32;
+// Warp roles.  The four single-thread roles sit on the warps that are multiples of four, which
+// share one of the SM's four warp schedulers; the dequant warps are all the others.  A lone thread
+// on a scheduler that also hosts seven always-ready dequant warps gets about an eighth of its
+// issue slots, and these threads' instruction chains are the k-loop's critical path.
+constexpr int kWarps = 32;
+constexpr int kThreads = kWarps * 32;
+constexpr int kDequantWarps = 24;          // warps with warp % 4 != 0
+constexpr int kActProducerWarp = 0;
+constexpr int kMmaWarp0 = 4;               // row tile 0 (also allocates tensor memory); row tile 1: warp 8
+constexpr int kWeightProducerWarp = 12;
+constexpr int kEpilogueWarp0 = 16;         // reads TMEM lanes 0-31 in the epilogue; warps 1-3 read the rest
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 224 * 1024;
 
@@ -315,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp0) {
     tmem_alloc(smem_u32(tmem_base_slot), (uint32_t)p.tmem_cols);
     tmem_relinquish();
   }
@@ -326,7 +333,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
 
   // The loops of the single-thread roles carry slot index and parity along: an integer division
   // by a run-time ring depth costs a lone thread hundreds of cycles per k-block.
-  if (warp == 0) {
+  const int wq = warp & 3;
+  bool ok = true;
+  if (warp == kActProducerWarp) {
     // ------------------------------------------------------------ activation producer (lane t: row tile t)
     if (lane < MT) {
       int s = 0;
@@ -367,12 +376,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
         if (++s == p.pk_stages) s = 0, par ^= 1u, dst = smem_u32(packed) + lane * p.pk_pitch;
       }
     }
-  } else if (warp < kFirstDequantWarp) {
-    // ------------------------------------------------------------ MMA issuers (warp 1: row tile 0, warp 2: row tile 1)
-    const int t = warp - 1;
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 4) {
+    // ------------------------------------------------------------ MMA issuers, one per row tile
+    const int t = (warp - kMmaWarp0) >> 2;
     if (lane == 0 && t < MT) {
       const uint32_t idesc = instr_desc(KIND == 4 ? 1 : 0, p.BN);
-      bool ok = true;
       int s = 0;
       uint32_t par = 0;
       // descriptors differ between slots and k-steps only in the start-address field
@@ -383,8 +391,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       const uint32_t d_tmem = tmem_base + (uint32_t)(t * p.BN);
       uint32_t soff = 0;
       for (int kb = 0; kb < nkb; kb++) {
-        ok = mbar_wait(smem_u32(&a_full[s]), par, abort_flag, p.status) &&
-             mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
+        // b_ready covers the activation tile too: the team's first warp waits for it before arriving
+        ok = mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         const uint64_t a_desc = a_desc0 + soff, b_desc = b_desc0 + soff;
@@ -400,13 +408,12 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       }
       if (ok) umma_commit(smem_u32(acc_ready));
     }
-  } else {
+  } else if (wq != 0) {
     // ------------------------------------------------------------ dequantise
-    const int dw = warp - kFirstDequantWarp;            // 0 .. kDequantWarps - 1
+    const int dw = (warp >> 2) * 3 + wq - 1;            // 0 .. kDequantWarps - 1
     const int team = dw % p.groups;                      // this warp's team
     const int team_threads = team_warps * 32;
     const int dt = (dw / p.groups) * 32 + lane;          // thread index inside the team
-    bool ok = true;
     int s = team, sp = team;                             // groups <= stages, pk_stages
     uint32_t par = 0, parp = 0;
     const int bn2 = 2 * p.BN, bn3 = 3 * p.BN, items = 4 * p.BN;
@@ -428,46 +435,50 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
         dequant_half<KIND>(pk, (uint32_t)(gl * p.pk_pitch + col * BB), bt, col, gl, part & 1, zero);
       }
       fence_async_smem();       // make the generic-proxy stores visible to the tensor core's reads
+      if (dw < p.groups) ok = mbar_wait(smem_u32(&a_full[s]), par, abort_flag, p.status);   // the team's first warp
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(&b_ready[s]));
         mbar_arrive(smem_u32(&pk_empty[sp]));
       }
+      if (!ok) break;
       s += p.groups;
       if (s >= p.stages) s -= p.stages, par ^= 1u;
       sp += p.groups;
       if (sp >= p.pk_stages) sp -= p.pk_stages, parp ^= 1u;
     }
-    // ---------------------------------------------------------- epilogue (first four dequant warps)
-    if (dw < 4) {
-      const bool got = ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status);
-      tc_fence_after();
-      if (got) {
-        const int q = warp & 3;                          // TMEM lane quarter this warp may read
+  }
+  // ---------------------------------------------------------------- epilogue
+  // Warps 1-3 (after their dequant work) and warp 16 read TMEM lane quarters 1-3 and 0.
+  if (warp == kEpilogueWarp0 || (warp >= 1 && warp <= 3)) {
+    // warp-uniform: the TMEM loads below are warp-collective
+    const bool got = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status));
+    tc_fence_after();
+    if (got) {
+      const int q = warp & 3;                          // TMEM lane quarter this warp may read
 #pragma unroll 1
-        for (int t = 0; t < MT; t++) {
-          const int row = row0 + t * kBM + q * 32 + lane;
-          const float inv = (KIND == 8 && row < p.M) ? p.row_inv[row] : 1.f;
+      for (int t = 0; t < MT; t++) {
+        const int row = row0 + t * kBM + q * 32 + lane;
+        const float inv = (KIND == 8 && row < p.M) ? p.row_inv[row] : 1.f;
 #pragma unroll 1
-          for (int c = 0; c < p.BN; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
-            tmem_ld_wait();
-            if (row < p.M) {
-              float* dst = p.C + (size_t)row * p.N + col0 + c;
-              if (c + 32 <= tn && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+        for (int c = 0; c < p.BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
+          tmem_ld_wait();
+          if (row < p.M) {
+            float* dst = p.C + (size_t)row * p.N + col0 + c;
+            if (c + 32 <= tn && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                  float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                                         __uint_as_float(r[i + 3]));
-                  if (KIND == 8) v.x *= inv, v.y *= inv, v.z *= inv, v.w *= inv;
-                  *reinterpret_cast<float4*>(dst + i) = v;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; i++)
-                  if (c + i < tn) dst[i] = __uint_as_float(r[i]) * inv;
+              for (int i = 0; i < 32; i += 4) {
+                float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                       __uint_as_float(r[i + 3]));
+                if (KIND == 8) v.x *= inv, v.y *= inv, v.z *= inv, v.w *= inv;
+                *reinterpret_cast<float4*>(dst + i) = v;
               }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (c + i < tn) dst[i] = __uint_as_float(r[i]) * inv;
             }
           }
         }
@@ -477,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
