@@ -63,6 +63,7 @@ constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of 
 constexpr int kWarps = 32;
 constexpr int kThreads = kWarps * 32;
 constexpr int kDequantWarps = 24;          // warps with warp % 4 != 0
+constexpr int kMaxItems = 3;               // blocks per dequant thread and k-block: 2 * 256 columns over the 192 threads of the smallest team
 constexpr int kActProducerWarp = 0;
 constexpr int kMmaWarp0 = 4;               // row tile 0 (also allocates tensor memory); row tile 1: warp 8
 constexpr int kWeightProducerWarp = 12;
@@ -208,23 +209,23 @@ __global__ void __launch_bounds__(256) convert_activations(const float* __restri
   }
 }
 
-// ---------------------------------------------------------------- dequantise half of a (column, group) block
-// Writes the 16 values k = 32*gl + 16*half .. +15 of B-tile row `col` (K-major,
-// 128-byte swizzle: 16-byte chunk c of row n sits at chunk position c ^ (n & 7)).
+// ---------------------------------------------------------------- dequantise one (column, group) block
+// Writes the 32 values of one group of B-tile row `col` (K-major, 128-byte swizzle: 16-byte
+// chunk c of row n sits at chunk position c ^ (n & 7)).  `blk` is the packed block in shared
+// memory, `blk_off` its byte offset inside the 16-byte-aligned packed slot (Q8 needs the
+// alignment), `dst` the position of the group's first chunk in the tile (row offset plus swizzled
+// chunk position); chunk i of the group then lies at dst ^ (i << 4) in offset terms.
 template <int KIND>
-__device__ __forceinline__ void dequant_half(const uint8_t* __restrict__ pk, uint32_t pk_off, uint8_t* __restrict__ bt,
-                                             int col, int gl, int half, bool zero_fill) {
-  uint8_t* row = bt + (size_t)(col >> 3) * 1024 + (col & 7) * 128;
-  const int sw = col & 7;
-  const int c0 = 4 * gl + 2 * half;
+__device__ __forceinline__ void dequant_block(const uint8_t* __restrict__ blk, uint32_t blk_off,
+                                              uint8_t* __restrict__ tile, uint32_t dst, bool zero_fill) {
   if (zero_fill) {
-    *reinterpret_cast<uint4*>(row + ((c0 ^ sw) << 4)) = make_uint4(0, 0, 0, 0);
-    *reinterpret_cast<uint4*>(row + (((c0 + 1) ^ sw) << 4)) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(tile + (dst ^ (uint32_t)(i << 4))) = make_uint4(0, 0, 0, 0);
     return;
   }
-  const uint8_t* blk = pk + pk_off;
   if (KIND == 4) {
-    const uint2 nib = *reinterpret_cast<const uint2*>(blk + 8 * half);
+    const uint2 n01 = *reinterpret_cast<const uint2*>(blk);
+    const uint2 n23 = *reinterpret_cast<const uint2*>(blk + 8);
     const float2 sz = *reinterpret_cast<const float2*>(blk + 16);
     // scale * (code - zero) = scale * (code - zi) + (-scale * zf), zi = round(zero): code - zi is an exact
     // small integer in bf16; the multiply-add rounds once.
@@ -236,9 +237,9 @@ __device__ __forceinline__ void dequant_half(const uint8_t* __restrict__ pk, uin
     asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(s2) : "f"(sz.x));
     asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(c2) : "f"(-sz.x * zf));
     asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(z2) : "f"(128.f + zi));
-    const uint32_t w[2] = {nib.x, nib.y};
+    const uint32_t w[4] = {n01.x, n01.y, n23.x, n23.y};
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < 4; i++) {
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -247,21 +248,21 @@ __device__ __forceinline__ void dequant_half(const uint8_t* __restrict__ pk, uin
         asm("sub.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(r), "r"(z2));
         asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[j]) : "r"(d), "r"(s2), "r"(c2));
       }
-      *reinterpret_cast<uint4*>(row + (((c0 + i) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(tile + (dst ^ (uint32_t)(i << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   } else {
-    // 34-byte blocks are 2-byte aligned: read aligned words around the codes and shift
-    const uint32_t off = pk_off + 2 + 16 * half;
-    const uint32_t sh = (off & 3u) * 8;
-    const uint32_t* al = reinterpret_cast<const uint32_t*>(blk + 2 + 16 * half - (off & 3u));
-    uint32_t raw[5];
+    // 34-byte blocks are 2-byte aligned: read the aligned words around the 32 codes and shift
+    const uint32_t mis = (blk_off + 2) & 3u;
+    const uint32_t sh = mis * 8;
+    const uint32_t* al = reinterpret_cast<const uint32_t*>(blk + 2 - mis);
+    uint32_t raw[9];
 #pragma unroll
-    for (int i = 0; i < 5; i++) raw[i] = al[i];
+    for (int i = 0; i < 9; i++) raw[i] = al[i];
     const uint32_t h = *reinterpret_cast<const unsigned short*>(blk);
     const uint32_t s2 = h | (h << 16);
     const uint32_t k1152 = 0x64806480u;
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < 4; i++) {
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 2; j++) {
@@ -273,7 +274,7 @@ __device__ __forceinline__ void dequant_half(const uint8_t* __restrict__ pk, uin
         asm("mul.f16x2 %0, %1, %2;" : "=r"(o[2 * j]) : "r"(p0), "r"(s2));
         asm("mul.f16x2 %0, %1, %2;" : "=r"(o[2 * j + 1]) : "r"(p1), "r"(s2));
       }
-      *reinterpret_cast<uint4*>(row + (((c0 + i) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(tile + (dst ^ (uint32_t)(i << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
@@ -416,7 +417,19 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     const int dt = (dw / p.groups) * 32 + lane;          // thread index inside the team
     int s = team, sp = team;                             // groups <= stages, pk_stages
     uint32_t par = 0, parp = 0;
-    const int bn2 = 2 * p.BN, bn3 = 3 * p.BN, items = 4 * p.BN;
+    // This thread's (column, group) blocks are the same in every k-block: index them once.
+    // item = group * BN + col over the 2 * BN blocks of a k-block, dealt round-robin to the team.
+    uint32_t it_src[kMaxItems], it_dst[kMaxItems];   // packed-slot offset; tile offset, bit 31: pad column, bit 30: group 1
+#pragma unroll
+    for (int i = 0; i < kMaxItems; i++) {
+      const int it = dt + i * team_threads;
+      const int gl = it >= p.BN ? 1 : 0;
+      const int col = it - gl * p.BN;
+      it_src[i] = (uint32_t)(gl * p.pk_pitch + col * BB);
+      it_dst[i] = (it < 2 * p.BN) ? ((uint32_t)((col >> 3) * 1024 + (col & 7) * 128 + ((gl * 64) ^ ((col & 7) << 4))) |
+                                     (col >= tn ? 0x80000000u : 0u) | (gl ? 0x40000000u : 0u))
+                                  : 0xffffffffu;                                  // no such item
+    }
     for (int kb = team; kb < nkb; kb += p.groups) {
       ok = mbar_wait(smem_u32(&pk_full[sp]), parp, abort_flag, p.status);
       if (ok && kb >= p.stages) {
@@ -426,13 +439,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       if (!ok) break;
       const uint8_t* pk = packed + (size_t)sp * p.pk_bytes;
       uint8_t* bt = tiles + (size_t)s * p.stage_bytes + p.a_bytes;
-      const int g0 = kb * 2;
-      for (int it = dt; it < items; it += team_threads) {
-        const int part = (it >= p.BN) + (it >= bn2) + (it >= bn3);   // part = 2 * group + half
-        const int col = it - part * p.BN;
-        const int gl = part >> 1;
-        const bool zero = (col >= tn) || (g0 + gl >= p.G);
-        dequant_half<KIND>(pk, (uint32_t)(gl * p.pk_pitch + col * BB), bt, col, gl, part & 1, zero);
+      const bool tail = kb * 2 + 1 >= p.G;           // the k-block's second group lies beyond K
+#pragma unroll
+      for (int i = 0; i < kMaxItems; i++) {
+        const uint32_t d = it_dst[i];
+        if (d != 0xffffffffu) {
+          const bool zero = (d & 0x80000000u) || (tail && (d & 0x40000000u));
+          dequant_block<KIND>(pk + it_src[i], it_src[i], bt, d & 0x0000ffffu, zero);
+        }
       }
       fence_async_smem();       // make the generic-proxy stores visible to the tensor core's reads
       if (dw < p.groups) ok = mbar_wait(smem_u32(&a_full[s]), par, abort_flag, p.status);   // the team's first warp
