@@ -62,14 +62,14 @@ constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of 
 // issue slots, and these threads' instruction chains are the k-loop's critical path.
 constexpr int kWarps = 32;
 constexpr int kThreads = kWarps * 32;
-constexpr int kDequantWarps = 24;          // warps with warp % 4 != 0
-constexpr int kMaxItems = 3;               // blocks per dequant thread and k-block: 2 * 256 columns over the 192 threads of the smallest team
+constexpr int kDequantWarps = 28;          // the 24 warps with warp % 4 != 0 first, then warps 16, 20, 24, 28
+constexpr int kMaxItems = 3;               // most blocks per dequant thread and k-block that a plan may ask for
 constexpr int kActProducerWarp = 0;
 constexpr int kMmaWarp0 = 4;               // row tile 0 (also allocates tensor memory); row tile 1: warp 8
 constexpr int kWeightProducerWarp = 12;
 constexpr int kEpilogueWarp0 = 16;         // reads TMEM lanes 0-31 in the epilogue; warps 1-3 read the rest
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 224 * 1024;
+constexpr int kSmemBudget = 227 * 1024;
 
 struct Params {
   const uint8_t* B;
@@ -79,7 +79,8 @@ struct Params {
   int BN;                 // columns per CTA, multiple of 16, <= 256
   int stages;             // tile ring depth
   int pk_stages;          // packed ring depth
-  int groups;             // dequant teams (1, 2 or 4); team size = kDequantWarps / groups
+  int groups;             // dequant teams; team t owns k-blocks t, t + groups, ...
+  int team_warps;         // warps per team; groups * team_warps <= kDequantWarps
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;  // stage_bytes = a_bytes + b_bytes: one tile slot
   int tmem_cols;
   int* status;
@@ -309,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   const int row0 = blockIdx.x * (MT * kBM);
   const int tn = min(p.BN, p.N - col0);
   const int nkb = (p.K + kBK - 1) / kBK;
-  const int team_warps = kDequantWarps / p.groups;
+  const int team_warps = p.team_warps;
 
   if (tid == 0) {
     for (int s = 0; s < kMaxStages; s++) {
@@ -409,9 +410,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       }
       if (ok) umma_commit(smem_u32(acc_ready));
     }
-  } else if (wq != 0) {
+  } else if (wq != 0 || warp >= kEpilogueWarp0) {
     // ------------------------------------------------------------ dequantise
-    const int dw = (warp >> 2) * 3 + wq - 1;            // 0 .. kDequantWarps - 1
+    // dequant warp index: the other three scheduler partitions first, the role partition's spare warps last
+    const int dw = wq ? (warp >> 2) * 3 + wq - 1 : 24 + ((warp - kEpilogueWarp0) >> 2);
+    if (dw < p.groups * team_warps) {
     const int team = dw % p.groups;                      // this warp's team
     const int team_threads = team_warps * 32;
     const int dt = (dw / p.groups) * 32 + lane;          // thread index inside the team
@@ -460,6 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       if (s >= p.stages) s -= p.stages, par ^= 1u;
       sp += p.groups;
       if (sp >= p.pk_stages) sp -= p.pk_stages, parp ^= 1u;
+    }
     }
   }
   // ---------------------------------------------------------------- epilogue
@@ -526,7 +530,7 @@ EncodeTiledFn encode_fn() {
 }
 
 struct Plan {
-  int MT, BN, stages, pk_stages, tmem_cols, groups;
+  int MT, BN, stages, pk_stages, tmem_cols, groups, team_warps;
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;
   size_t smem;
   dim3 grid;
@@ -563,8 +567,25 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   pl.pk_stages = (budget - pl.stages * pl.stage_bytes) / pl.pk_bytes;
   if (pl.pk_stages > kMaxStages) pl.pk_stages = kMaxStages;
-  // dequant teams: k-blocks dequantised side by side; each needs a tile slot beside the one being multiplied
-  pl.groups = pl.stages >= 5 ? 4 : (pl.stages >= 3 ? 2 : 1);
+  // Dequant teams: g teams work on g k-blocks side by side (each needs a tile slot beside the one
+  // being multiplied), every thread taking ceil(blocks / team threads) of the k-block's 2 * BN
+  // blocks.  Pick the g with the least passes per k-block; ties go to fewer passes (shorter latency).
+  const int blocks = 2 * pl.BN;
+  pl.groups = 1, pl.team_warps = kDequantWarps;
+  double best_cost = 1e9;
+  int best_passes = 1 << 30;
+  for (int g = 1; g <= 4 && (g == 1 || g < pl.stages); g++) {
+    for (int pool = 24; pool <= kDequantWarps; pool += kDequantWarps - 24) {
+      int tw = pool / g;
+      if (tw > (blocks + 31) / 32) tw = (blocks + 31) / 32;      // no more warps than a single pass needs
+      const int passes = (blocks + tw * 32 - 1) / (tw * 32);
+      if (passes > kMaxItems) continue;
+      // warps beyond the first 24 share the single-thread roles' scheduler and slow them down
+      const double cost = (double)passes / g * (g * tw > 24 ? 1.4 : 1.0);
+      if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && passes < best_passes))
+        best_cost = cost, best_passes = passes, pl.groups = g, pl.team_warps = tw;
+    }
+  }
   int cols = 32;
   while (cols < pl.MT * pl.BN) cols <<= 1;
   pl.tmem_cols = cols;
@@ -643,7 +664,7 @@ cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C
   Params p{};
   p.B = B, p.C = C, p.row_inv = (kind == 8) ? row_inv : nullptr;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
-  p.BN = pl.BN, p.stages = pl.stages, p.pk_stages = pl.pk_stages, p.groups = pl.groups;
+  p.BN = pl.BN, p.stages = pl.stages, p.pk_stages = pl.pk_stages, p.groups = pl.groups, p.team_warps = pl.team_warps;
   p.a_bytes = pl.a_bytes, p.pk_pitch = pl.pk_pitch, p.pk_bytes = pl.pk_bytes, p.b_bytes = pl.b_bytes;
   p.stage_bytes = pl.stage_bytes, p.tmem_cols = pl.tmem_cols;
   p.status = kernel_status_ptr();
