@@ -111,15 +111,38 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] x B[smem], 128 x N x 16, 16-bit inputs, f32 accumulate.
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// D[tmem] (+)= A[smem] x B[smem], 128 x N x 16 per tcgen05.mma, 16-bit inputs, f32 accumulate.
+// The four MMAs of one 64-wide k-block in one go: k-step j reads both operands 32 bytes (two
+// descriptor address units) further along the swizzled 128-byte rows.  The descriptors' high
+// words are equal (same stride, version and layout) and only the first step may overwrite D.
+__device__ __forceinline__ void umma_f16_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                uint32_t idesc, uint32_t accumulate_first) {
   asm volatile(
       "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      ".reg .pred p, q;\n"
+      ".reg .b32 ta, tb;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "setp.ne.b32 q, %4, 0;\n"          // the instruction descriptor is never zero: q = true
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+      "add.u32 ta, %1, 2;\n"
+      "add.u32 tb, %2, 2;\n"
+      "mov.b64 da, {ta, %3};\n"
+      "mov.b64 db, {tb, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n"
+      "add.u32 ta, %1, 4;\n"
+      "add.u32 tb, %2, 4;\n"
+      "mov.b64 da, {ta, %3};\n"
+      "mov.b64 db, {tb, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n"
+      "add.u32 ta, %1, 6;\n"
+      "add.u32 tb, %2, 6;\n"
+      "mov.b64 da, {ta, %3};\n"
+      "mov.b64 db, {tb, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)
       : "memory");
 }
 // mbarrier arrive once every MMA issued so far by this thread has completed.
@@ -168,6 +191,9 @@ template <int KIND>
 __global__ void __launch_bounds__(256) convert_activations(const float* __restrict__ A, uint16_t* __restrict__ out,
                                                             float* __restrict__ row_inv, int M, int K) {
   __shared__ float red[8];
+  // the main kernel may start now: everything in it but the activation loads (and the Q8 row
+  // scales) is independent of this kernel and waits for it explicitly
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int row = blockIdx.x;
   const float* src = A + (size_t)row * K;
   float up = 1.f;
@@ -343,6 +369,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       int s = 0;
       uint32_t par = 0;
       uint32_t dst = smem_u32(tiles) + lane * (kBM * kBK * 2);
+      asm volatile("griddepcontrol.wait;" ::: "memory");   // the 16-bit activations are written by the launch before
       for (int kb = 0; kb < nkb; kb++) {
         if (kb >= p.stages) {
           if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status)) break;
@@ -389,21 +416,17 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       // (bytes >> 4, the low 14 bits): add, do not rebuild
       const uint64_t a_desc0 = smem_desc_sw128(smem_u32(tiles + t * (kBM * kBK * 2)));
       const uint64_t b_desc0 = smem_desc_sw128(smem_u32(tiles + p.a_bytes));
+      const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0, desc_hi = (uint32_t)(a_desc0 >> 32);
       const uint32_t slot_step = (uint32_t)p.stage_bytes >> 4;
       const uint32_t d_tmem = tmem_base + (uint32_t)(t * p.BN);
       uint32_t soff = 0;
+      static_assert(kBK == 64, "umma_f16_kblock issues the four k-steps of a 64-wide k-block");
       for (int kb = 0; kb < nkb; kb++) {
         // b_ready covers the activation tile too: the team's first warp waits for it before arriving
         ok = mbar_wait(smem_u32(&b_ready[s]), par, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t a_desc = a_desc0 + soff, b_desc = b_desc0 + soff;
-#pragma unroll
-        for (int j = 0; j < kBK / 16; j++) {
-          // 16 k = 32 bytes further along the swizzled 128-byte row
-          umma_f16(d_tmem, a_desc + (uint64_t)((j * 32) >> 4), b_desc + (uint64_t)((j * 32) >> 4), idesc,
-                   (kb > 0 || j > 0) ? 1u : 0u);
-        }
+        umma_f16_kblock(d_tmem, a_lo0 + soff, b_lo0 + soff, desc_hi, idesc, kb > 0 ? 1u : 0u);
         umma_commit(smem_u32(&empty[s]));
         soff += slot_step;
         if (++s == p.stages) s = 0, par ^= 1u, soff = 0;
@@ -472,6 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     // warp-uniform: the TMEM loads below are warp-collective
     const bool got = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status));
     tc_fence_after();
+    if (KIND == 8) asm volatile("griddepcontrol.wait;" ::: "memory");   // row_inv comes from the launch before
     if (got) {
       const int q = warp & 3;                          // TMEM lane quarter this warp may read
 #pragma unroll 1
@@ -603,9 +627,17 @@ cudaError_t launch_main(const CUtensorMap& map, const Params& p, const Plan& pl,
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  qgemm_tc_kernel<KIND, MT><<<pl.grid, kThreads, pl.smem, s>>>(map, p);
+  // Programmatic dependent launch: CTAs start as SMs come free while the activation conversion is
+  // still running; their weight pipeline fills meanwhile.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = pl.grid, cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = pl.smem, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemm_tc_kernel<KIND, MT>, map, p);
   count_launch();
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
