@@ -79,7 +79,8 @@ struct Params {
   int BN;                 // columns per CTA, multiple of 16, <= 256
   int stages;             // tile ring depth
   int pk_stages;          // packed ring depth
-  int groups;             // dequant teams; team t owns k-blocks t, t + groups, ...
+  int sb;                 // 64-wide k-blocks per slot and hand-off (1 or 2): a "step" is sb k-blocks
+  int groups;             // dequant teams; team t owns steps t, t + groups, ...
   int team_warps;         // warps per team; groups * team_warps <= kDequantWarps
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;  // stage_bytes = a_bytes + b_bytes: one tile slot
   int tmem_cols;
@@ -335,7 +336,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   const int col0 = blockIdx.y * p.BN;
   const int row0 = blockIdx.x * (MT * kBM);
   const int tn = min(p.BN, p.N - col0);
-  const int nkb = (p.K + kBK - 1) / kBK;
+  const int nkb = (p.K + p.sb * kBK - 1) / (p.sb * kBK);   // steps of sb k-blocks
   const int team_warps = p.team_warps;
 
   if (tid == 0) {
@@ -365,44 +366,49 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
   bool ok = true;
   if (warp == kActProducerWarp) {
     // ------------------------------------------------------------ activation producer (lane t: row tile t)
-    if (lane < MT) {
+    if (lane < MT * p.sb) {                 // lane = sub * MT + t: k-block `sub` of the step, row tile t
       int s = 0;
       uint32_t par = 0;
-      uint32_t dst = smem_u32(tiles) + lane * (kBM * kBK * 2);
+      const int sub = lane / MT, t = lane - sub * MT;
+      const uint32_t dst0 = smem_u32(tiles) + lane * (kBM * kBK * 2);
+      uint32_t dst = dst0;
       asm volatile("griddepcontrol.wait;" ::: "memory");   // the 16-bit activations are written by the launch before
       for (int kb = 0; kb < nkb; kb++) {
         if (kb >= p.stages) {
           if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status)) break;
         }
         const uint32_t bar = smem_u32(&a_full[s]);
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(MT * kBM * kBK * 2));
-        tma_load_2d(dst, &tmap_a, kb * kBK, row0 + lane * kBM, bar);
+        // a box beyond K is filled with zeros and still counts its bytes
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(p.sb * MT * kBM * kBK * 2));
+        tma_load_2d(dst, &tmap_a, (kb * p.sb + sub) * kBK, row0 + t * kBM, bar);
         dst += p.stage_bytes;
-        if (++s == p.stages) s = 0, par ^= 1u, dst = smem_u32(tiles) + lane * (kBM * kBK * 2);
+        if (++s == p.stages) s = 0, par ^= 1u, dst = dst0;
       }
     }
   } else if (warp == kWeightProducerWarp) {
     // ------------------------------------------------------------ weight producer (lane g: group-row g of the k-block)
-    if (lane < 2) {
+    if (lane < 2 * p.sb) {                  // lane: group-row of the step
       int s = 0;
       uint32_t par = 0;
       const size_t brow = (size_t)p.N * BB;
       const uint8_t* src = p.B + (size_t)col0 * BB + lane * brow;
       const uint32_t b_tx = (uint32_t)tn * BB;
-      uint32_t dst = smem_u32(packed) + lane * p.pk_pitch;
+      const int per = 2 * p.sb;
+      const uint32_t dst0 = smem_u32(packed) + lane * p.pk_pitch;
+      uint32_t dst = dst0;
       for (int kb = 0; kb < nkb; kb++) {
         if (kb >= p.pk_stages) {
           if (!mbar_wait(smem_u32(&pk_empty[s]), par ^ 1u, abort_flag, p.status)) break;
         }
         const uint32_t bar = smem_u32(&pk_full[s]);
-        const int ngr = min(2, p.G - kb * 2);
+        const int ngr = min(per, p.G - kb * per);
         // the copy's complete_tx may reach the barrier before lane 0's expect_tx: the phase cannot
         // complete before that arrival, and the transaction count may run negative meanwhile
         if (lane == 0) mbar_expect_tx(bar, (uint32_t)ngr * b_tx);
         if (lane < ngr) bulk_load_plain(dst, src, b_tx, bar);
-        src += 2 * brow;
+        src += per * brow;
         dst += p.pk_bytes;
-        if (++s == p.pk_stages) s = 0, par ^= 1u, dst = smem_u32(packed) + lane * p.pk_pitch;
+        if (++s == p.pk_stages) s = 0, par ^= 1u, dst = dst0;
       }
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 4) {
@@ -416,6 +422,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       // (bytes >> 4, the low 14 bits): add, do not rebuild
       const uint64_t a_desc0 = smem_desc_sw128(smem_u32(tiles + t * (kBM * kBK * 2)));
       const uint64_t b_desc0 = smem_desc_sw128(smem_u32(tiles + p.a_bytes));
+      const uint32_t a_sub = (uint32_t)(MT * kBM * kBK * 2) >> 4, b_sub = (uint32_t)(p.BN * kBK * 2) >> 4;
       const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0, desc_hi = (uint32_t)(a_desc0 >> 32);
       const uint32_t slot_step = (uint32_t)p.stage_bytes >> 4;
       const uint32_t d_tmem = tmem_base + (uint32_t)(t * p.BN);
@@ -427,6 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
         if (!ok) break;
         tc_fence_after();
         umma_f16_kblock(d_tmem, a_lo0 + soff, b_lo0 + soff, desc_hi, idesc, kb > 0 ? 1u : 0u);
+        if (p.sb == 2) umma_f16_kblock(d_tmem, a_lo0 + soff + a_sub, b_lo0 + soff + b_sub, desc_hi, idesc, 1u);
         umma_commit(smem_u32(&empty[s]));
         soff += slot_step;
         if (++s == p.stages) s = 0, par ^= 1u, soff = 0;
@@ -443,18 +451,23 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     const int dt = (dw / p.groups) * 32 + lane;          // thread index inside the team
     int s = team, sp = team;                             // groups <= stages, pk_stages
     uint32_t par = 0, parp = 0;
-    // This thread's (column, group) blocks are the same in every k-block: index them once.
-    // item = group * BN + col over the 2 * BN blocks of a k-block, dealt round-robin to the team.
-    uint32_t it_src[kMaxItems], it_dst[kMaxItems];   // packed-slot offset; tile offset, bit 31: pad column, bit 30: group 1
+    // This thread's (column, group) blocks are the same in every step: index them once.
+    // item = group * BN + col over the step's 2 * sb * BN blocks, dealt round-robin to the team.
+    // it_dst: tile-slot offset of the block's first chunk (bits 0-19), group of the step (bits 28-30),
+    // pad column (bit 31).
+    uint32_t it_src[kMaxItems], it_dst[kMaxItems];
+    const int per = 2 * p.sb;
 #pragma unroll
     for (int i = 0; i < kMaxItems; i++) {
       const int it = dt + i * team_threads;
-      const int gl = it >= p.BN ? 1 : 0;
-      const int col = it - gl * p.BN;
+      int gl = 0, col = it;
+      while (gl < per - 1 && col >= p.BN) col -= p.BN, gl++;
       it_src[i] = (uint32_t)(gl * p.pk_pitch + col * BB);
-      it_dst[i] = (it < 2 * p.BN) ? ((uint32_t)((col >> 3) * 1024 + (col & 7) * 128 + ((gl * 64) ^ ((col & 7) << 4))) |
-                                     (col >= tn ? 0x80000000u : 0u) | (gl ? 0x40000000u : 0u))
-                                  : 0xffffffffu;                                  // no such item
+      it_dst[i] = (it < per * p.BN)
+                      ? ((uint32_t)((gl >> 1) * (p.BN * kBK * 2) + (col >> 3) * 1024 + (col & 7) * 128 +
+                                    (((gl & 1) * 64) ^ ((col & 7) << 4))) |
+                         (col >= tn ? 0x80000000u : 0u) | ((uint32_t)gl << 28))
+                      : 0xffffffffu;                                              // no such item
     }
     for (int kb = team; kb < nkb; kb += p.groups) {
       ok = mbar_wait(smem_u32(&pk_full[sp]), parp, abort_flag, p.status);
@@ -465,13 +478,13 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       if (!ok) break;
       const uint8_t* pk = packed + (size_t)sp * p.pk_bytes;
       uint8_t* bt = tiles + (size_t)s * p.stage_bytes + p.a_bytes;
-      const bool tail = kb * 2 + 1 >= p.G;           // the k-block's second group lies beyond K
+      const int left = p.G - kb * per;               // groups of this step that lie inside K
 #pragma unroll
       for (int i = 0; i < kMaxItems; i++) {
         const uint32_t d = it_dst[i];
         if (d != 0xffffffffu) {
-          const bool zero = (d & 0x80000000u) || (tail && (d & 0x40000000u));
-          dequant_block<KIND>(pk + it_src[i], it_src[i], bt, d & 0x0000ffffu, zero);
+          const bool zero = (d & 0x80000000u) || (int)((d >> 28) & 7u) >= left;
+          dequant_block<KIND>(pk + it_src[i], it_src[i], bt, d & 0x000fffffu, zero);
         }
       }
       fence_async_smem();       // make the generic-proxy stores visible to the tensor core's reads
@@ -554,7 +567,7 @@ EncodeTiledFn encode_fn() {
 }
 
 struct Plan {
-  int MT, BN, stages, pk_stages, tmem_cols, groups, team_warps;
+  int MT, BN, sb, stages, pk_stages, tmem_cols, groups, team_warps;
   int a_bytes, pk_pitch, pk_bytes, b_bytes, stage_bytes;
   size_t smem;
   dim3 grid;
@@ -565,12 +578,13 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
   Plan pl{};
   pl.MT = (M > kBM) ? 2 : 1;
   const int64_t mtiles = (M + pl.MT * kBM - 1) / (pl.MT * kBM);
-  // Column tile: the multiple of 16 in [64, 256] that wastes the least of the
+  // Column tile: the multiple of 16 in [16, 256] that wastes the least of the
   // machine (partial last tile x partial last wave); wider wins ties.
   double best = -1.0;
   int bestBN = 128;
-  for (int bn = 256; bn >= 64; bn -= 16) {
+  for (int bn = 256; bn >= 16; bn -= 16) {
     const int64_t nt = (N + bn - 1) / bn;
+    if (nt > 65535) continue;                                  // grid.y
     const int64_t ctas = nt * mtiles;
     const int64_t waves = (ctas + 147) / 148;
     // useful fraction of the tiles x fill of the last wave x a mild preference for wide MMAs
@@ -580,21 +594,26 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
     if (eff > best + 1e-9) best = eff, bestBN = bn;
   }
   pl.BN = bestBN;
-  pl.a_bytes = pl.MT * kBM * kBK * 2;
-  pl.pk_pitch = ((pl.BN * BB + 15) / 16) * 16;
-  pl.pk_bytes = ((2 * pl.pk_pitch + 16 + 1023) / 1024) * 1024;   // + slack for the Q8 read-ahead
-  pl.b_bytes = pl.BN * kBK * 2;
-  pl.stage_bytes = pl.a_bytes + pl.b_bytes;                      // one tile slot; every part a multiple of 1024
-  // tile ring as deep as fits beside four packed slots, the packed ring takes what is left
+  // Steps of two k-blocks halve the hand-offs between the roles; they pay when there is a single row
+  // tile (little tensor time per k-block to hide the hand-offs behind) and three slots still fit.
   const int budget = kSmemBudget - 1024;
-  pl.stages = (budget - 4 * pl.pk_bytes) / pl.stage_bytes;
+  for (pl.sb = (pl.MT == 1 ? 2 : 1); pl.sb >= 1; pl.sb--) {
+    pl.a_bytes = pl.sb * pl.MT * kBM * kBK * 2;
+    pl.pk_pitch = ((pl.BN * BB + 15) / 16) * 16;
+    pl.pk_bytes = ((2 * pl.sb * pl.pk_pitch + 16 + 1023) / 1024) * 1024;   // + slack for the Q8 read-ahead
+    pl.b_bytes = pl.sb * pl.BN * kBK * 2;
+    pl.stage_bytes = pl.a_bytes + pl.b_bytes;                      // one tile slot; every part a multiple of 1024
+    // tile ring as deep as fits beside four packed slots, the packed ring takes what is left
+    pl.stages = (budget - 4 * pl.pk_bytes) / pl.stage_bytes;
+    if (pl.stages >= 3 || pl.sb == 1) break;
+  }
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   pl.pk_stages = (budget - pl.stages * pl.stage_bytes) / pl.pk_bytes;
   if (pl.pk_stages > kMaxStages) pl.pk_stages = kMaxStages;
   // Dequant teams: g teams work on g k-blocks side by side (each needs a tile slot beside the one
   // being multiplied), every thread taking ceil(blocks / team threads) of the k-block's 2 * BN
   // blocks.  Pick the g with the least passes per k-block; ties go to fewer passes (shorter latency).
-  const int blocks = 2 * pl.BN;
+  const int blocks = 2 * pl.sb * pl.BN;
   pl.groups = 1, pl.team_warps = kDequantWarps;
   double best_cost = 1e9;
   int best_passes = 1 << 30;
@@ -610,8 +629,10 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
         best_cost = cost, best_passes = passes, pl.groups = g, pl.team_warps = tw;
     }
   }
+  // the epilogue reads the accumulators 32 columns at a time, so the last tile is rounded up
+  const int need = (pl.MT - 1) * pl.BN + ((pl.BN + 31) / 32) * 32;
   int cols = 32;
-  while (cols < pl.MT * pl.BN) cols <<= 1;
+  while (cols < need) cols <<= 1;
   pl.tmem_cols = cols;
   pl.smem = 1024 + (size_t)pl.stages * pl.stage_bytes + (size_t)pl.pk_stages * pl.pk_bytes;
   pl.grid = dim3((unsigned)mtiles, (unsigned)((N + pl.BN - 1) / pl.BN));
@@ -652,7 +673,7 @@ bool qgemm_tc_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups
   // reductions go to the any-shape kernel.  Q8 runs in f16 (2^-12) and has no such limit.
   if (kind == 4 && K < 1024) return false;
   if (N > (1 << 30) || K > (1 << 24)) return false;
-  if ((N + 63) / 64 > 65535) return false;
+  if ((N + 255) / 256 > 65535) return false;
   return encode_fn() != nullptr;
 }
 
@@ -696,7 +717,7 @@ cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C
   Params p{};
   p.B = B, p.C = C, p.row_inv = (kind == 8) ? row_inv : nullptr;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)groups;
-  p.BN = pl.BN, p.stages = pl.stages, p.pk_stages = pl.pk_stages, p.groups = pl.groups, p.team_warps = pl.team_warps;
+  p.BN = pl.BN, p.stages = pl.stages, p.pk_stages = pl.pk_stages, p.groups = pl.groups, p.team_warps = pl.team_warps, p.sb = pl.sb;
   p.a_bytes = pl.a_bytes, p.pk_pitch = pl.pk_pitch, p.pk_bytes = pl.pk_bytes, p.b_bytes = pl.b_bytes;
   p.stage_bytes = pl.stage_bytes, p.tmem_cols = pl.tmem_cols;
   p.status = kernel_status_ptr();
