@@ -511,31 +511,51 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     if (KIND == 8) asm volatile("griddepcontrol.wait;" ::: "memory");   // row_inv comes from the launch before
     if (got) {
       const int q = warp & 3;                          // TMEM lane quarter this warp may read
+      // tcgen05.ld hands lane l the 32 columns of accumulator row 32 * q + l.  Storing those straight to
+      // C would touch 32 rows per instruction (32 wavefronts of the L1 data pipe each); instead the warp
+      // turns the 32 x 32 chunk around in shared memory (the tile ring is idle by now) and stores
+      // four whole 128-byte row segments per instruction.
+      constexpr int kPitch = 36;                       // floats per staged row: 16-byte aligned, conflict-free
+      float* stage = reinterpret_cast<float*>(tiles) + q * (32 * kPitch);
+      const int sr = lane >> 3, sc = (lane & 7) * 4;   // this lane's row (of each 4) and column in the read-back
 #pragma unroll 1
       for (int t = 0; t < MT; t++) {
-        const int row = row0 + t * kBM + q * 32 + lane;
-        const float inv = (KIND == 8 && row < p.M) ? p.row_inv[row] : 1.f;
+        const int rbase = row0 + t * kBM + q * 32;
+        const float inv = (KIND == 8 && rbase + lane < p.M) ? p.row_inv[rbase + lane] : 1.f;
 #pragma unroll 1
         for (int c = 0; c < p.BN; c += 32) {
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
           tmem_ld_wait();
-          if (row < p.M) {
-            float* dst = p.C + (size_t)row * p.N + col0 + c;
-            if (c + 32 <= tn && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                                       __uint_as_float(r[i + 3]));
-                if (KIND == 8) v.x *= inv, v.y *= inv, v.z *= inv, v.w *= inv;
-                *reinterpret_cast<float4*>(dst + i) = v;
+          for (int i = 0; i < 32; i += 4) {
+            float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                   __uint_as_float(r[i + 3]));
+            if (KIND == 8) v.x *= inv, v.y *= inv, v.z *= inv, v.w *= inv;
+            *reinterpret_cast<float4*>(stage + lane * kPitch + i) = v;
+          }
+          __syncwarp();
+          const int cc = c + sc;                        // first of this lane's four columns within the tile
+          float* dcol = p.C + col0 + cc;
+          const bool vec = (cc + 4 <= tn) && ((reinterpret_cast<uintptr_t>(dcol) & 15) == 0);   // N % 8 == 0: same for all rows
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int rr = 4 * i + sr;
+            const int row = rbase + rr;
+            if (row < p.M) {
+              const float4 v = *reinterpret_cast<const float4*>(stage + rr * kPitch + sc);
+              float* dst = dcol + (size_t)row * p.N;
+              if (vec) {
+                *reinterpret_cast<float4*>(dst) = v;
+              } else {
+                if (cc < tn) dst[0] = v.x;
+                if (cc + 1 < tn) dst[1] = v.y;
+                if (cc + 2 < tn) dst[2] = v.z;
+                if (cc + 3 < tn) dst[3] = v.w;
               }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; i++)
-                if (c + i < tn) dst[i] = __uint_as_float(r[i]) * inv;
             }
           }
+          __syncwarp();
         }
       }
     }
