@@ -67,8 +67,9 @@ def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return dict(hbm=d["hbm_gbs"], tensor=d["bf16_tflops"], source="measured")
-    return dict(hbm=6650.0, tensor=1590.0, source="fallback")
+        return dict(hbm=d["hbm_gbs"], tensor=d["bf16_tflops"],
+                    tensor_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
 
 
 def traffic_for(name):
@@ -351,10 +352,15 @@ def main():
         e2e_value, _ = metric_of(kind, M, K, N, e2e_s / (e2e_steps * R))
         peaks = measured_peaks()
         nbytes_l, flops_l = algorithmic(kind, M, K, Nl)       # what this rank's kernel moves per launch
+        sustained = False
         if M <= 64:
             ach, peak, runit, bound = nbytes_l / per_launch_s / 1e9, peaks["hbm"], "GB/s", "hbm"
         else:
-            ach, peak, runit, bound = flops_l / per_launch_s / 1e12, peaks["tensor"], "TFLOP/s", "tensor"
+            # A long timed region runs under the power cap like the sustained cuBLAS loop the peak file
+            # holds beside the burst figure; a short one is compared with the burst figure.
+            sustained = ms > 100.0
+            ach, peak, runit, bound = (flops_l / per_launch_s / 1e12,
+                                       peaks["tensor_sustained"] if sustained else peaks["tensor"], "TFLOP/s", "tensor")
         path = {0: "auto", 1: "generic", 2: "decode_mma", 3: "tensor_tcgen05", 4: "gemv_dp4a"}[D.qmatmulPath(kind, M, Nl, K)]
         line = {
             "metric": metric_name(M), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
@@ -377,6 +383,9 @@ def main():
                          "traffic": traffic_for(args.workload) if world == 1 else None,
                          "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
                          else "fallback (no MEASURED_PEAKS.json)",
+                         "peak_kind": ("copy bandwidth" if bound == "hbm" else
+                                       ("sustained cuBLAS bf16 (timed region %.0f ms)" % ms if sustained
+                                        else "burst cuBLAS bf16 (timed region %.0f ms)" % ms)),
                          "frac_of_nominal": ach / (8000.0 if bound == "hbm" else 2250.0),
                          "algorithmic_per_launch": nbytes_l if bound == "hbm" else flops_l},
             "clocks": clocks,
