@@ -52,6 +52,7 @@
 //
 // Waits are time-bounded as in pipeline.cuh.
 #include <cuda_fp16.h>
+#include <cstdlib>
 
 #include "kernels.h"
 #include "pipeline.cuh"
@@ -401,7 +402,8 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   // activations' digit form alone takes most of a half SM.
   const bool solo = (xdig_bytes + xsc_bytes) > 48 * 1024 || N <= (int64_t)sms * 128;
   const int slots = solo ? sms : sms * kCtasPerSm;
-  const int budget = solo ? kSmemBudgetSolo : kSmemBudget;
+  int budget = solo ? kSmemBudgetSolo : kSmemBudget;
+  if (solo && getenv("SMITH_GEMV_SOLO_BUDGET")) budget = atoi(getenv("SMITH_GEMV_SOLO_BUDGET")) * 1024;
   // Tile width: the smallest width that covers N in a whole number of waves of resident CTAs.
   // A tile's group-row span must start and end on 16 bytes: any even width for 24-byte blocks,
   // a multiple of 8 for 34-byte blocks.
