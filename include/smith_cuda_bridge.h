@@ -196,6 +196,20 @@ int32_t smith_qmatmul_allgather(void* ctx, uint32_t kind, void* a, void* b, uint
                                 uint64_t n0, uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world,
                                 uint32_t rank, void* const* y_bufs, void* const* state_bufs, uint32_t target);
 int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
+/* Fused GEMV + all-reduce for weights sharded along K (M <= 4; the Wo / down projections of a
+ * tensor-parallel layer).  This rank multiplies its K-slice: a = [M, k_local] activations, b = its
+ * groups_local = k_local / 32 group-rows of all N columns (a contiguous byte range of the packed
+ * matrix).  Each CTA stores its tile of partial sums into this rank's partial buffer
+ * partial_bufs[rank] (2*M*N floats), flags the tile in every rank's state_bufs[r]
+ * (smith_qmatmul_allreduce_state_bytes bytes, zero-initialised once; local or IPC-imported), waits
+ * -- bounded, ~0.2 s -- for the same tile of all ranks, adds the partial tiles in rank order
+ * (identical bits on every rank) and writes the sum to out [M, N].  If a peer never arrives
+ * smith_kernel_status reports it.  Every rank must make the same sequence of calls.  Asynchronous;
+ * may be captured in a graph. */
+int32_t smith_qmatmul_allreduce(void* ctx, uint32_t kind, void* a, void* b, void* out, uint64_t M, uint64_t N,
+                                uint64_t k_local, uint64_t groups_local, uint32_t world, uint32_t rank,
+                                void* const* partial_bufs, void* const* state_bufs);
+uint64_t smith_qmatmul_allreduce_state_bytes(uint32_t kind, uint64_t M, uint64_t N, uint64_t k_local);
 
 /* No counterpart in the reference.  The same product as smith_qmatmul, for
  * callers that cannot allocate device memory when they make the call: a

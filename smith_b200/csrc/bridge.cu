@@ -902,6 +902,45 @@ int32_t smith_qmatmul_allgather(void* p, uint32_t kind, void* a, void* b, uint64
   return e == cudaSuccess ? 0 : fail("fused GEMV + all-gather launch failed: %s", cudaGetErrorString(e));
 }
 
+int32_t smith_qmatmul_allreduce(void* p, uint32_t kind, void* a, void* b, void* out, uint64_t M, uint64_t N,
+                                uint64_t k_local, uint64_t groups_local, uint32_t world, uint32_t rank,
+                                void* const* partial_bufs, void* const* state_bufs) {
+  Context* c = as_ctx(p);
+  Buffer *ba = as_buf(a), *bb = as_buf(b), *bo = as_buf(out);
+  if (!c || !ba || !bb || !bo) return 1;
+  if (kind != 4 && kind != 8) return fail("kind must be 4 or 8, got %u", kind);
+  if (world < 1 || world > 8 || rank >= world) return fail("smith_qmatmul_allreduce: world %u / rank %u out of range", world, rank);
+  if (!partial_bufs || !state_bufs) return fail("smith_qmatmul_allreduce: null buffer lists");
+  if (!ba->dev || !bb->dev || !bo->dev) return fail("smith_qmatmul_allreduce needs buffers with a device side");
+  const uint64_t blk = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  if (ba->bytes < M * k_local * 4 || bb->bytes < groups_local * N * blk || bo->bytes < M * N * 4)
+    return fail("smith_qmatmul_allreduce: buffer too small");
+  if (!qgemv_supports((int)kind, M, N, k_local, groups_local))
+    return fail("fused all-reduce is built into the GEMV kernel only (M <= 4, N %% 8 == 0, K %% 32 == 0); M=%llu N=%llu K=%llu",
+                (unsigned long long)M, (unsigned long long)N, (unsigned long long)k_local);
+  const int tiles = qgemv_tiles((int)kind, M, N, k_local);
+  GemvGather g{};
+  g.world = (int)world, g.rank = (int)rank, g.n0 = 0, g.n_total = (int64_t)N, g.target = 0, g.reduce = 1;
+  for (uint32_t r = 0; r < world; r++) {
+    Buffer *by = as_buf(partial_bufs[r]), *bs = as_buf(state_bufs[r]);
+    if (!by || !bs || !by->dev || !bs->dev) return fail("smith_qmatmul_allreduce: rank %u buffers have no device side", r);
+    if (by->bytes < 2 * M * N * 4 || bs->bytes < smith_qmatmul_allreduce_state_bytes(kind, M, N, k_local))
+      return fail("smith_qmatmul_allreduce: rank %u buffers too small", r);
+    g.y[r] = (float*)by->dev;
+    g.state[r] = (unsigned*)bs->dev;
+  }
+  (void)tiles;
+  cudaError_t e = launch_qgemv_gather((int)kind, (const float*)ba->dev, (const uint8_t*)bb->dev, (float*)bo->dev, M, N,
+                                      k_local, groups_local, &g, c->stream);
+  return e == cudaSuccess ? 0 : fail("fused GEMV + all-reduce launch failed: %s", cudaGetErrorString(e));
+}
+
+uint64_t smith_qmatmul_allreduce_state_bytes(uint32_t kind, uint64_t M, uint64_t N, uint64_t k_local) {
+  const int tiles = qgemv_tiles((int)kind, M, N, k_local);
+  if (tiles < 0) return 0;
+  return 16 + (uint64_t)2 * tiles * 8 * 4;      // control words + flags [2][tiles][8]
+}
+
 // ---------------------------------------------------------------- graphs
 int32_t smith_graph_begin(void* p) {
   Context* c = as_ctx(p);

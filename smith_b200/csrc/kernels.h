@@ -58,6 +58,10 @@ struct GemvGather {
   int world, rank;
   int64_t n0, n_total;
   unsigned target;      // CTAs (tiles) arriving per step, summed over ranks
+  // reduce != 0: weights are sharded along K instead; y[r] are the ranks' partial rows [2][M][N],
+  // state[r] continues with flags [2][tiles][8] after the four control words, and C receives the
+  // sum over ranks (n0 = 0, n_total = N, target unused).
+  int reduce;
 };
 cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                                 int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s);

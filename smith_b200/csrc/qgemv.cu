@@ -50,6 +50,16 @@
 //    because its step cannot complete without the other's arrivals), and the
 //    step number lives in device memory so that a captured graph can be replayed.
 //
+//    With weights sharded along K the same kernel ends in a fused all-reduce: a CTA stores its
+//    tile of partial sums into this rank's partial buffer, writes "tile t of step s is there" flags
+//    into every rank's flag array (remote stores), waits -- bounded -- for the flags of the same tile
+//    from all ranks (the ranks tile N identically), then reads the peers' partial tiles over NVLink,
+//    adds them in rank order (so every rank gets the same bits) and writes the finished tile.
+//    Tile-level flags mean a CTA waits only for the CTAs that work on its columns elsewhere, which
+//    run at the same time.  Partial buffers and flags are double-buffered by step parity; a rank
+//    writes them only after its previous launch has completed (griddepcontrol.wait), so it cannot
+//    run further than one step ahead of a peer that still reads them.
+//
 // Waits are time-bounded as in pipeline.cuh.
 #include <cuda_fp16.h>
 
@@ -61,8 +71,10 @@ namespace {
 
 constexpr int kMaxRowsM = 4;
 constexpr int kMaxPeers = 8;
-constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage (fewer, larger stages
-                                           // measured faster than more, smaller ones)
+constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage: fewer, larger stages measured
+                                           // faster than more, smaller ones (4096 x 14336 Q4: 9.4 us at 4 rows,
+                                           // 11.3 at 2, 16.4 at 1, ring depth in bytes equal); 3 where 4 would
+                                           // leave fewer than four stages (Q8's wider rows: 12.3 -> 11.8 us)
 constexpr int kMaxStages = 8;
 constexpr int kHeader = 256;               // barriers + abort flag
 constexpr int kSmemBudget = 110 * 1024;    // per CTA: two CTAs share an SM
@@ -86,6 +98,9 @@ struct Params {
   unsigned* state[kMaxPeers];
   int world, rank, n0, n_total;
   unsigned target;  // tiles that arrive per step, summed over all ranks
+  // Fused all-reduce instead (weights sharded along K): y[r] holds rank r's PARTIAL rows [2][M][N],
+  // state[r] continues after its four control words with flags [2][tiles][kMaxPeers]; C gets the sum.
+  int reduce;
 };
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) {
@@ -216,7 +231,7 @@ __device__ __forceinline__ void block_dot(const uint8_t* __restrict__ blk, uint3
   }
 }
 
-template <int KIND, int MR>
+template <int KIND, int MR, int RPP>
 __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_kernel(const Params p) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -305,14 +320,14 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
       const int g0 = st * p.stage_rows + phase;
       if (st * p.stage_rows + p.stage_rows <= p.G) {
 #pragma unroll
-        for (int rr = 0; rr < kRowsPerPhase; rr++) {
+        for (int rr = 0; rr < RPP; rr++) {
           const int row = phase + rr * p.phases;
           const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)col * BB;
           const int g = g0 + rr * p.phases;
           block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, p.G, acc);
         }
       } else {
-        for (int rr = 0; rr < kRowsPerPhase; rr++) {
+        for (int rr = 0; rr < RPP; rr++) {
           const int row = phase + rr * p.phases;
           const int g = g0 + rr * p.phases;
           if (g < p.G) {
@@ -344,8 +359,71 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     }
     return;
   }
-  // ---------------------------------------------- fused all-gather over peer memory
   const unsigned par = step & 1u;
+  if (p.reduce) {
+    // -------------------------------------------- fused all-reduce over peer memory
+    const size_t half = (size_t)par * p.M * p.N;
+    float* mine_y = p.y[p.rank] + half;
+    for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+      const int m = i / tn, c = i - m * tn;
+      float sum = 0.f;
+      for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
+      mine_y[(size_t)m * p.N + col0 + c] = sum;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // the partial tile is stored
+    const size_t flag_at = 4 + ((size_t)par * gridDim.x + blockIdx.x) * kMaxPeers;
+    int* wait_ok = reinterpret_cast<int*>(smem + 2 * kMaxStages * 8 + 8);
+    if (tid == 0) *wait_ok = 1;
+    if (tid < p.world) {
+      __threadfence_system();                             // partial tile before the flag, system-wide
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.state[tid] + flag_at + p.rank), "r"(step + 1u)
+                   : "memory");
+      // this rank's flags from rank `tid`, polled in local memory
+      const unsigned* f = p.state[p.rank] + flag_at + tid;
+      const long long t0 = clock64();
+      bool there = false;
+      for (unsigned spin = 0;; spin++) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+        if (seen >= step + 1u) {
+          there = true;
+          break;
+        }
+        if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) break;
+      }
+      if (!there) {
+        *wait_ok = 0;
+        atomicExch(p.status, 1);                          // a peer never arrived: the result is not valid
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+    if (*reinterpret_cast<volatile int*>(wait_ok)) {
+      for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+        const int m = i / tn, c = i - m * tn;
+        const size_t at = half + (size_t)m * p.N + col0 + c;
+        float sum = 0.f;
+        for (int r = 0; r < p.world; r++) {
+          float v;                                        // volatile: never a line cached two steps ago
+          asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p.y[r] + at) : "memory");
+          sum += v;
+        }
+        p.C[(size_t)m * p.N + col0 + c] = sum;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+    if (tid == 0) {
+      unsigned* mine = p.state[p.rank];
+      __threadfence();
+      const unsigned ticket = atomicAdd(mine + 1, 1u);
+      if (ticket == gridDim.x - 1) {                      // last CTA of this rank's grid
+        mine[1] = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(mine) = step + 1u;
+      }
+    }
+    return;
+  }
+  // ---------------------------------------------- fused all-gather over peer memory
   for (int i = tid; i < p.M * tn; i += nwarps * 32) {
     const int m = i / tn, c = i - m * tn;
     float sum = 0.f;
@@ -383,6 +461,7 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
 struct Plan {
   Params p;
   int tiles;
+  int rpp;                // group-rows per phase and stage (template argument of the kernel)
   size_t smem;
   bool ok;
 };
@@ -414,26 +493,32 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   p.TN = TN;
   pl.tiles = (int)((N + TN - 1) / TN);
   // Phases: a multiple of 4 (so TN * phases fills whole warps), aiming at kMaxConsumerThreads.
-  int phases = (kMaxConsumerThreads / TN) & ~3;
-  if (phases < 4) phases = 4;
-  while (phases > 4 && (phases * kRowsPerPhase > p.G * 2)) phases -= 4;  // short K: do not over-split
-  p.phases = phases;
-  p.nthreads = TN * phases;
-  p.row_pitch = TN * BB;
-  p.stage_rows = phases * kRowsPerPhase;
-  p.stage_bytes = ((p.stage_rows * p.row_pitch + 15) / 16) * 16;
-  p.xdig_off = kHeader;
-  p.xsc_off = p.xdig_off + xdig_bytes;
-  p.ring_off = ((p.xsc_off + xsc_bytes + 1023) / 1024) * 1024;
-  // A one-CTA-per-SM tile whose whole K-slice fits a half-SM ring needs no more than that: the
-  // smaller footprint lets the next launch's CTA move in beside it (programmatic dependent launch),
-  // so start-up and tail of back-to-back launches overlap (4096 x 4096: 6.6 -> 5.6 us).
-  if (solo && (int64_t)p.G * p.row_pitch <= (int64_t)(kSmemBudget - p.ring_off - 64) &&
-      (kSmemBudget - p.ring_off - 64) / p.stage_bytes >= 2)
-    budget = kSmemBudget;
-  const int room = budget - p.ring_off - 64;
-  int stages = room / p.stage_bytes;
-  if (stages > kMaxStages) stages = kMaxStages;
+  int phases = 0, stages = 0;
+  for (pl.rpp = kRowsPerPhase; pl.rpp >= kRowsPerPhase - 1; pl.rpp--) {
+    phases = (kMaxConsumerThreads / TN) & ~3;
+    if (phases < 4) phases = 4;
+    while (phases > 4 && (phases * pl.rpp > p.G * 2)) phases -= 4;  // short K: do not over-split
+    p.phases = phases;
+    p.nthreads = TN * phases;
+    p.row_pitch = TN * BB;
+    p.stage_rows = phases * pl.rpp;
+    p.stage_bytes = ((p.stage_rows * p.row_pitch + 15) / 16) * 16;
+    p.xdig_off = kHeader;
+    p.xsc_off = p.xdig_off + xdig_bytes;
+    p.ring_off = ((p.xsc_off + xsc_bytes + 1023) / 1024) * 1024;
+    // A one-CTA-per-SM tile whose whole K-slice fits a half-SM ring needs no more than that: the
+    // smaller footprint lets the next launch's CTA move in beside it (programmatic dependent launch),
+    // so start-up and tail of back-to-back launches overlap (4096 x 4096: 6.6 -> 5.6 us).
+    int budget_here = budget;
+    if (solo && (int64_t)p.G * p.row_pitch <= (int64_t)(kSmemBudget - p.ring_off - 64) &&
+        (kSmemBudget - p.ring_off - 64) / p.stage_bytes >= 2)
+      budget_here = kSmemBudget;
+    const int room = budget_here - p.ring_off - 64;
+    stages = room / p.stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages >= 4 || (int64_t)stages * p.stage_rows >= p.G) break;   // deep enough, or the ring holds all of K
+  }
+  if (pl.rpp < kRowsPerPhase - 1) pl.rpp = kRowsPerPhase - 1;
   p.stages = stages;
   const size_t red = (size_t)phases * MR * TN * 4;
   const size_t ring = (size_t)(stages > 0 ? stages : 0) * p.stage_bytes + 64;
@@ -442,12 +527,12 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   return pl;
 }
 
-template <int KIND, int MR>
+template <int KIND, int MR, int RPP>
 cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
-        cudaFuncSetAttribute(qgemv_kernel<KIND, MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(qgemv_kernel<KIND, MR, RPP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured = true;
   }
@@ -462,7 +547,7 @@ cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR>, pl.p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR, RPP>, pl.p);
   count_launch();
   return e;
 }
@@ -502,6 +587,8 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
     if (g->world < 1 || g->world > kMaxPeers || g->rank < 0 || g->rank >= g->world) return cudaErrorInvalidValue;
     pl.p.world = g->world, pl.p.rank = g->rank, pl.p.n0 = (int)g->n0, pl.p.n_total = (int)g->n_total;
     pl.p.target = g->target;
+    pl.p.reduce = g->reduce;
+    if (g->reduce && !C) return cudaErrorInvalidValue;
     for (int r = 0; r < g->world; r++) {
       pl.p.y[r] = g->y[r];
       pl.p.state[r] = g->state[r];
@@ -509,7 +596,7 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
     }
   }
 #define SMITH_GEMV_CASE(KD, MRV) \
-  if (kind == KD && M == MRV) return launch_one<KD, MRV>(pl, s);
+  if (kind == KD && M == MRV) return pl.rpp == 3 ? launch_one<KD, MRV, 3>(pl, s) : launch_one<KD, MRV, 4>(pl, s);
   SMITH_GEMV_CASE(4, 1) SMITH_GEMV_CASE(4, 2) SMITH_GEMV_CASE(4, 3) SMITH_GEMV_CASE(4, 4)
   SMITH_GEMV_CASE(8, 1) SMITH_GEMV_CASE(8, 2) SMITH_GEMV_CASE(8, 3) SMITH_GEMV_CASE(8, 4)
 #undef SMITH_GEMV_CASE

@@ -89,6 +89,9 @@ SYMBOLS = {
     "smith_ipc_import": (_p, [_p, _p, _u64]),
     "smith_qmatmul_allgather": (_i32, [_p, _u32, _p, _p, _u64, _u64, _u64, _u64, _u64, _u64, _u32, _u32,
                                         C.POINTER(_p), C.POINTER(_p), _u32]),
+    "smith_qmatmul_allreduce": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32, _u32, C.POINTER(_p),
+                                       C.POINTER(_p)]),
+    "smith_qmatmul_allreduce_state_bytes": (_u64, [_u32, _u64, _u64, _u64]),
     "smith_qgemv_tiles": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_kernel_status": (_i32, [_p]),
     "smith_launch_count": (_u64, [_p]),
@@ -411,6 +414,18 @@ def qmatmulAllGather(kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, w
     ss = (_p * world)(*stateBuffers)
     _check(lib.smith_qmatmul_allgather(ctx(), kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank,
                                        ys, ss, target), "qmatmul_allgather")
+
+
+def qmatmulAllReduce(kind, aBuffer, bBuffer, outBuffer, M, N, kLocal, groupsLocal, world, rank, partialBuffers,
+                     stateBuffers):
+    ps = (_p * world)(*partialBuffers)
+    ss = (_p * world)(*stateBuffers)
+    _check(lib.smith_qmatmul_allreduce(ctx(), kind, aBuffer, bBuffer, outBuffer, M, N, kLocal, groupsLocal, world,
+                                       rank, ps, ss), "qmatmul_allreduce")
+
+
+def qmatmulAllReduceStateBytes(kind, M, N, kLocal):
+    return int(lib.smith_qmatmul_allreduce_state_bytes(kind, M, N, kLocal))
 
 
 def kernelStatus():

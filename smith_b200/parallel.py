@@ -166,6 +166,108 @@ class FusedGather:
         self.ys = self.states = []
 
 
+class FusedReduce:
+    """Sum over ranks of K-sharded partial products, formed by the GEMV kernel itself (M <= 4): every
+    rank's kernel flags each finished tile of partial sums in every rank's flag array, then reads
+    the peers' tiles through peer-mapped memory and adds them in rank order.  No NCCL call on the
+    data path; capturable in a CUDA graph; every rank ends with the same bits.
+
+    Owns this rank's partial buffer (two halves used alternately) and its state block, and holds
+    IPC mappings of the other ranks'."""
+    capturable = True
+    kernels_per_call = 0    # the reduction is part of the matmul launch
+
+    def __init__(self, kind, M, N, k_local, world, rank, group=None):
+        from . import device as D
+        self.kind, self.M, self.N, self.k_local, self.world, self.rank = kind, M, N, k_local, world, rank
+        sbytes = D.qmatmulAllReduceStateBytes(kind, M, N, k_local)
+        if sbytes == 0:
+            raise D.SmithError("smith: the GEMV kernel does not take this shard shape")
+        self.partial = D.alloc(2 * M * N * 4, D.PRIVATE)
+        self.state = D.alloc(sbytes, D.PRIVATE)
+        D.upload(self.state, np.zeros(sbytes // 4, np.uint32))
+        D.upload(self.partial, np.zeros(2 * M * N, np.float32))
+        self.partials, self.states = [None] * world, [None] * world
+        self.partials[rank], self.states[rank] = self.partial, self.state
+        if world > 1:
+            import torch.distributed as dist
+            mine = (D.ipcExport(self.partial), D.ipcExport(self.state))
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+            for r in range(world):
+                if r != rank:
+                    self.partials[r] = D.ipcImport(handles[r][0], 2 * M * N * 4)
+                    self.states[r] = D.ipcImport(handles[r][1], sbytes)
+            dist.barrier(group=group)     # everyone has mapped everyone before the first flag is written
+
+    def enqueue(self, a_buf, packed_shard_buf, out_buf):
+        from . import device as D
+        D.qmatmulAllReduce(self.kind, a_buf, packed_shard_buf, out_buf, self.M, self.N, self.k_local,
+                           self.k_local // 32, self.world, self.rank, self.partials, self.states)
+
+    def close(self):
+        from . import device as D
+        for r in range(self.world):
+            if r != self.rank and self.partials[r]:
+                D.releaseBuffer(self.partials[r])
+                D.releaseBuffer(self.states[r])
+        D.releaseBuffer(self.partial)
+        D.releaseBuffer(self.state)
+        self.partials = self.states = []
+
+
+class KShardedMatmul:
+    """y = a @ dequant(W) with W sharded along K over the process group (the Wo / down projections
+    of a tensor-parallel layer): rank r holds group-rows ``group_shard(K / 32, P, r)`` of all N
+    columns and multiplies the matching K-slice of the activations; the partial [M, N] products are
+    summed over ranks -- inside the GEMV kernel for M <= 4, by an NCCL all-reduce otherwise.
+    The summation order differs from the single-device sequential one, so results agree with it to
+    the stated tolerance, not bitwise."""
+
+    def __init__(self, kind, K, N, packed_shard_buffer, M, world, rank):
+        import torch
+        from . import device as D
+        self.kind, self.K, self.N, self.M, self.world, self.rank = kind, K, N, M, world, rank
+        g0, g1 = group_shard(K // 32, world, rank)
+        self.k0, self.k1 = g0 * 32, g1 * 32
+        self.kl = self.k1 - self.k0
+        self.packed = packed_shard_buffer
+        shapes = [(b - a) * 32 for a, b in (group_shard(K // 32, world, r) for r in range(world))]
+        # the fused form needs the same tiling of N on every rank: equal K-slices and a GEMV-shaped M
+        self.fused = M <= 4 and len(set(shapes)) == 1 and D.qgemvTiles(kind, M, N, self.kl) > 0
+        self.a_dev = D.alloc(M * self.kl * 4, D.PRIVATE)
+        if self.fused:
+            self.reduce = FusedReduce(kind, M, N, self.kl, world, rank)
+            self.out = D.alloc(M * N * 4, D.PRIVATE)
+        else:
+            self.reduce = None
+            self.out_t = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+            self.out = D.wrapDeviceMemory(self.out_t.data_ptr(), M * N * 4)
+            self.stream = torch.cuda.ExternalStream(D.stream())
+
+    def enqueue(self, a_dev=None):
+        """Asynchronous: this rank's partial product and the sum over ranks into ``self.out``."""
+        import torch
+        from . import device as D
+        if self.fused:
+            self.reduce.enqueue(a_dev or self.a_dev, self.packed, self.out)
+            return
+        D.qmatmul(self.kind, a_dev or self.a_dev, self.packed, self.out, self.M, self.N, self.kl, self.kl // 32,
+                  D.PATH_AUTO)
+        with torch.cuda.stream(self.stream):
+            reduce_partials(self.out_t)
+
+    def forward(self, a_host):
+        """End to end from host memory: ``a_host`` is the full [M, K] activation matrix; this rank
+        uploads its K-slice, computes, reduces, and downloads the full [M, N] result."""
+        from . import device as D
+        a = np.ascontiguousarray(np.asarray(a_host, dtype=np.float32)[:, self.k0:self.k1])
+        D.upload(self.a_dev, a)
+        self.enqueue()
+        D.synchronize()
+        return D.download(self.out, self.M * self.N * 4, np.float32).reshape(self.M, self.N)
+
+
 class ShardedMatmul:
     """y = a @ dequant(W) with W N-sharded over the process group: the multi-GPU
     counterpart of matmulQ4 / matmulQ8 for one weight matrix."""

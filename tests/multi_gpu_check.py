@@ -3,8 +3,10 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 tests/multi_gpu_check.py
 
 Every rank multiplies its column shard; the output row is gathered either inside the GEMV
-kernel (peer stores over NVLink, M <= 4) or by NCCL (wider M).  Rank 0 compares the gathered
-rows of every rank-visible result with the CPU oracle.  Ranks only ever leave between steps."""
+kernel (peer stores over NVLink, M <= 4) or by NCCL (wider M).  Then the same for weights
+sharded along K, where the partial products are summed inside the GEMV kernel (peer loads,
+M <= 4) or by an NCCL all-reduce.  Every rank compares its result with the CPU oracle.
+Ranks only ever leave between steps."""
 import os
 import sys
 
@@ -53,6 +55,41 @@ def main():
         if rank == 0:
             print(f"world={world} kind={knd} M={M} K={K} N={N} fused={sm.fused}: worst err/bound {worst_all:.3f} "
                   f"failures(all ranks)={int(flag.item())}", flush=True)
+        dist.barrier()
+    # ---- weights sharded along K, partial products summed over ranks
+    for kind, M, K, N in [(4, 1, 4096, 4096), (8, 2, 2048, 1024), (4, 4, 14336, 4096), (4, 16, 2048, 1024)]:
+        knd, bb = ("q4", 24) if kind == 4 else ("q8", 34)
+        rng = np.random.default_rng(4321 + M + N)
+        w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+        packed = O.quantize_q4(w) if kind == 4 else O.quantize_q8(w)
+        g0, g1 = P.group_shard(K // 32, world, rank)
+        shard = D.alloc((g1 - g0) * N * bb, D.PRIVATE)
+        D.upload(shard, P.slice_packed_groups(packed, K // 32, N, bb, g0, g1))
+        km = P.KShardedMatmul(kind, K, N, shard, M, world, rank)
+        worst_all, same = 0.0, 1
+        for step in range(3):
+            a = rng.standard_normal((M, K)).astype(np.float32)
+            got = km.forward(a)
+            assert D.kernelStatus() == 0, "a bounded device-side wait gave up"
+            want = O.matmul(a, packed, K, N, knd, threads=O.max_threads())
+            ok, worst = within_tolerance(got, want, a, packed, K, N, knd, 1e-3)
+            worst_all = max(worst_all, worst)
+            if not ok:
+                failures += 1
+            if km.fused:                                      # rank-ordered sums: the same bits everywhere
+                mine = torch.from_numpy(got.view(np.int32).astype(np.int64)).cuda()
+                lo, hi = mine.clone(), mine.clone()
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                same &= int(torch.equal(lo, hi))
+        if not same:
+            failures += 1
+        flag = torch.tensor([failures], device="cuda")
+        dist.all_reduce(flag)
+        if rank == 0:
+            print(f"world={world} K-sharded kind={knd} M={M} K={K} N={N} fused={km.fused}: worst err/bound "
+                  f"{worst_all:.3f} identical on all ranks={bool(same)} failures(all ranks)={int(flag.item())}",
+                  flush=True)
         dist.barrier()
     dist.destroy_process_group()
     sys.exit(1 if failures else 0)

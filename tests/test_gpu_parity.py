@@ -367,6 +367,79 @@ def test_fused_gather_two_shards_emulated_on_one_gpu():
         b.free()
 
 
+# ------------------------------------------------------------------ fused all-reduce epilogue (one GPU)
+def test_fused_reduce_world_of_one_and_alternating_halves():
+    from smith_b200.parallel import FusedReduce
+    K, N, M = 2048, 1024, 2
+    rng = np.random.default_rng(31)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    packed = O.quantize_q4(w)
+    pb = DevBuf.of(packed)
+    out = DevBuf.of(np.zeros(M * N, np.float32))
+    fr = FusedReduce(4, M, N, K, 1, 0)
+    for call in range(3):                                   # halves 0, 1, 0; flags keep counting
+        a = rng.standard_normal((M, K)).astype(np.float32)
+        ab = DevBuf.of(a)
+        fr.enqueue(ab.handle, pb.handle, out.handle)
+        device.synchronize()
+        assert device.kernelStatus() == 0
+        want = matmul_on_device(a, packed, K, N, "q4", device.PATH_GEMV)
+        got = out.get(np.float32).reshape(M, N)
+        assert np.array_equal(got, want)                    # 0 + x: the one partial, unchanged
+        ab.free()
+    assert device.download(fr.state, 16, np.uint32)[0] == 3    # three steps completed
+    fr.close()
+    for b in (pb, out):
+        b.free()
+
+
+def test_fused_reduce_two_k_shards_with_a_preseeded_peer():
+    # Rank 0 of a world of two runs alone on this GPU.  Its peer's partial rows and "tile is there"
+    # flags are written by the host beforehand, so the launch never waits on another launch (two
+    # kernels that wait on each other must never share a GPU); what is checked is rank 0's side of
+    # the protocol: partial tile stored, flags written to both ranks, peers' partials added in rank order.
+    from smith_b200 import parallel as P
+    K, N, M, world = 2048, 1536, 3, 2
+    rng = np.random.default_rng(32)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    packed = O.quantize_q8(w)
+    G = K // 32
+    g0, g1 = P.group_shard(G, world, 0)
+    h0, h1 = P.group_shard(G, world, 1)
+    kl = (g1 - g0) * 32
+    peer_partial = O.matmul(a[:, h0 * 32:h1 * 32], P.slice_packed_groups(packed, G, N, 34, h0, h1), (h1 - h0) * 32, N, "q8")
+    sbytes = device.qmatmulAllReduceStateBytes(8, M, N, kl)
+    tiles = device.qgemvTiles(8, M, N, kl)
+    assert sbytes == 16 + 2 * tiles * 8 * 4
+    mine_state = np.zeros(sbytes // 4, np.uint32)
+    flags = mine_state[4:].reshape(2, tiles, 8)
+    flags[:, :, 1] = 0x7fffffff                             # the peer's tiles of every step "are there"
+    partials = [DevBuf.of(np.zeros(2 * M * N, np.float32)),
+                DevBuf.of(np.concatenate([peer_partial.reshape(-1), peer_partial.reshape(-1)]).astype(np.float32))]
+    states = [DevBuf.of(mine_state), DevBuf.of(np.zeros(sbytes // 4, np.uint32))]
+    ab = DevBuf.of(np.ascontiguousarray(a[:, g0 * 32:g1 * 32]))
+    shard = DevBuf.of(P.slice_packed_groups(packed, G, N, 34, g0, g1))
+    out = DevBuf.of(np.zeros(M * N, np.float32))
+    want = matmul_on_device(a, packed, K, N, "q8", device.PATH_GENERIC)
+    for call in range(2):                                   # both halves
+        device.qmatmulAllReduce(8, ab.handle, shard.handle, out.handle, M, N, kl, kl // 32, world, 0,
+                                [b.handle for b in partials], [b.handle for b in states])
+        device.synchronize()
+        assert device.kernelStatus() == 0
+        got = out.get(np.float32).reshape(M, N)
+        ok, worst = within_tolerance(got, want, a, packed, K, N, "q8", REL)
+        assert ok, (call, worst)
+        own = partials[0].get(np.float32).reshape(2, M, N)[call]
+        assert np.array_equal(got, own + peer_partial)      # rank order: own partial first, then the peer's
+        peer_flags = states[1].get(np.uint32)[4:].reshape(2, tiles, 8)
+        assert (peer_flags[call, :, 0] == call + 1).all()   # rank 0 announced every tile of this step to its peer
+        assert (states[0].get(np.uint32)[4:].reshape(2, tiles, 8)[call, :, 0] == call + 1).all()
+    assert states[0].get(np.uint32)[0] == 2                 # two steps completed
+    for b in partials + states + [ab, shard, out]:
+        b.free()
+
+
 # ------------------------------------------------------------------ full-size projection shapes, sampled columns
 # BASELINE configs 4 and 5: every Q4 linear projection of a Llama-3-8B-shaped and a 70B-shaped decode
 # step.  Weights are generated and packed on the device at full size; a window of columns is
