@@ -52,6 +52,9 @@ WORKLOADS = {
     "q4_gemv_4096x4096_m1": dict(kind=4, M=1, K=4096, N=4096, std=0.02),            # configs[0]
     "q4_lm_head_4096x128256_m1": dict(kind=4, M=1, K=4096, N=128256, std=0.02),
     "q8_decode_gemv_4096x14336_m1": dict(kind=8, M=1, K=4096, N=14336, std=0.02),
+    # BASELINE configs[3]: every Q4 projection of an 8B-Llama-shaped decode step (32 layers + lm_head, 5.63 GB)
+    "q4_llama8b_step_m1": dict(kind=4, M=1, step=dict(layers=32, dim=4096, kv=1024, ffn=14336, vocab=128256), std=0.02,
+                               K=4096, N=14336),
 }
 DEFAULT = "q4_decode_gemv_4096x14336_m1"
 L2_BYTES = 126e6
@@ -192,6 +195,215 @@ def run_reference_arm(args, wl, name):
     print(json.dumps(line))
 
 
+# ----------------------------------------------------------------------------- decode-step workload
+def run_step_workload(args, wl):
+    """One decode step's projection list (no pointwise glue): per layer wq, wk, wv, wo, gate, up, down,
+    then lm_head: 225 matmuls over 5.63 GB of distinct packed weights (larger than L2 by itself),
+    issued as 129 launches (wq/wk/wv share one, gate/up share one).  N > 1: tensor parallel -- wq/wk/wv/gate/up column-sharded (outputs stay sharded), wo/down
+    sharded along K with the all-reduce fused into the GEMV kernel, lm_head column-sharded with the
+    all-gather fused into the GEMV kernel."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import smith_b200 as smith
+    from smith_b200 import device as D
+    from smith_b200 import parallel as P
+    kind, M, st = wl["kind"], wl["M"], wl["step"]
+    dim, kv, ffn, vocab, layers = st["dim"], st["kv"], st["ffn"], st["vocab"], st["layers"]
+    bb = 24
+    D.ctx()
+    stream = torch.cuda.ExternalStream(D.stream())
+    steps = min(args.steps, 200)
+    warm = max(min(args.warmup, 10), 3)
+
+    def shard_n(N):
+        a, b = P.column_shard(N, world, rank)
+        return b - a
+
+    def shard_k(K):
+        g0, g1 = P.group_shard(K // 32, world, rank)
+        return (g1 - g0) * 32
+
+    # (name, K_local, N_local, K_full, N_full, collective)
+    per_layer = [("wq", dim, shard_n(dim), dim, dim, None), ("wk", dim, shard_n(kv), dim, kv, None),
+                 ("wv", dim, shard_n(kv), dim, kv, None), ("wo", shard_k(dim), dim, dim, dim, "reduce"),
+                 ("gate", dim, shard_n(ffn), dim, ffn, None), ("up", dim, shard_n(ffn), dim, ffn, None),
+                 ("down", shard_k(ffn), dim, ffn, dim, "reduce")]
+    head = ("lm_head", dim, shard_n(vocab), dim, vocab, "gather")
+    biggest = max(k * n for _, k, n, _, _, _ in per_layer + [head])
+    wtmp = D.alloc(biggest * 4, D.PRIVATE)
+    seed = [17 + rank]
+
+    def make(kl, nl):
+        D.fillNormal(wtmp, kl * nl, seed[0], wl["std"])
+        seed[0] += world
+        pk = D.alloc((kl // 32) * nl * bb, D.PRIVATE)
+        D.q4Pack(wtmp, pk, kl, nl)
+        return pk
+
+    x_dim = D.alloc(M * dim * 4, D.PRIVATE)          # activations of width dim / ffn (synthetic, replicated)
+    x_ffn = D.alloc(M * ffn * 4, D.PRIVATE)
+    D.fillNormal(x_dim, M * dim, 7, 1.0)
+    D.fillNormal(x_ffn, M * ffn, 8, 1.0)
+    y = D.alloc(M * max(ffn, dim, shard_n(vocab)) * 4, D.PRIVATE)
+    y2 = [D.alloc(M * max(ffn, dim) * 4, D.PRIVATE) for _ in range(2)]     # second and third output of a shared launch
+    ops, weight_bytes, alg_bytes = [], 0, 0
+    reducers = {}
+    # projections that read the same activations go out as one launch (smith_qmatmul_multi)
+    shared = {"wq": "qkv", "wk": "qkv", "wv": "qkv", "gate": "gate_up", "up": "gate_up"}
+    for layer in range(layers):
+        open_group = None
+        for name, kl, nl, kf, nf, coll in per_layer:
+            pk = make(kl, nl)
+            weight_bytes += (kl // 32) * nl * bb
+            alg_bytes += (kl // 32) * nl * bb + 4 * M * kl + 4 * M * nl
+            grp = shared.get(name)
+            if grp and open_group and open_group[0] == grp:
+                open_group[1].append(pk)
+                open_group[3].append(nl)
+                continue
+            open_group = (grp or name, [pk], kl, [nl], coll)
+            ops.append(open_group)
+    pk = make(head[1], head[2])
+    weight_bytes += (head[1] // 32) * head[2] * bb
+    alg_bytes += (head[1] // 32) * head[2] * bb + 4 * M * head[1] + 4 * M * head[2]
+    ops.append((head[0], [pk], head[1], [head[2]], head[5]))
+    D.synchronize()
+    D.releaseBuffer(wtmp)
+    if world > 1:
+        reducers["wo"] = P.FusedReduce(kind, M, dim, shard_k(dim), world, rank)
+        reducers["down"] = P.FusedReduce(kind, M, dim, shard_k(ffn), world, rank)
+        gather = P.FusedGather(M, vocab, world, rank)
+
+    def one_pass():
+        for name, pks, kl, nls, coll in ops:
+            src = x_ffn if name == "down" else x_dim       # the K-slice a rank reads is the head of the buffer
+            if world > 1 and coll == "reduce":
+                reducers[name].enqueue(src, pks[0], y)
+            elif world > 1 and coll == "gather":
+                gather.enqueue(kind, src, pks[0], kl)
+            elif len(pks) > 1:
+                D.qmatmulMulti(kind, src, pks, ([y] + y2)[:len(pks)], nls, M, kl, kl // 32)
+            else:
+                D.qmatmul(kind, src, pks[0], y, M, nls[0], kl, kl // 32, D.PATH_AUTO)
+
+    def barrier():
+        D.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    one_pass()
+    D.synchronize()
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up during warm-up")
+    D.graphBegin()
+    one_pass()
+    graph = D.graphEnd()
+    for _ in range(warm):
+        D.graphLaunch(graph)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        D.graphLaunch(graph)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # ---- end to end: the step's input row from page-locked host memory, all projections, the logits back
+    x_host = smith.tensorFrom(D.download(x_dim, M * dim * 4, np.float32), [M, dim])
+    x_np = smith.toNumpy(x_host)
+    n_logits = M * (vocab if world > 1 else head[2])
+
+    def e2e_pass():
+        D.upload(x_dim, x_np)
+        D.graphLaunch(graph)
+        D.synchronize()
+        if world > 1:
+            return gather.read((gather.calls - 1) & 1)
+        return D.download(y, n_logits * 4, np.float32)
+
+    for _ in range(2):
+        e2e_pass()
+    barrier()
+    e2e_steps = max(3, min(steps, 50))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up: results invalid")
+    if world > 1:
+        tot = torch.tensor([float(alg_bytes)], device="cuda")
+        dist.all_reduce(tot)
+        alg_all = float(tot.item())
+    else:
+        alg_all = float(alg_bytes)
+    if rank == 0:
+        step_s = ms * 1e-3 / steps
+        peaks = measured_peaks()
+        ach = alg_bytes / step_s / 1e9                       # this rank's kernels against this GPU's HBM
+        line = {
+            "metric": "Q4 decode step HBM GB/s (algorithmic bytes of all projections / time)",
+            "value": alg_all / step_s / 1e9, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32 accumulate over u4 codes", "data": "synthetic",
+            "config": {"workload": args.workload, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv,
+                       "ffn": ffn, "vocab": vocab, "matmuls_per_step": 7 * layers + 1, "launches_per_step": len(ops),
+                       "packed_bytes_per_gpu": weight_bytes, "tokens_per_s": M / step_s,
+                       "sharding": ("tensor parallel over %d GPUs: wq/wk/wv/gate/up column-sharded, wo/down K-sharded "
+                                    "with the all-reduce fused into the GEMV kernel, lm_head column-sharded with the "
+                                    "all-gather fused into the GEMV kernel" % world) if world > 1 else "single GPU",
+                       "l2": "every launch reads its own packed matrix; one step's weights are 45 x the 126 MB L2",
+                       "timing": "CUDA events on the launch stream around replays of one CUDA graph per step, "
+                                 "max over ranks"},
+            "e2e": {"value": alg_all / (e2e_s / e2e_steps) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * M * dim * world,
+                    "d2h_bytes_per_step": 4 * n_logits * world, "steps": e2e_steps,
+                    "note": "per step: H2D of the input row from page-locked memory, graph launch, wait, D2H of the logits"},
+            "gpu_launches": int((steps + e2e_steps) * len(ops)),
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s", "frac": ach / peaks["hbm"],
+                         "traffic": None,
+                         "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
+                         else "fallback (no MEASURED_PEAKS.json)",
+                         "peak_kind": "copy bandwidth", "frac_of_nominal": ach / 8000.0,
+                         "algorithmic_per_launch": alg_bytes / len(ops),
+                         "note": "all %d launches of a step taken together (the GEMV kernel throughout)" % len(ops)},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            per_call, threads, ckind, sample = cpu_run(kind, M, dim, ffn, seconds=args.cpu_seconds)
+            gate_bytes = algorithmic(kind, M, dim, ffn)[0]
+            line["cpu_baseline"] = {"value": gate_bytes / per_call / 1e9, "unit": "GB/s", "cores": threads, "kind": ckind,
+                                    "sample": "the step's gate projection (4096 x 14336): " + sample}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -206,6 +418,8 @@ def main():
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         return run_reference_arm(args, wl, args.workload)
+    if "step" in wl:
+        return run_step_workload(args, wl)
 
     import numpy as np
     import torch

@@ -167,6 +167,14 @@ int32_t smith_q8_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
 int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint64_t M, uint64_t N,
                       uint64_t K, uint64_t groups, uint32_t path);
 /* Which path 0 would resolve to for a shape (for tests and reports). */
+/* No counterpart in the reference, whose callers issue one matmul per weight matrix
+ * (src/gguf_cache.js:121-171: wq, wk, wv on the same input; gate and up on the same input).
+ * c_bufs[i] [M, n_list[i]] = a [M, K] x dequant(b_bufs[i]) for 1 to 4 packed matrices of the same K
+ * and kind.  For M <= 4 they run as ONE launch of the GEMV kernel (its grid covers the tiles of all
+ * matrices), which saves the start-up and tail of the launches it replaces; other shapes fall
+ * back to one launch per matrix.  Results are those of smith_qmatmul per matrix. */
+int32_t smith_qmatmul_multi(void* ctx, uint32_t kind, void* a, uint32_t count, void* const* b_bufs,
+                            void* const* c_bufs, const uint64_t* n_list, uint64_t M, uint64_t K, uint64_t groups);
 int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
 /* Device-side waits in these kernels (on a shared-memory barrier, a peer's
  * flag) are bounded; one that gives up marks the launch's result invalid.

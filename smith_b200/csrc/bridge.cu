@@ -791,6 +791,40 @@ int32_t smith_qmatmul(void* p, uint32_t kind, void* a, void* b, void* cbuf, uint
   return do_qmatmul(c, (int)kind, (const float*)ba->dev, (const uint8_t*)bb->dev, (float*)bc->dev, M, N, K, groups, path);
 }
 
+int32_t smith_qmatmul_multi(void* p, uint32_t kind, void* a, uint32_t count, void* const* b_bufs, void* const* c_bufs,
+                            const uint64_t* n_list, uint64_t M, uint64_t K, uint64_t groups) {
+  Context* c = as_ctx(p);
+  Buffer* ba = as_buf(a);
+  if (!c || !ba) return 1;
+  if (kind != 4 && kind != 8) return fail("kind must be 4 or 8, got %u", kind);
+  if (count < 1 || count > 4) return fail("smith_qmatmul_multi takes 1 to 4 matrices, got %u", count);
+  if (!b_bufs || !c_bufs || !n_list) return fail("smith_qmatmul_multi: null lists");
+  if (!ba->dev) return fail("smith_qmatmul_multi needs buffers with a device side");
+  if (ba->bytes < M * K * 4) return fail("smith_qmatmul_multi: A holds %llu bytes, needs %llu",
+                                         (unsigned long long)ba->bytes, (unsigned long long)(M * K * 4));
+  const uint64_t blk = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  const uint8_t* Bs[4];
+  float* Cs[4];
+  int64_t Ns[4];
+  for (uint32_t i = 0; i < count; i++) {
+    Buffer *bb = as_buf(b_bufs[i]), *bc = as_buf(c_bufs[i]);
+    if (!bb || !bc) return 1;
+    if (!bb->dev || !bc->dev) return fail("smith_qmatmul_multi needs buffers with a device side");
+    if (bb->bytes < groups * n_list[i] * blk || bc->bytes < M * n_list[i] * 4)
+      return fail("smith_qmatmul_multi: matrix %u: a buffer is too small for N = %llu", i, (unsigned long long)n_list[i]);
+    Bs[i] = (const uint8_t*)bb->dev, Cs[i] = (float*)bc->dev, Ns[i] = (int64_t)n_list[i];
+  }
+  if (count > 1 && qgemv_supports_multi((int)kind, (int64_t)M, Ns, (int)count, (int64_t)K, (int64_t)groups)) {
+    cudaError_t e = launch_qgemv_multi((int)kind, (const float*)ba->dev, (int)count, Bs, Cs, Ns, (int64_t)M, (int64_t)K,
+                                       (int64_t)groups, c->stream);
+    if (e != cudaSuccess) return fail("multi-matrix GEMV launch failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  for (uint32_t i = 0; i < count; i++)      // shapes the GEMV kernel does not take: one launch each
+    if (do_qmatmul(c, (int)kind, (const float*)ba->dev, Bs[i], Cs[i], M, (uint64_t)Ns[i], K, groups, kAuto)) return 1;
+  return 0;
+}
+
 int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
   return resolve_path((int)kind, (int64_t)M, (int64_t)N, (int64_t)K, (int64_t)((K + 31) / 32));
 }

@@ -65,6 +65,11 @@ struct GemvGather {
 };
 cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                                 int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s);
+// Up to four weight matrices that share the activations A [M, K], as one launch:
+// C_i [M, N_i] = A x dequant(B_i).
+bool qgemv_supports_multi(int kind, int64_t M, const int64_t* Ns, int count, int64_t K, int64_t groups);
+cudaError_t launch_qgemv_multi(int kind, const float* A, int count, const uint8_t* const* Bs, float* const* Cs,
+                               const int64_t* Ns, int64_t M, int64_t K, int64_t groups, cudaStream_t s);
 // Grid size the GEMV uses for a shape (-1 if it does not take it).
 int qgemv_tiles(int kind, int64_t M, int64_t N, int64_t K);
 

@@ -71,6 +71,7 @@ namespace {
 
 constexpr int kMaxRowsM = 4;
 constexpr int kMaxPeers = 8;
+constexpr int kMaxMats = 4;                // weight matrices that may share one launch
 constexpr int kRowsPerPhase = 4;           // group-rows a phase handles per stage: fewer, larger stages measured
                                            // faster than more, smaller ones (4096 x 14336 Q4: 9.4 us at 4 rows,
                                            // 11.3 at 2, 16.4 at 1, ring depth in bytes equal); 3 where 4 would
@@ -84,9 +85,15 @@ constexpr int kCtasPerSm = 2;
 
 struct Params {
   const float* A;
-  const uint8_t* B;
-  float* C;
-  int M, N, K, G;
+  // Weight matrices that share the activations (wq/wk/wv, gate/up) run as ONE launch: matrix i
+  // owns the tiles [tile0[i], tile0[i + 1]) of the grid and has its own width and output.  One
+  // launch instead of several saves their start-up and tail, the GEMV's only idle HBM time.
+  const uint8_t* B[kMaxMats];
+  float* C[kMaxMats];
+  int N[kMaxMats];
+  int tile0[kMaxMats + 1];
+  int nmat;
+  int M, K, G;
   int TN, phases, nthreads;  // consumer threads = TN * phases
   int row_pitch, stage_rows, stage_bytes, stages;
   int xdig_off, xsc_off, ring_off;  // byte offsets in dynamic shared memory
@@ -244,8 +251,13 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   uint8_t* ring = smem + p.ring_off;
 
   const int tid = threadIdx.x;
-  const int col0 = blockIdx.x * p.TN;
-  const int tn = min(p.TN, p.N - col0);
+  int mat = 0;
+  while (mat + 1 < p.nmat && (int)blockIdx.x >= p.tile0[mat + 1]) mat++;
+  const uint8_t* __restrict__ Bm = p.B[mat];
+  float* __restrict__ Cm = p.C[mat];
+  const int Nm = p.N[mat];
+  const int col0 = ((int)blockIdx.x - p.tile0[mat]) * p.TN;
+  const int tn = min(p.TN, Nm - col0);
   const int nthr = tn * p.phases;                 // consumer threads with work in this CTA
   const int nwarps = (p.nthreads + 31) / 32;      // consumer warps launched
   const int nst = (p.G + p.stage_rows - 1) / p.stage_rows;
@@ -283,9 +295,9 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
       if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
       __syncwarp();
       const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
-      const uint8_t* src = p.B + ((size_t)st * p.stage_rows * p.N + col0) * BB;
+      const uint8_t* src = Bm + ((size_t)st * p.stage_rows * Nm + col0) * BB;
       for (int rr = lane; rr < rows; rr += 32)
-        bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * p.N * BB, row_bytes, bar, policy);
+        bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * Nm * BB, row_bytes, bar, policy);
     }
     return;  // consumers observe every full barrier, so the copies land before the CTA ends
   }
@@ -355,20 +367,20 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
       const int m = i / tn, c = i - m * tn;
       float sum = 0.f;
       for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
-      p.C[(size_t)m * p.N + col0 + c] = sum;
+      Cm[(size_t)m * Nm + col0 + c] = sum;
     }
     return;
   }
   const unsigned par = step & 1u;
   if (p.reduce) {
     // -------------------------------------------- fused all-reduce over peer memory
-    const size_t half = (size_t)par * p.M * p.N;
+    const size_t half = (size_t)par * p.M * Nm;
     float* mine_y = p.y[p.rank] + half;
     for (int i = tid; i < p.M * tn; i += nwarps * 32) {
       const int m = i / tn, c = i - m * tn;
       float sum = 0.f;
       for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
-      mine_y[(size_t)m * p.N + col0 + c] = sum;
+      mine_y[(size_t)m * Nm + col0 + c] = sum;
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // the partial tile is stored
     const size_t flag_at = 4 + ((size_t)par * gridDim.x + blockIdx.x) * kMaxPeers;
@@ -400,14 +412,14 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     if (*reinterpret_cast<volatile int*>(wait_ok)) {
       for (int i = tid; i < p.M * tn; i += nwarps * 32) {
         const int m = i / tn, c = i - m * tn;
-        const size_t at = half + (size_t)m * p.N + col0 + c;
+        const size_t at = half + (size_t)m * Nm + col0 + c;
         float sum = 0.f;
         for (int r = 0; r < p.world; r++) {
           float v;                                        // volatile: never a line cached two steps ago
           asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p.y[r] + at) : "memory");
           sum += v;
         }
-        p.C[(size_t)m * p.N + col0 + c] = sum;
+        Cm[(size_t)m * Nm + col0 + c] = sum;
       }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
@@ -466,13 +478,15 @@ struct Plan {
   bool ok;
 };
 
-Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
+Plan make_plan(int kind, int64_t M, const int64_t* Ns, int count, int64_t K) {
   const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
   const int sms = 148;
   Plan pl{};
   Params& p = pl.p;
   const int MR = (int)M;
-  p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)(K / 32);
+  int64_t N = 0;                                   // all matrices' columns together
+  for (int i = 0; i < count; i++) N += Ns[i];
+  p.M = (int)M, p.K = (int)K, p.G = (int)(K / 32), p.nmat = count;
   const int xdig_bytes = MR * p.G * 64, xsc_bytes = MR * p.G * 8;
   // One CTA per SM with a deep ring when the whole matrix fits one wave of 128-column tiles
   // (nothing follows a CTA on its SM, so depth beats overlap); two per SM when tiles come in
@@ -486,12 +500,23 @@ Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   // a multiple of 8 for 34-byte blocks.
   const int64_t q = (kind == 4) ? 2 : 8;
   int TN = 0;
+  auto tiles_at = [&](int tn) {
+    int64_t t = 0;
+    for (int i = 0; i < count; i++) t += (Ns[i] + tn - 1) / tn;
+    return t;
+  };
   for (int64_t waves = 1;; waves++) {
     TN = (int)(q * ((N + q * slots * waves - 1) / (q * slots * waves)));
+    while (tiles_at(TN) > slots * waves) TN += (int)q;   // several matrices: each one's last tile is partial
     if (TN <= (solo ? 128 : 112)) break;
   }
   p.TN = TN;
-  pl.tiles = (int)((N + TN - 1) / TN);
+  p.tile0[0] = 0;
+  for (int i = 0; i < count; i++) {
+    p.N[i] = (int)Ns[i];
+    p.tile0[i + 1] = p.tile0[i] + (int)((Ns[i] + TN - 1) / TN);
+  }
+  pl.tiles = p.tile0[count];
   // Phases: a multiple of 4 (so TN * phases fills whole warps), aiming at kMaxConsumerThreads.
   int phases = 0, stages = 0;
   for (pl.rpp = kRowsPerPhase; pl.rpp >= kRowsPerPhase - 1; pl.rpp--) {
@@ -555,7 +580,7 @@ cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
 }  // namespace
 
 int qgemv_tiles(int kind, int64_t M, int64_t N, int64_t K) {
-  const Plan pl = make_plan(kind, M, N, K);
+  const Plan pl = make_plan(kind, M, &N, 1, K);
   return pl.ok ? pl.tiles : -1;
 }
 
@@ -565,7 +590,37 @@ bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups) {
   if (N < 8 || (N % 8) != 0) return false;  // 16-byte alignment of every group-row span
   if (K < 32 || (K % 32) != 0 || groups != K / 32) return false;
   if (N > (1 << 30) || K > (1 << 22)) return false;
-  return make_plan(kind, M, N, K).ok;        // activations' digit form must fit beside the ring
+  return make_plan(kind, M, &N, 1, K).ok;    // activations' digit form must fit beside the ring
+}
+
+bool qgemv_supports_multi(int kind, int64_t M, const int64_t* Ns, int count, int64_t K, int64_t groups) {
+  if (count < 1 || count > kMaxMats) return false;
+  for (int i = 0; i < count; i++)
+    if (!qgemv_supports(kind, M, Ns[i], K, groups)) return false;
+  return make_plan(kind, M, Ns, count, K).ok;
+}
+
+cudaError_t launch_qgemv_multi(int kind, const float* A, int count, const uint8_t* const* Bs, float* const* Cs,
+                               const int64_t* Ns, int64_t M, int64_t K, int64_t groups, cudaStream_t s) {
+  (void)groups;
+  if (count < 1 || count > kMaxMats) return cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(A) & 15) return cudaErrorMisalignedAddress;
+  Plan pl = make_plan(kind, M, Ns, count, K);
+  if (!pl.ok) return cudaErrorInvalidValue;
+  pl.p.A = A;
+  for (int i = 0; i < count; i++) {
+    if (reinterpret_cast<uintptr_t>(Bs[i]) & 15) return cudaErrorMisalignedAddress;
+    pl.p.B[i] = Bs[i], pl.p.C[i] = Cs[i];
+  }
+  pl.p.status = kernel_status_ptr();
+  if (!pl.p.status) return cudaErrorUnknown;
+  pl.p.world = 0;
+#define SMITH_GEMV_CASE(KD, MRV) \
+  if (kind == KD && M == MRV) return pl.rpp == 3 ? launch_one<KD, MRV, 3>(pl, s) : launch_one<KD, MRV, 4>(pl, s);
+  SMITH_GEMV_CASE(4, 1) SMITH_GEMV_CASE(4, 2) SMITH_GEMV_CASE(4, 3) SMITH_GEMV_CASE(4, 4)
+  SMITH_GEMV_CASE(8, 1) SMITH_GEMV_CASE(8, 2) SMITH_GEMV_CASE(8, 3) SMITH_GEMV_CASE(8, 4)
+#undef SMITH_GEMV_CASE
+  return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
@@ -577,9 +632,9 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
                                 int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s) {
   (void)groups;
   if ((reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(A) & 15)) return cudaErrorMisalignedAddress;
-  Plan pl = make_plan(kind, M, N, K);
+  Plan pl = make_plan(kind, M, &N, 1, K);
   if (!pl.ok) return cudaErrorInvalidValue;
-  pl.p.A = A, pl.p.B = B, pl.p.C = C;
+  pl.p.A = A, pl.p.B[0] = B, pl.p.C[0] = C;
   pl.p.status = kernel_status_ptr();
   if (!pl.p.status) return cudaErrorUnknown;
   pl.p.world = 0;

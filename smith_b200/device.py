@@ -89,6 +89,7 @@ SYMBOLS = {
     "smith_ipc_import": (_p, [_p, _p, _u64]),
     "smith_qmatmul_allgather": (_i32, [_p, _u32, _p, _p, _u64, _u64, _u64, _u64, _u64, _u64, _u32, _u32,
                                         C.POINTER(_p), C.POINTER(_p), _u32]),
+    "smith_qmatmul_multi": (_i32, [_p, _u32, _p, _u32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_u64), _u64, _u64, _u64]),
     "smith_qmatmul_allreduce": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32, _u32, C.POINTER(_p),
                                        C.POINTER(_p)]),
     "smith_qmatmul_allreduce_state_bytes": (_u64, [_u32, _u64, _u64, _u64]),
@@ -414,6 +415,13 @@ def qmatmulAllGather(kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, w
     ss = (_p * world)(*stateBuffers)
     _check(lib.smith_qmatmul_allgather(ctx(), kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank,
                                        ys, ss, target), "qmatmul_allgather")
+
+
+def qmatmulMulti(kind, aBuffer, bBuffers, cBuffers, Ns, M, K, groups):
+    """One launch for several packed matrices that share the activations (M <= 4); see the header."""
+    n = len(bBuffers)
+    _check(lib.smith_qmatmul_multi(ctx(), kind, aBuffer, n, (_p * n)(*bBuffers), (_p * n)(*cBuffers),
+                                   (_u64 * n)(*[int(x) for x in Ns]), M, K, groups), "qmatmul_multi")
 
 
 def qmatmulAllReduce(kind, aBuffer, bBuffer, outBuffer, M, N, kLocal, groupsLocal, world, rank, partialBuffers,

@@ -367,6 +367,35 @@ def test_fused_gather_two_shards_emulated_on_one_gpu():
         b.free()
 
 
+# ------------------------------------------------------------------ several matrices sharing one launch
+@pytest.mark.parametrize("kind,M,K,Ns", [("q4", 1, 4096, [4096, 1024, 1024]), ("q8", 3, 1024, [512, 2048]),
+                                         ("q4", 2, 2048, [1000 // 8 * 8, 24, 4096, 136]), ("q4", 8, 1024, [256, 512])])
+def test_qmatmul_multi_matches_one_launch_per_matrix(kind, M, K, Ns):
+    rng = np.random.default_rng(41 + M)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    ab = DevBuf.of(a)
+    packs, pbs, cbs = [], [], []
+    for n in Ns:
+        w = (rng.standard_normal((K, n)) * 0.02).astype(np.float32)
+        packs.append(O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w))
+        pbs.append(DevBuf.of(packs[-1]))
+        cbs.append(DevBuf.of(np.full(M * n, np.nan, np.float32)))
+    launches0 = device.launchCount()
+    device.qmatmulMulti(4 if kind == "q4" else 8, ab.handle, [b.handle for b in pbs], [b.handle for b in cbs], Ns, M, K,
+                        K // 32)
+    device.synchronize()
+    assert device.kernelStatus() == 0
+    if M <= 4:
+        assert device.launchCount() - launches0 == 1        # one launch for all of them
+    for n, packed, cb in zip(Ns, packs, cbs):
+        got = cb.get(np.float32).reshape(M, n)
+        want = O.matmul(a, packed, K, n, kind)
+        ok, worst = within_tolerance(got, want, a, packed, K, n, kind, REL)
+        assert ok, (n, worst)
+    for b in pbs + cbs + [ab]:
+        b.free()
+
+
 # ------------------------------------------------------------------ fused all-reduce epilogue (one GPU)
 def test_fused_reduce_world_of_one_and_alternating_halves():
     from smith_b200.parallel import FusedReduce
