@@ -28,6 +28,11 @@
 //    group-rows (TN * block_bytes contiguous bytes each) arrive through a ring
 //    of shared-memory stages filled by 1-D bulk async copies from a producer
 //    thread (full/empty mbarriers, no multicast); lanes read adjacent blocks.
+//    Where a tile's row segment is short (narrow N: 4096 columns give 672-byte
+//    segments) the per-copy cost of the copy engine, about 40 ns, would set the
+//    pace, so such tiles fetch a whole stage as ONE 2-D tensor-map box
+//    (cp.async.bulk.tensor.2d over the packed matrix seen as [groups][N * block
+//    bytes / 8] 64-bit words; rows past the end are zero-filled).
 //  * The phases of a column are summed through shared memory in fixed order
 //    and each output is written once.  No atomics, no global scratch.
 //  * Tiles are sized so that two CTAs share an SM (more warps in flight, and
@@ -61,6 +66,7 @@
 //    run further than one step ahead of a peer that still reads them.
 //
 // Waits are time-bounded as in pipeline.cuh.
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -93,6 +99,7 @@ struct Params {
   int N[kMaxMats];
   int tile0[kMaxMats + 1];
   int nmat;
+  int use_tma;            // stages arrive as one 2-D tensor-map box each instead of one bulk copy per group-row
   int M, K, G;
   int TN, phases, nthreads;  // consumer threads = TN * phases
   int row_pitch, stage_rows, stage_bytes, stages;
@@ -238,8 +245,21 @@ __device__ __forceinline__ void block_dot(const uint8_t* __restrict__ blk, uint3
   }
 }
 
+struct alignas(64) TensorMaps {
+  CUtensorMap m[kMaxMats];
+};
+
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
+                                           uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+
 template <int KIND, int MR, int RPP>
-__global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_kernel(const Params p) {
+__global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_kernel(const Params p,
+                                                                                     const __grid_constant__ TensorMaps tm) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -292,9 +312,17 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
       }
       const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
       const uint32_t bar = smem_u32(&full[slot]);
+      const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
+      if (p.use_tma) {
+        // the box is always stage_rows x TN blocks: what lies beyond N or the last group-row is zero-filled
+        if (lane == 0) {
+          mbar_expect_tx(bar, (uint32_t)p.stage_rows * (uint32_t)p.row_pitch);
+          tma_box_2d(dst, &tm.m[mat], (col0 * BB) >> 3, st * p.stage_rows, bar, policy);
+        }
+        continue;
+      }
       if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
       __syncwarp();
-      const uint32_t dst = smem_u32(ring + (size_t)slot * p.stage_bytes);
       const uint8_t* src = Bm + ((size_t)st * p.stage_rows * Nm + col0) * BB;
       for (int rr = lane; rr < rows; rr += 32)
         bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * Nm * BB, row_bytes, bar, policy);
@@ -527,7 +555,7 @@ Plan make_plan(int kind, int64_t M, const int64_t* Ns, int count, int64_t K) {
     p.nthreads = TN * phases;
     p.row_pitch = TN * BB;
     p.stage_rows = phases * pl.rpp;
-    p.stage_bytes = ((p.stage_rows * p.row_pitch + 15) / 16) * 16;
+    p.stage_bytes = ((p.stage_rows * p.row_pitch + 127) / 128) * 128;   // 128: alignment of a tensor-map box in shared memory
     p.xdig_off = kHeader;
     p.xsc_off = p.xdig_off + xdig_bytes;
     p.ring_off = ((p.xsc_off + xsc_bytes + 1023) / 1024) * 1024;
@@ -545,6 +573,11 @@ Plan make_plan(int kind, int64_t M, const int64_t* Ns, int count, int64_t K) {
   }
   if (pl.rpp < kRowsPerPhase - 1) pl.rpp = kRowsPerPhase - 1;
   p.stages = stages;
+  // Boxes pay where the per-copy cost of row-by-row bulk copies sets the pace: short row segments and
+  // many of them.  Measured (M = 1, Q4): 14336 x 4096 (672-byte rows, 448 group-rows) 18.2 -> 12.2 us,
+  // 8192 x 8192 (1344, 256) 13.1 -> 11.5 us; but 4096 x 4096 (672, 128) 5.6 -> 6.1 us and
+  // 4096 x 11008 (1824, 128) 9.1 -> 10.1 us.  (A box side holds at most 256 64-bit words.)
+  p.use_tma = (p.row_pitch <= 1408 && p.G >= 192 && p.stage_rows <= 256) ? 1 : 0;
   const size_t red = (size_t)phases * MR * TN * 4;
   const size_t ring = (size_t)(stages > 0 ? stages : 0) * p.stage_bytes + 64;
   pl.smem = p.ring_off + (ring > red ? ring : red);
@@ -552,8 +585,43 @@ Plan make_plan(int kind, int64_t M, const int64_t* Ns, int count, int64_t K) {
   return pl;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor maps of the plan's matrices: each packed matrix as [G][N * block bytes / 8] 64-bit words,
+// box = one stage of one tile.  Leaves the plan on plain bulk copies if the driver entry is missing.
+void make_tensor_maps(Plan& pl, int kind, TensorMaps& tm) {
+  if (!pl.p.use_tma) return;
+  EncodeTiledFn enc = encode_fn();
+  const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  for (int i = 0; i < pl.p.nmat && enc; i++) {
+    const cuuint64_t dims[2] = {(cuuint64_t)pl.p.N[i] * BB / 8, (cuuint64_t)pl.p.G};
+    const cuuint64_t strides[1] = {(cuuint64_t)pl.p.N[i] * BB};
+    const cuuint32_t box[2] = {(cuuint32_t)pl.p.row_pitch / 8, (cuuint32_t)pl.p.stage_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&tm.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(pl.p.B[i]), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      enc = nullptr;
+  }
+  if (!enc) pl.p.use_tma = 0;
+}
+
 template <int KIND, int MR, int RPP>
-cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
+cudaError_t launch_one(Plan& pl, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
@@ -572,7 +640,9 @@ cudaError_t launch_one(const Plan& pl, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR, RPP>, pl.p);
+  TensorMaps tm{};
+  make_tensor_maps(pl, KIND, tm);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR, RPP>, pl.p, tm);
   count_launch();
   return e;
 }
