@@ -135,9 +135,7 @@ __device__ __forceinline__ int dp4a_su(int a, unsigned b, int c) {  // a signed 
 //                      Q8: word i*2 + {0,1} = {hi, lo} of k = 4i .. 4i+3.
 //   sc: {2^-e, float(sum_k x_int)}.
 template <int KIND>
-__device__ __forceinline__ void quantise_quarter(const float* __restrict__ x, int lane8, uint8_t* digits,
-                                                 float2* sc) {
-  const float4 t = __ldg(reinterpret_cast<const float4*>(x) + lane8);
+__device__ __forceinline__ void quantise_quarter(const float4 t, int lane8, uint8_t* digits, float2* sc) {
   const float v[4] = {t.x, t.y, t.z, t.w};
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
   int bad = 0;
@@ -337,10 +335,27 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   if (p.world > 0) step = *reinterpret_cast<volatile unsigned*>(p.state[p.rank]);  // advanced by the previous launch
   // Activations -> digit words (overlaps the first weight copies).
   // (row, group) pairs are laid out as [MR][G], which is also the order of A's 32-element chunks.
-  for (int i = tid; i < ((MR * p.G * 8 + 31) & ~31); i += nwarps * 32) {
-    const int grp = min(i >> 3, MR * p.G - 1);  // clamp keeps whole warps in the shuffles; duplicates rewrite equal bytes
-    quantise_quarter<KIND>(p.A + (size_t)grp * 32, i & 7, reinterpret_cast<uint8_t*>(xdig + (size_t)grp * 4),
-                           xsc + grp);
+  // Four passes' loads are issued before the first is used: a pass is one L2 round trip long, and a
+  // long K (14336: eight passes) would otherwise spend several microseconds here.
+  {
+    const int total = (MR * p.G * 8 + 31) & ~31, stride = nwarps * 32, last = MR * p.G - 1;
+    for (int i0 = tid; i0 < total; i0 += 4 * stride) {
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * stride;
+        // clamp keeps whole warps in the shuffles; duplicates rewrite equal bytes
+        if (i < total) t[u] = __ldg(reinterpret_cast<const float4*>(p.A + (size_t)min(i >> 3, last) * 32) + (i & 7));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * stride;            // warp-uniform: total and stride are multiples of 32
+        if (i < total) {
+          const int grp = min(i >> 3, last);
+          quantise_quarter<KIND>(t[u], i & 7, reinterpret_cast<uint8_t*>(xdig + (size_t)grp * 4), xsc + grp);
+        }
+      }
+    }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
 
