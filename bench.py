@@ -282,7 +282,7 @@ def run_step_workload(args, wl):
     if world > 1:
         reducers["wo"] = P.FusedReduce(kind, M, dim, shard_k(dim), world, rank)
         reducers["down"] = P.FusedReduce(kind, M, dim, shard_k(ffn), world, rank)
-        gather = P.FusedGather(M, vocab, world, rank)
+        gather = P.FusedGather(M, vocab, world, rank, deferred=True)
 
     def one_pass():
         for name, pks, kl, nls, coll in ops:
@@ -295,6 +295,8 @@ def run_step_workload(args, wl):
                 D.qmatmulMulti(kind, src, pks, ([y] + y2)[:len(pks)], nls, M, kl, kl // 32)
             else:
                 D.qmatmul(kind, src, pks[0], y, M, nls[0], kl, kl // 32, D.PATH_AUTO)
+        if world > 1:
+            gather.finish()
 
     def barrier():
         D.synchronize()
@@ -467,7 +469,7 @@ def main():
     if world > 1:
         fused = M <= 4 and all(D.qgemvTiles(kind, M, b - a, K) > 0
                                for a, b in (P.column_shard(N, world, r) for r in range(world)))
-        gather = P.FusedGather(M, N, world, rank) if fused else P.OutputGather(M, N, world, rank)
+        gather = P.FusedGather(M, N, world, rank, deferred=True) if fused else P.OutputGather(M, N, world, rank)
     c_dev = D.alloc(M * Nl * 4, D.PRIVATE) if (not gather or fused) else gather.local_buf
 
     def one_pass():
@@ -478,6 +480,8 @@ def main():
                 D.qmatmul(kind, a_dev, pk, c_dev, M, Nl, K, G, D.PATH_AUTO)
                 if gather:
                     gather.enqueue()
+        if fused:
+            gather.finish()                       # the last launch's row is whole when the pass ends
 
     one_pass()                                    # sizes scratch before capture
     D.synchronize()
@@ -584,7 +588,7 @@ def main():
             "config": {"workload": args.workload, "kind": f"q{kind}", "M": M, "K": K, "N": N,
                        "launches_per_step": R, "kernel": path,
                        "sharding": (f"N-sharded over {world} GPU(s), all-gather of outputs "
-                                    + ("fused into the GEMV kernel (peer stores over NVLink)" if fused else "by NCCL"))
+                                    + ("fused into the GEMV kernel (peer stores over NVLink; each launch waits for its predecessor's tiles after its own weight stream has started, a final wait closes the step)" if fused else "by NCCL"))
                        if world > 1 else "single GPU",
                        "l2": f"defeated by rotating over {R} distinct packed matrices per step "
                              f"({R * wbytes_full / 1e6:.0f} MB > 4 x 126 MB L2)",

@@ -203,6 +203,17 @@ void* smith_ipc_import(void* ctx, const void* handle64, uint64_t bytes);
 int32_t smith_qmatmul_allgather(void* ctx, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total,
                                 uint64_t n0, uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world,
                                 uint32_t rank, void* const* y_bufs, void* const* state_bufs, uint32_t target);
+/* The same with flags.  SMITH_GATHER_DEFER (1): the launch does not wait for the other ranks' tiles.
+ * Instead the next smith_qmatmul_allgather_ex call on the same state waits for them before it reads
+ * its activations -- by then its weights are already streaming, so the NVLink round trip is hidden --
+ * and a chain of such calls is closed by smith_allgather_wait (asynchronous, bounded like the
+ * others), after which the last row is whole on this rank. */
+#define SMITH_GATHER_DEFER 1u
+int32_t smith_qmatmul_allgather_ex(void* ctx, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total,
+                                   uint64_t n0, uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world,
+                                   uint32_t rank, void* const* y_bufs, void* const* state_bufs, uint32_t target,
+                                   uint32_t flags);
+int32_t smith_allgather_wait(void* ctx, void* state_buf, uint32_t target);
 int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
 /* Fused GEMV + all-reduce for weights sharded along K (M <= 4; the Wo / down projections of a
  * tensor-parallel layer).  This rank multiplies its K-slice: a = [M, k_local] activations, b = its

@@ -907,6 +907,22 @@ int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
 int32_t smith_qmatmul_allgather(void* p, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total, uint64_t n0,
                                 uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world, uint32_t rank,
                                 void* const* y_bufs, void* const* state_bufs, uint32_t target) {
+  return smith_qmatmul_allgather_ex(p, kind, a, b, M, n_total, n0, n_local, K, groups, world, rank, y_bufs, state_bufs,
+                                    target, 0);
+}
+
+int32_t smith_allgather_wait(void* p, void* state_buf, uint32_t target) {
+  Context* c = as_ctx(p);
+  Buffer* bs = as_buf(state_buf);
+  if (!c || !bs) return 1;
+  if (!bs->dev || bs->bytes < 16) return fail("smith_allgather_wait: not a state buffer");
+  cudaError_t e = launch_gather_wait((const unsigned*)bs->dev, target, c->stream);
+  return e == cudaSuccess ? 0 : fail("all-gather wait launch failed: %s", cudaGetErrorString(e));
+}
+
+int32_t smith_qmatmul_allgather_ex(void* p, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total, uint64_t n0,
+                                   uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world, uint32_t rank,
+                                   void* const* y_bufs, void* const* state_bufs, uint32_t target, uint32_t flags) {
   Context* c = as_ctx(p);
   Buffer *ba = as_buf(a), *bb = as_buf(b);
   if (!c || !ba || !bb) return 1;
@@ -924,6 +940,7 @@ int32_t smith_qmatmul_allgather(void* p, uint32_t kind, void* a, void* b, uint64
                 (unsigned long long)M, (unsigned long long)n_local, (unsigned long long)K);
   GemvGather g{};
   g.world = (int)world, g.rank = (int)rank, g.n0 = (int64_t)n0, g.n_total = (int64_t)n_total, g.target = target;
+  g.defer = (flags & 1u) ? 1 : 0;
   for (uint32_t r = 0; r < world; r++) {
     Buffer *by = as_buf(y_bufs[r]), *bs = as_buf(state_bufs[r]);
     if (!by || !bs || !by->dev || !bs->dev) return fail("smith_qmatmul_allgather: rank %u buffers have no device side", r);

@@ -62,7 +62,12 @@ struct GemvGather {
   // state[r] continues with flags [2][tiles][8] after the four control words, and C receives the
   // sum over ranks (n0 = 0, n_total = N, target unused).
   int reduce;
+  // all-gather only: the launch does not wait for the peers; the next launch on the same state
+  // (or launch_gather_wait) does, before it reads its activations
+  int defer;
 };
+// Returns when the last deferred all-gather step on `state` is whole on this rank (bounded wait).
+cudaError_t launch_gather_wait(const unsigned* state, unsigned target, cudaStream_t s);
 cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                                 int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s);
 // Up to four weight matrices that share the activations A [M, K], as one launch:

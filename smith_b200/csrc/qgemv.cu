@@ -115,6 +115,10 @@ struct Params {
   // Fused all-reduce instead (weights sharded along K): y[r] holds rank r's PARTIAL rows [2][M][N],
   // state[r] continues after its four control words with flags [2][tiles][kMaxPeers]; C gets the sum.
   int reduce;
+  // All-gather only: do not wait for the peers at the end of the launch; instead the NEXT launch on
+  // the same state waits for this step's arrivals before it reads its activations -- after its
+  // producer has begun to stream weights, so the NVLink round trip hides behind the stream.
+  int defer;
 };
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) {
@@ -243,6 +247,26 @@ __device__ __forceinline__ void block_dot(const uint8_t* __restrict__ blk, uint3
   }
 }
 
+// Bounded wait until an arrival counter (written by peers with system-scope atomics) reaches `expected`.
+__device__ __forceinline__ bool wait_arrivals(const unsigned* counter, unsigned expected) {
+  const long long t0 = clock64();
+  for (unsigned spin = 0;; spin++) {
+    unsigned seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (seen >= expected) return true;
+    if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) return false;
+  }
+}
+
+// Closes a chain of deferred all-gathers: returns when the last step's row on this rank is whole.
+__global__ void gather_wait_kernel(const unsigned* state, unsigned target, int* status) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const unsigned step = *reinterpret_cast<const volatile unsigned*>(state);
+  if (step == 0) return;
+  const unsigned prev = step - 1u;
+  if (!wait_arrivals(state + 2 + (prev & 1u), (prev / 2u + 1u) * target)) atomicExch(status, 1);
+}
+
 struct alignas(64) TensorMaps {
   CUtensorMap m[kMaxMats];
 };
@@ -333,6 +357,14 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned step = 0;
   if (p.world > 0) step = *reinterpret_cast<volatile unsigned*>(p.state[p.rank]);  // advanced by the previous launch
+  if (p.world > 0 && p.defer && step > 0) {
+    // the previous step's gathered row (which may be this launch's input) must be whole
+    if (tid == 0) {
+      const unsigned prev = step - 1u;
+      if (!wait_arrivals(p.state[p.rank] + 2 + (prev & 1u), (prev / 2u + 1u) * p.target)) atomicExch(p.status, 1);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+  }
   // Activations -> digit words (overlaps the first weight copies).
   // (row, group) pairs are laid out as [MR][G], which is also the order of A's 32-element chunks.
   // Four passes' loads are issued before the first is used: a pass is one L2 round trip long, and a
@@ -493,19 +525,8 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     unsigned* mine = p.state[p.rank];
     const unsigned ticket = atomicAdd(mine + 1, 1u);
     if (ticket == gridDim.x - 1) {                      // last CTA of this rank's grid
-      const unsigned expected = (step / 2u + 1u) * p.target;
-      const long long t0 = clock64();
-      bool whole = false;
-      for (unsigned spin = 0;; spin++) {
-        unsigned seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + 2 + par) : "memory");
-        if (seen >= expected) {
-          whole = true;
-          break;
-        }
-        if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) break;
-      }
-      if (!whole) atomicExch(p.status, 1);              // a peer never arrived: the row is not valid
+      // a peer that never arrives leaves the row invalid: the status word says so
+      if (!p.defer && !wait_arrivals(mine + 2 + par, (step / 2u + 1u) * p.target)) atomicExch(p.status, 1);
       mine[1] = 0u;
       __threadfence();
       *reinterpret_cast<volatile unsigned*>(mine) = step + 1u;
@@ -728,6 +749,7 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
     pl.p.world = g->world, pl.p.rank = g->rank, pl.p.n0 = (int)g->n0, pl.p.n_total = (int)g->n_total;
     pl.p.target = g->target;
     pl.p.reduce = g->reduce;
+    pl.p.defer = (g->defer && !g->reduce) ? 1 : 0;
     if (g->reduce && !C) return cudaErrorInvalidValue;
     for (int r = 0; r < g->world; r++) {
       pl.p.y[r] = g->y[r];
@@ -741,6 +763,14 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
   SMITH_GEMV_CASE(8, 1) SMITH_GEMV_CASE(8, 2) SMITH_GEMV_CASE(8, 3) SMITH_GEMV_CASE(8, 4)
 #undef SMITH_GEMV_CASE
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_gather_wait(const unsigned* state, unsigned target, cudaStream_t s) {
+  int* status = kernel_status_ptr();
+  if (!status) return cudaErrorUnknown;
+  gather_wait_kernel<<<1, 1, 0, s>>>(state, target, status);
+  count_launch();
+  return cudaGetLastError();
 }
 
 }  // namespace smith

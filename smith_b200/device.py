@@ -89,6 +89,9 @@ SYMBOLS = {
     "smith_ipc_import": (_p, [_p, _p, _u64]),
     "smith_qmatmul_allgather": (_i32, [_p, _u32, _p, _p, _u64, _u64, _u64, _u64, _u64, _u64, _u32, _u32,
                                         C.POINTER(_p), C.POINTER(_p), _u32]),
+    "smith_qmatmul_allgather_ex": (_i32, [_p, _u32, _p, _p, _u64, _u64, _u64, _u64, _u64, _u64, _u32, _u32,
+                                           C.POINTER(_p), C.POINTER(_p), _u32, _u32]),
+    "smith_allgather_wait": (_i32, [_p, _p, _u32]),
     "smith_qmatmul_multi": (_i32, [_p, _u32, _p, _u32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_u64), _u64, _u64, _u64]),
     "smith_qmatmul_allreduce": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32, _u32, C.POINTER(_p),
                                        C.POINTER(_p)]),
@@ -409,12 +412,19 @@ def qgemvTiles(kind, M, N, K):
     return int(lib.smith_qgemv_tiles(kind, M, N, K))
 
 
+GATHER_DEFER = 1
+
+
 def qmatmulAllGather(kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank, yBuffers, stateBuffers,
-                     target):
+                     target, flags=0):
     ys = (_p * world)(*yBuffers)
     ss = (_p * world)(*stateBuffers)
-    _check(lib.smith_qmatmul_allgather(ctx(), kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank,
-                                       ys, ss, target), "qmatmul_allgather")
+    _check(lib.smith_qmatmul_allgather_ex(ctx(), kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world,
+                                          rank, ys, ss, target, flags), "qmatmul_allgather")
+
+
+def allGatherWait(stateBuffer, target):
+    _check(lib.smith_allgather_wait(ctx(), stateBuffer, target), "allgather_wait")
 
 
 def qmatmulMulti(kind, aBuffer, bBuffers, cBuffers, Ns, M, K, groups):

@@ -102,13 +102,19 @@ class FusedGather:
     when the local row is whole.  No NCCL call on the data path; capturable in a CUDA graph.
 
     Owns this rank's row buffer (two halves used alternately) and its 16-byte control block,
-    and holds IPC mappings of the other ranks' buffers."""
+    and holds IPC mappings of the other ranks' buffers.
+
+    ``deferred=True``: a launch does not wait for the peers' tiles; the next ``enqueue`` does, after
+    its weights have begun to stream (the NVLink round trip hides behind the stream), and
+    ``finish()`` closes the chain -- call it before reading the last row."""
     capturable = True
     kernels_per_call = 0    # the gather is part of the matmul launch
 
-    def __init__(self, M, N, world, rank, group=None):
+    def __init__(self, M, N, world, rank, group=None, deferred=False):
         from . import device as D
         self.M, self.N, self.world, self.rank = M, N, world, rank
+        self.deferred = deferred
+        self._last = None
         self.spans = [column_shard(N, world, r) for r in range(world)]
         self.y = D.alloc(2 * M * N * 4, D.PRIVATE)
         self.state = D.alloc(256, D.PRIVATE)
@@ -144,13 +150,21 @@ class FusedGather:
         from . import device as D
         n0, n1 = self.spans[self.rank]
         D.qmatmulAllGather(kind, a_buf, packed_shard_buf, self.M, self.N, n0, n1 - n0, K, K // 32, self.world,
-                           self.rank, self.ys, self.states, self.target(kind, K))
+                           self.rank, self.ys, self.states, self.target(kind, K),
+                           D.GATHER_DEFER if self.deferred else 0)
+        self._last = (kind, K)
         half = self.calls & 1
         self.calls += 1
         return half
 
+    def finish(self):
+        """Deferred mode: enqueue the wait that makes the last step's row whole on this rank."""
+        from . import device as D
+        if self.deferred and self._last:
+            D.allGatherWait(self.state, self.target(*self._last))
+
     def read(self, half):
-        """The gathered rows [M, N] of one half (after a synchronize)."""
+        """The gathered rows [M, N] of one half (after ``finish()`` in deferred mode, and a synchronize)."""
         from . import device as D
         n = self.M * self.N
         return D.download(self.y, n * 4, np.float32, offset=half * n * 4).reshape(self.M, self.N)
@@ -281,7 +295,7 @@ class ShardedMatmul:
         self.Nl = n1 - n0
         self.fused = M <= 4 and all(D.qgemvTiles(kind, M, b - a, K) > 0
                                     for a, b in (column_shard(N, world, r) for r in range(world)))
-        self.gather = FusedGather(M, N, world, rank) if self.fused else OutputGather(M, N, world, rank)
+        self.gather = FusedGather(M, N, world, rank, deferred=True) if self.fused else OutputGather(M, N, world, rank)
         self.a_dev = D.alloc(M * K * 4, D.PRIVATE)
 
     def enqueue(self, a_dev=None):
@@ -299,6 +313,8 @@ class ShardedMatmul:
         from . import device as D
         D.upload(self.a_dev, np.ascontiguousarray(a_host, dtype=np.float32))
         out = self.enqueue()
+        if self.fused:
+            self.gather.finish()
         D.synchronize()
         if self.fused:
             return self.gather.read(out)

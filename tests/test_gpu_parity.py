@@ -332,6 +332,29 @@ def test_fused_gather_world_of_one_and_alternating_halves():
     pb.free()
 
 
+def test_fused_gather_deferred_chain_world_of_one():
+    # deferred mode: no launch waits at its end; each waits for its predecessor's arrivals at its
+    # start, and finish() closes the chain
+    from smith_b200.parallel import FusedGather
+    K, N, M = 1024, 2048, 1
+    rng = np.random.default_rng(23)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    packed = O.quantize_q4(w)
+    pb = DevBuf.of(packed)
+    fg = FusedGather(M, N, 1, 0, deferred=True)
+    acts = [rng.standard_normal((M, K)).astype(np.float32) for _ in range(3)]
+    abs_ = [DevBuf.of(a) for a in acts]
+    halves = [fg.enqueue(4, ab.handle, pb.handle, K) for ab in abs_]      # back to back, no host wait between
+    fg.finish()
+    device.synchronize()
+    assert device.kernelStatus() == 0 and halves == [0, 1, 0]
+    assert bits_equal(fg.read(0), matmul_on_device(acts[2], packed, K, N, "q4", device.PATH_GEMV))
+    assert bits_equal(fg.read(1), matmul_on_device(acts[1], packed, K, N, "q4", device.PATH_GEMV))
+    fg.close()
+    for b in abs_ + [pb]:
+        b.free()
+
+
 def test_fused_gather_two_shards_emulated_on_one_gpu():
     # Two ranks' launches run one after the other on this GPU, each storing its column slice into
     # both ranks' rows.  The first launch is told to expect only its own tiles (its peer has not run
