@@ -911,12 +911,17 @@ int32_t smith_qmatmul_allgather(void* p, uint32_t kind, void* a, void* b, uint64
                                     target, 0);
 }
 
-int32_t smith_allgather_wait(void* p, void* state_buf, uint32_t target) {
+int32_t smith_allgather_wait(void* p, uint32_t world, uint32_t rank, void* const* state_bufs) {
   Context* c = as_ctx(p);
-  Buffer* bs = as_buf(state_buf);
-  if (!c || !bs) return 1;
-  if (!bs->dev || bs->bytes < 16) return fail("smith_allgather_wait: not a state buffer");
-  cudaError_t e = launch_gather_wait((const unsigned*)bs->dev, target, c->stream);
+  if (!c) return 1;
+  if (world < 1 || world > 8 || rank >= world || !state_bufs) return fail("smith_allgather_wait: bad world / rank / list");
+  unsigned* states[8];
+  for (uint32_t r = 0; r < world; r++) {
+    Buffer* bs = as_buf(state_bufs[r]);
+    if (!bs || !bs->dev || bs->bytes < 32) return fail("smith_allgather_wait: rank %u: not a state buffer", r);
+    states[r] = (unsigned*)bs->dev;
+  }
+  cudaError_t e = launch_gather_wait(states, (int)world, (int)rank, c->stream);
   return e == cudaSuccess ? 0 : fail("all-gather wait launch failed: %s", cudaGetErrorString(e));
 }
 
@@ -944,7 +949,7 @@ int32_t smith_qmatmul_allgather_ex(void* p, uint32_t kind, void* a, void* b, uin
   for (uint32_t r = 0; r < world; r++) {
     Buffer *by = as_buf(y_bufs[r]), *bs = as_buf(state_bufs[r]);
     if (!by || !bs || !by->dev || !bs->dev) return fail("smith_qmatmul_allgather: rank %u buffers have no device side", r);
-    if (by->bytes < 2 * M * n_total * 4 || bs->bytes < 16) return fail("smith_qmatmul_allgather: rank %u buffers too small", r);
+    if (by->bytes < 2 * M * n_total * 4 || bs->bytes < 32) return fail("smith_qmatmul_allgather: rank %u buffers too small", r);
     g.y[r] = (float*)by->dev;
     g.state[r] = (unsigned*)bs->dev;
   }

@@ -62,12 +62,14 @@ struct GemvGather {
   // state[r] continues with flags [2][tiles][8] after the four control words, and C receives the
   // sum over ranks (n0 = 0, n_total = N, target unused).
   int reduce;
-  // all-gather only: the launch does not wait for the peers; the next launch on the same state
-  // (or launch_gather_wait) does, before it reads its activations
+  // all-gather only: the CTAs store and leave; the next launch on the same state (or
+  // launch_gather_wait) signals this rank's step to all ranks and waits for theirs before it
+  // reads its activations (one arrival per rank and step; `target` is not used)
   int defer;
 };
-// Returns when the last deferred all-gather step on `state` is whole on this rank (bounded wait).
-cudaError_t launch_gather_wait(const unsigned* state, unsigned target, cudaStream_t s);
+// Signals this rank's last deferred step to every rank and returns when all ranks' arrivals for it
+// are here (bounded wait): the last row is then whole on this rank.
+cudaError_t launch_gather_wait(unsigned* const* states, int world, int rank, cudaStream_t s);
 cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                                 int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s);
 // Up to four weight matrices that share the activations A [M, K], as one launch:

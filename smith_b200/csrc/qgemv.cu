@@ -115,9 +115,12 @@ struct Params {
   // Fused all-reduce instead (weights sharded along K): y[r] holds rank r's PARTIAL rows [2][M][N],
   // state[r] continues after its four control words with flags [2][tiles][kMaxPeers]; C gets the sum.
   int reduce;
-  // All-gather only: do not wait for the peers at the end of the launch; instead the NEXT launch on
-  // the same state waits for this step's arrivals before it reads its activations -- after its
-  // producer has begun to stream weights, so the NVLink round trip hides behind the stream.
+  // All-gather only, deferred form: the threads of a CTA store their outputs, fence them and leave --
+  // no barrier, no per-CTA arrival, no wait at the end.  One thread
+  // of the NEXT launch on the same state (or of the closing wait kernel) then tells
+  // every rank "my step s is complete" (one arrival per rank and step), and that launch waits for
+  // the other ranks' arrivals before it reads its activations -- after its producer has begun to
+  // stream weights, so the NVLink round trip hides behind the stream.
   int defer;
 };
 
@@ -258,13 +261,32 @@ __device__ __forceinline__ bool wait_arrivals(const unsigned* counter, unsigned 
   }
 }
 
-// Closes a chain of deferred all-gathers: returns when the last step's row on this rank is whole.
-__global__ void gather_wait_kernel(const unsigned* state, unsigned target, int* status) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const unsigned step = *reinterpret_cast<const volatile unsigned*>(state);
+// Deferred all-gather: tell every rank about the steps of this rank that are complete and not yet
+// announced (word 4 of the state counts the announced ones; the callers are serialised by stream
+// order, so a plain read-modify-write does).  One arrival per rank and step.
+__device__ __forceinline__ void announce_steps(unsigned* const* state, int world, int rank, unsigned step) {
+  unsigned* mine = state[rank];
+  unsigned told = *reinterpret_cast<volatile unsigned*>(mine + 4);
+  if (told >= step) return;
+  __threadfence_system();
+  for (; told < step; told++)
+    for (int r = 0; r < world; r++) atomicAdd_system(state[r] + 2 + (told & 1u), 1u);
+  *reinterpret_cast<volatile unsigned*>(mine + 4) = step;
+}
+
+// Closes a chain of deferred all-gathers: tells every rank that this rank's last step is complete
+// and returns when the last step's row on this rank is whole.
+struct GatherPeers {
+  unsigned* state[kMaxPeers];
+  int world, rank;
+};
+__global__ void gather_wait_kernel(const GatherPeers g, int* status) {
+  const unsigned* mine = g.state[g.rank];
+  const unsigned step = *reinterpret_cast<const volatile unsigned*>(mine);
   if (step == 0) return;
   const unsigned prev = step - 1u;
-  if (!wait_arrivals(state + 2 + (prev & 1u), (prev / 2u + 1u) * target)) atomicExch(status, 1);
+  announce_steps(g.state, g.world, g.rank, step);
+  if (!wait_arrivals(mine + 2 + (prev & 1u), (prev / 2u + 1u) * (unsigned)g.world)) atomicExch(status, 1);
 }
 
 struct alignas(64) TensorMaps {
@@ -361,7 +383,10 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     // the previous step's gathered row (which may be this launch's input) must be whole
     if (tid == 0) {
       const unsigned prev = step - 1u;
-      if (!wait_arrivals(p.state[p.rank] + 2 + (prev & 1u), (prev / 2u + 1u) * p.target)) atomicExch(p.status, 1);
+      // the previous launch has completed (griddepcontrol.wait) and its CTAs fenced their stores
+      if (blockIdx.x == 0) announce_steps(p.state, p.world, p.rank, step);
+      if (!wait_arrivals(p.state[p.rank] + 2 + (prev & 1u), (prev / 2u + 1u) * (unsigned)p.world))
+        atomicExch(p.status, 1);
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
   }
@@ -428,6 +453,16 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     if ((tid & 31) == 0) mbar_arrive(smem_u32(&empty[slot]));
   }
 
+  if (p.world > 0 && p.defer && tid == 0) {
+    // Count this CTA as past its main loop.  The last one to get here knows that every CTA of the
+    // launch has read `step`, so it may already advance it for the next launch (which reads it only
+    // after this launch has completed); the round trip of the atomic overlaps the phase reduction.
+    unsigned* mine = p.state[p.rank];
+    if (atomicAdd(mine + 1, 1u) == gridDim.x - 1) {
+      mine[1] = 0u;
+      *reinterpret_cast<volatile unsigned*>(mine) = step + 1u;
+    }
+  }
   // ---------------------------------------------- sum the phases, fixed order
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every consumer is done with the ring
   float* red = reinterpret_cast<float*>(ring);        // [phases][MR][TN]
@@ -518,6 +553,13 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     const size_t at = ((size_t)par * p.M + m) * p.n_total + p.n0 + col0 + c;
     for (int r = 0; r < p.world; r++) p.y[r][at] = sum;
   }
+  if (p.defer) {
+    // Deferred form: one system-scope fence per CTA behind a barrier makes the CTA's remote stores
+    // visible before it leaves; the next launch (or the closing wait) does the signalling.
+    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
+    if (tid == 0) __threadfence_system();
+    return;
+  }
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every store of this CTA is issued
   if (tid == 0) {
     __threadfence_system();                             // ... and ordered before the arrivals
@@ -526,7 +568,7 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     const unsigned ticket = atomicAdd(mine + 1, 1u);
     if (ticket == gridDim.x - 1) {                      // last CTA of this rank's grid
       // a peer that never arrives leaves the row invalid: the status word says so
-      if (!p.defer && !wait_arrivals(mine + 2 + par, (step / 2u + 1u) * p.target)) atomicExch(p.status, 1);
+      if (!wait_arrivals(mine + 2 + par, (step / 2u + 1u) * p.target)) atomicExch(p.status, 1);
       mine[1] = 0u;
       __threadfence();
       *reinterpret_cast<volatile unsigned*>(mine) = step + 1u;
@@ -765,10 +807,14 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
   return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_gather_wait(const unsigned* state, unsigned target, cudaStream_t s) {
+cudaError_t launch_gather_wait(unsigned* const* states, int world, int rank, cudaStream_t s) {
   int* status = kernel_status_ptr();
   if (!status) return cudaErrorUnknown;
-  gather_wait_kernel<<<1, 1, 0, s>>>(state, target, status);
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return cudaErrorInvalidValue;
+  GatherPeers g{};
+  g.world = world, g.rank = rank;
+  for (int r = 0; r < world; r++) g.state[r] = states[r];
+  gather_wait_kernel<<<1, 1, 0, s>>>(g, status);    // an ordinary launch: it starts after its predecessor has completed
   count_launch();
   return cudaGetLastError();
 }

@@ -161,7 +161,7 @@ class FusedGather:
         """Deferred mode: enqueue the wait that makes the last step's row whole on this rank."""
         from . import device as D
         if self.deferred and self._last:
-            D.allGatherWait(self.state, self.target(*self._last))
+            D.allGatherWait(self.world, self.rank, self.states)
 
     def read(self, half):
         """The gathered rows [M, N] of one half (after ``finish()`` in deferred mode, and a synchronize)."""

@@ -56,6 +56,44 @@ def main():
             print(f"world={world} kind={knd} M={M} K={K} N={N} fused={sm.fused}: worst err/bound {worst_all:.3f} "
                   f"failures(all ranks)={int(flag.item())}", flush=True)
         dist.barrier()
+    # ---- a real chain: each launch reads the row the launch before it gathered (no host round trip)
+    K = N = 4096
+    steps = 6
+    rng = np.random.default_rng(99)
+    ws = [(rng.standard_normal((K, N)) * 0.02).astype(np.float32) for _ in range(2)]
+    packs = [O.quantize_q4(w) for w in ws]
+    n0, n1 = P.column_shard(N, world, rank)
+    shards = []
+    for pk in packs:
+        sh = D.alloc((K // 32) * (n1 - n0) * 24, D.PRIVATE)
+        D.upload(sh, P.slice_packed_columns(pk, K // 32, N, 24, n0, n1))
+        shards.append(sh)
+    fg = P.FusedGather(1, N, world, rank, deferred=True)
+    base = D.devicePtr(fg.y)
+    halves = [D.wrapDeviceMemory(base + h * N * 4, N * 4) for h in range(2)]
+    x0 = rng.standard_normal((1, K)).astype(np.float32)
+    x_dev = D.alloc(K * 4, D.PRIVATE)
+    D.upload(x_dev, x0)
+    src = x_dev
+    for i in range(steps):                                   # enqueued back to back
+        half = fg.enqueue(4, src, shards[i & 1], K)
+        src = halves[half]
+    fg.finish()
+    D.synchronize()
+    assert D.kernelStatus() == 0, "a bounded device-side wait gave up"
+    got = fg.read((steps - 1) & 1)
+    want = x0
+    for i in range(steps):
+        want = O.matmul(want, packs[i & 1], K, N, "q4", threads=O.max_threads())
+    err = float(np.abs(got - want).max() / (np.abs(want).max() + 1e-30))
+    bad = int(not (err < 5e-3))
+    failures += bad
+    flag = torch.tensor([failures], device="cuda")
+    dist.all_reduce(flag)
+    if rank == 0:
+        print(f"world={world} chained gathers ({steps} launches, each reading its predecessor's gathered row): "
+              f"max err / max |y| = {err:.2e} failures(all ranks)={int(flag.item())}", flush=True)
+    dist.barrier()
     # ---- weights sharded along K, partial products summed over ranks
     for kind, M, K, N in [(4, 1, 4096, 4096), (8, 2, 2048, 1024), (4, 4, 14336, 4096), (4, 16, 2048, 1024)]:
         knd, bb = ("q4", 24) if kind == 4 else ("q8", 34)
