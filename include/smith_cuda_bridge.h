@@ -194,7 +194,7 @@ void* smith_ipc_import(void* ctx, const void* handle64, uint64_t bytes);
  * column shard b (n_local columns starting at column n0 of a row of n_total) and stores the
  * result slice into EVERY rank's gathered output through y_bufs[r] (rank r's buffer of
  * 2*M*n_total floats, local or IPC-imported), then adds its tile arrivals to every rank's
- * state_bufs[r] (32 bytes, zero-initialised once).  The launch completes when this rank's
+ * state_bufs[r] (16 bytes, zero-initialised once).  The launch completes when this rank's
  * own row has received the tiles of all ranks: `target` = sum over ranks of
  * smith_qgemv_tiles(kind, M, n_local_r, K).  The two halves of y are used alternately:
  * the k-th call (k = 0, 1, ...) on a state leaves its row in half k % 2.  The wait is
@@ -203,19 +203,25 @@ void* smith_ipc_import(void* ctx, const void* handle64, uint64_t bytes);
 int32_t smith_qmatmul_allgather(void* ctx, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total,
                                 uint64_t n0, uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world,
                                 uint32_t rank, void* const* y_bufs, void* const* state_bufs, uint32_t target);
-/* The same with flags.  SMITH_GATHER_DEFER (1): the threads store and fence their own outputs and leave --
- * no per-CTA arrival and no wait at the end of the launch (which keep SMs idle for microseconds).  The
- * next smith_qmatmul_allgather_ex call on the same state tells every rank that this rank's previous
- * step is complete (one thread, one fence) and waits for the other ranks' word before it reads its
- * activations -- by then its weights are already streaming, so the NVLink round trip is hidden.
- * A chain of such calls is closed by smith_allgather_wait (asynchronous, bounded like the others),
- * after which the last row is whole on this rank.  `target` is not used in this form. */
+/* The same with flags.  SMITH_GATHER_DEFER (1): the low-latency form.  A system-scope fence per CTA
+ * costs several microseconds per launch, so this form has none: every output travels as one 8-byte
+ * store {value bits, step + 1}, y_bufs[r] are then arrays of 2*M*n_total such pairs (zero-initialised
+ * once), and a reader accepts a pair only when it carries the tag of the step it expects.  The launch
+ * neither signals nor waits; the next smith_qmatmul_allgather_ex call on the same state polls the
+ * tags of the previous row before it reads its activations -- by then its weights are already
+ * streaming, so the NVLink latency is hidden -- and a chain of such calls is closed by
+ * smith_allgather_wait (asynchronous, bounded like the others), after which the last row is whole
+ * on this rank: pair i of half (k % 2) after the k-th call holds element i of the row.  `target`
+ * is not used in this form. */
 #define SMITH_GATHER_DEFER 1u
+/* With SMITH_GATHER_DEFER: the activations of this call are the row the previous call on the same
+ * state gathered (K == n_total); `a` is then only a placeholder for the very first call of a state. */
+#define SMITH_GATHER_INPUT_IS_PREVIOUS_ROW 2u
 int32_t smith_qmatmul_allgather_ex(void* ctx, uint32_t kind, void* a, void* b, uint64_t M, uint64_t n_total,
                                    uint64_t n0, uint64_t n_local, uint64_t K, uint64_t groups, uint32_t world,
                                    uint32_t rank, void* const* y_bufs, void* const* state_bufs, uint32_t target,
                                    uint32_t flags);
-int32_t smith_allgather_wait(void* ctx, uint32_t world, uint32_t rank, void* const* state_bufs);
+int32_t smith_allgather_wait(void* ctx, void* state_buf, void* y_buf, uint64_t M, uint64_t n_total);
 int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
 /* Fused GEMV + all-reduce for weights sharded along K (M <= 4; the Wo / down projections of a
  * tensor-parallel layer).  This rank multiplies its K-slice: a = [M, k_local] activations, b = its

@@ -911,17 +911,14 @@ int32_t smith_qmatmul_allgather(void* p, uint32_t kind, void* a, void* b, uint64
                                     target, 0);
 }
 
-int32_t smith_allgather_wait(void* p, uint32_t world, uint32_t rank, void* const* state_bufs) {
+int32_t smith_allgather_wait(void* p, void* state_buf, void* y_buf, uint64_t M, uint64_t n_total) {
   Context* c = as_ctx(p);
-  if (!c) return 1;
-  if (world < 1 || world > 8 || rank >= world || !state_bufs) return fail("smith_allgather_wait: bad world / rank / list");
-  unsigned* states[8];
-  for (uint32_t r = 0; r < world; r++) {
-    Buffer* bs = as_buf(state_bufs[r]);
-    if (!bs || !bs->dev || bs->bytes < 32) return fail("smith_allgather_wait: rank %u: not a state buffer", r);
-    states[r] = (unsigned*)bs->dev;
-  }
-  cudaError_t e = launch_gather_wait(states, (int)world, (int)rank, c->stream);
+  Buffer *bs = as_buf(state_buf), *by = as_buf(y_buf);
+  if (!c || !bs || !by) return 1;
+  if (!bs->dev || bs->bytes < 16 || !by->dev || by->bytes < 2 * M * n_total * 8)
+    return fail("smith_allgather_wait: not the state and row buffers of a deferred all-gather of %llu x %llu",
+                (unsigned long long)M, (unsigned long long)n_total);
+  cudaError_t e = launch_gather_wait((const unsigned*)bs->dev, by->dev, (int64_t)M, (int64_t)n_total, c->stream);
   return e == cudaSuccess ? 0 : fail("all-gather wait launch failed: %s", cudaGetErrorString(e));
 }
 
@@ -946,10 +943,14 @@ int32_t smith_qmatmul_allgather_ex(void* p, uint32_t kind, void* a, void* b, uin
   GemvGather g{};
   g.world = (int)world, g.rank = (int)rank, g.n0 = (int64_t)n0, g.n_total = (int64_t)n_total, g.target = target;
   g.defer = (flags & 1u) ? 1 : 0;
+  g.a_prev = (flags & 2u) ? 1 : 0;
+  if (g.a_prev && (!g.defer || K != n_total))
+    return fail("smith_qmatmul_allgather_ex: SMITH_GATHER_INPUT_IS_PREVIOUS_ROW needs SMITH_GATHER_DEFER and K == n_total");
   for (uint32_t r = 0; r < world; r++) {
     Buffer *by = as_buf(y_bufs[r]), *bs = as_buf(state_bufs[r]);
     if (!by || !bs || !by->dev || !bs->dev) return fail("smith_qmatmul_allgather: rank %u buffers have no device side", r);
-    if (by->bytes < 2 * M * n_total * 4 || bs->bytes < 32) return fail("smith_qmatmul_allgather: rank %u buffers too small", r);
+    if (by->bytes < 2 * M * n_total * (g.defer ? 8 : 4) || bs->bytes < 16)
+      return fail("smith_qmatmul_allgather: rank %u buffers too small", r);
     g.y[r] = (float*)by->dev;
     g.state[r] = (unsigned*)bs->dev;
   }

@@ -62,14 +62,16 @@ struct GemvGather {
   // state[r] continues with flags [2][tiles][8] after the four control words, and C receives the
   // sum over ranks (n0 = 0, n_total = N, target unused).
   int reduce;
-  // all-gather only: the CTAs store and leave; the next launch on the same state (or
-  // launch_gather_wait) signals this rank's step to all ranks and waits for theirs before it
-  // reads its activations (one arrival per rank and step; `target` is not used)
+  // all-gather only, deferred form: y[r] are arrays [2][M][n_total] of 8-byte {value, step + 1}
+  // pairs; the launch neither fences nor signals nor waits, and the next launch on the same state
+  // (or launch_gather_wait) polls the tags of this step's row (`target` is not used)
   int defer;
+  int a_prev;           // deferred form: read the activations from the previous step's gathered row (K == n_total)
 };
-// Signals this rank's last deferred step to every rank and returns when all ranks' arrivals for it
-// are here (bounded wait): the last row is then whole on this rank.
-cudaError_t launch_gather_wait(unsigned* const* states, int world, int rank, cudaStream_t s);
+// Returns when the last deferred all-gather step's row (tagged pairs in y) is whole on this rank
+// (bounded wait).
+cudaError_t launch_gather_wait(const unsigned* state, const void* y, int64_t M, int64_t n_total, cudaStream_t s);
+
 cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                                 int64_t K, int64_t groups, const GemvGather* g, cudaStream_t s);
 // Up to four weight matrices that share the activations A [M, K], as one launch:

@@ -115,13 +115,15 @@ struct Params {
   // Fused all-reduce instead (weights sharded along K): y[r] holds rank r's PARTIAL rows [2][M][N],
   // state[r] continues after its four control words with flags [2][tiles][kMaxPeers]; C gets the sum.
   int reduce;
-  // All-gather only, deferred form: the threads of a CTA store their outputs, fence them and leave --
-  // no barrier, no per-CTA arrival, no wait at the end.  One thread
-  // of the NEXT launch on the same state (or of the closing wait kernel) then tells
-  // every rank "my step s is complete" (one arrival per rank and step), and that launch waits for
-  // the other ranks' arrivals before it reads its activations -- after its producer has begun to
-  // stream weights, so the NVLink round trip hides behind the stream.
+  // All-gather only, deferred form.  A system-scope fence per CTA costs 4-6 us per launch on this
+  // part (measured, even with local memory only), so this form has none: every output travels as
+  // one 8-byte store {value bits, step + 1} into y[r] (then [2][M][n_total] such pairs), which a
+  // reader accepts only when the tag is the step it expects.  No counters, no arrivals, no wait at
+  // the end of the launch.  The NEXT launch on the same state (or the closing wait kernel) polls
+  // the tags of the previous row before it reads its activations -- after its producer has begun
+  // to stream weights, so the NVLink latency hides behind the stream.
   int defer;
+  int a_prev;             // deferred form: the activations ARE the previous step's gathered row (K == n_total)
 };
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) {
@@ -261,32 +263,48 @@ __device__ __forceinline__ bool wait_arrivals(const unsigned* counter, unsigned 
   }
 }
 
-// Deferred all-gather: tell every rank about the steps of this rank that are complete and not yet
-// announced (word 4 of the state counts the announced ones; the callers are serialised by stream
-// order, so a plain read-modify-write does).  One arrival per rank and step.
-__device__ __forceinline__ void announce_steps(unsigned* const* state, int world, int rank, unsigned step) {
-  unsigned* mine = state[rank];
-  unsigned told = *reinterpret_cast<volatile unsigned*>(mine + 4);
-  if (told >= step) return;
-  __threadfence_system();
-  for (; told < step; told++)
-    for (int r = 0; r < world; r++) atomicAdd_system(state[r] + 2 + (told & 1u), 1u);
-  *reinterpret_cast<volatile unsigned*>(mine + 4) = step;
+// Deferred all-gather: wait (bounded) until `count` {value, tag} pairs all carry `tag`; the calling
+// threads share the work.  Returns false if some pair never got there.
+__device__ __forceinline__ bool wait_tags(const uint2* row, int count, unsigned tag, int tid, int nthreads) {
+  // two pairs per 16-byte load (count is even: n_total is a multiple of 8), eight loads in flight per thread
+  const uint4* row4 = reinterpret_cast<const uint4*>(row);
+  const int n4 = count >> 1;
+  const long long t0 = clock64();
+  bool ok = true;
+  for (int base = tid; base < n4 && ok; base += 8 * nthreads) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int i = base + u * nthreads;
+      if (i < n4)
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(row4 + i) : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int i = base + u * nthreads;
+      if (i < n4) {
+        for (unsigned spin = 0; v[u].y != tag || v[u].w != tag; spin++) {
+          if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) {
+            ok = false;
+            break;
+          }
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(row4 + i) : "memory");
+        }
+      }
+    }
+  }
+  return ok;
 }
 
-// Closes a chain of deferred all-gathers: tells every rank that this rank's last step is complete
-// and returns when the last step's row on this rank is whole.
-struct GatherPeers {
-  unsigned* state[kMaxPeers];
-  int world, rank;
-};
-__global__ void gather_wait_kernel(const GatherPeers g, int* status) {
-  const unsigned* mine = g.state[g.rank];
-  const unsigned step = *reinterpret_cast<const volatile unsigned*>(mine);
+// Closes a chain of deferred all-gathers: returns when the last step's row on this rank is whole.
+__global__ void __launch_bounds__(256) gather_wait_kernel(const unsigned* state, const uint2* y, int count,
+                                                          int* status) {
+  const unsigned step = *reinterpret_cast<const volatile unsigned*>(state);
   if (step == 0) return;
   const unsigned prev = step - 1u;
-  announce_steps(g.state, g.world, g.rank, step);
-  if (!wait_arrivals(mine + 2 + (prev & 1u), (prev / 2u + 1u) * (unsigned)g.world)) atomicExch(status, 1);
+  if (!wait_tags(y + (size_t)(prev & 1u) * count, count, step, threadIdx.x, blockDim.x)) atomicExch(status, 1);
 }
 
 struct alignas(64) TensorMaps {
@@ -380,14 +398,11 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   unsigned step = 0;
   if (p.world > 0) step = *reinterpret_cast<volatile unsigned*>(p.state[p.rank]);  // advanced by the previous launch
   if (p.world > 0 && p.defer && step > 0) {
-    // the previous step's gathered row (which may be this launch's input) must be whole
-    if (tid == 0) {
-      const unsigned prev = step - 1u;
-      // the previous launch has completed (griddepcontrol.wait) and its CTAs fenced their stores
-      if (blockIdx.x == 0) announce_steps(p.state, p.world, p.rank, step);
-      if (!wait_arrivals(p.state[p.rank] + 2 + (prev & 1u), (prev / 2u + 1u) * (unsigned)p.world))
-        atomicExch(p.status, 1);
-    }
+    // the previous step's gathered row (which may be this launch's input) must be whole: every
+    // pair of it carries the tag `step`
+    const unsigned prev = step - 1u;
+    const uint2* row = reinterpret_cast<const uint2*>(p.y[p.rank]) + (size_t)(prev & 1u) * p.M * p.n_total;
+    if (!wait_tags(row, p.M * p.n_total, step, tid, nwarps * 32)) atomicExch(p.status, 1);
     asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
   }
   // Activations -> digit words (overlaps the first weight copies).
@@ -402,7 +417,22 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
       for (int u = 0; u < 4; u++) {
         const int i = i0 + u * stride;
         // clamp keeps whole warps in the shuffles; duplicates rewrite equal bytes
-        if (i < total) t[u] = __ldg(reinterpret_cast<const float4*>(p.A + (size_t)min(i >> 3, last) * 32) + (i & 7));
+        if (i < total) {
+          if (p.a_prev && step > 0) {
+            // four {value, tag} pairs of the previous row (its tags were checked above); volatile,
+            // so that no line cached two steps ago is read
+            const uint2* pairs = reinterpret_cast<const uint2*>(p.y[p.rank]) +
+                                 (size_t)((step - 1u) & 1u) * p.M * p.n_total + (size_t)min(i >> 3, last) * 32 + (i & 7) * 4;
+            uint4 a, b;
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(pairs) : "memory");
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(pairs + 2) : "memory");
+            t[u] = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+          } else {
+            t[u] = __ldg(reinterpret_cast<const float4*>(p.A + (size_t)min(i >> 3, last) * 32) + (i & 7));
+          }
+        }
       }
 #pragma unroll
       for (int u = 0; u < 4; u++) {
@@ -546,19 +576,25 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     return;
   }
   // ---------------------------------------------- fused all-gather over peer memory
+  if (p.defer) {
+    for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+      const int m = i / tn, c = i - m * tn;
+      float sum = 0.f;
+      for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
+      const size_t at = ((size_t)par * p.M + m) * p.n_total + p.n0 + col0 + c;
+      for (int r = 0; r < p.world; r++)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2*>(p.y[r]) + at),
+                     "r"(__float_as_uint(sum)), "r"(step + 1u)
+                     : "memory");
+    }
+    return;
+  }
   for (int i = tid; i < p.M * tn; i += nwarps * 32) {
     const int m = i / tn, c = i - m * tn;
     float sum = 0.f;
     for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
     const size_t at = ((size_t)par * p.M + m) * p.n_total + p.n0 + col0 + c;
     for (int r = 0; r < p.world; r++) p.y[r][at] = sum;
-  }
-  if (p.defer) {
-    // Deferred form: one system-scope fence per CTA behind a barrier makes the CTA's remote stores
-    // visible before it leaves; the next launch (or the closing wait) does the signalling.
-    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
-    if (tid == 0) __threadfence_system();
-    return;
   }
   asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // every store of this CTA is issued
   if (tid == 0) {
@@ -792,6 +828,8 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
     pl.p.target = g->target;
     pl.p.reduce = g->reduce;
     pl.p.defer = (g->defer && !g->reduce) ? 1 : 0;
+    pl.p.a_prev = (pl.p.defer && g->a_prev) ? 1 : 0;
+    if (pl.p.a_prev && (K != g->n_total)) return cudaErrorInvalidValue;
     if (g->reduce && !C) return cudaErrorInvalidValue;
     for (int r = 0; r < g->world; r++) {
       pl.p.y[r] = g->y[r];
@@ -807,14 +845,11 @@ cudaError_t launch_qgemv_gather(int kind, const float* A, const uint8_t* B, floa
   return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_gather_wait(unsigned* const* states, int world, int rank, cudaStream_t s) {
+cudaError_t launch_gather_wait(const unsigned* state, const void* y, int64_t M, int64_t n_total, cudaStream_t s) {
   int* status = kernel_status_ptr();
   if (!status) return cudaErrorUnknown;
-  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return cudaErrorInvalidValue;
-  GatherPeers g{};
-  g.world = world, g.rank = rank;
-  for (int r = 0; r < world; r++) g.state[r] = states[r];
-  gather_wait_kernel<<<1, 1, 0, s>>>(g, status);    // an ordinary launch: it starts after its predecessor has completed
+  // an ordinary launch: it starts after its predecessor has completed
+  gather_wait_kernel<<<1, 256, 0, s>>>(state, static_cast<const uint2*>(y), (int)(M * n_total), status);
   count_launch();
   return cudaGetLastError();
 }

@@ -91,7 +91,7 @@ SYMBOLS = {
                                         C.POINTER(_p), C.POINTER(_p), _u32]),
     "smith_qmatmul_allgather_ex": (_i32, [_p, _u32, _p, _p, _u64, _u64, _u64, _u64, _u64, _u64, _u32, _u32,
                                            C.POINTER(_p), C.POINTER(_p), _u32, _u32]),
-    "smith_allgather_wait": (_i32, [_p, _u32, _u32, C.POINTER(_p)]),
+    "smith_allgather_wait": (_i32, [_p, _p, _p, _u64, _u64]),
     "smith_qmatmul_multi": (_i32, [_p, _u32, _p, _u32, C.POINTER(_p), C.POINTER(_p), C.POINTER(_u64), _u64, _u64, _u64]),
     "smith_qmatmul_allreduce": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32, _u32, C.POINTER(_p),
                                        C.POINTER(_p)]),
@@ -413,6 +413,7 @@ def qgemvTiles(kind, M, N, K):
 
 
 GATHER_DEFER = 1
+GATHER_INPUT_IS_PREVIOUS_ROW = 2
 
 
 def qmatmulAllGather(kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, world, rank, yBuffers, stateBuffers,
@@ -423,8 +424,8 @@ def qmatmulAllGather(kind, aBuffer, bBuffer, M, nTotal, n0, nLocal, K, groups, w
                                           rank, ys, ss, target, flags), "qmatmul_allgather")
 
 
-def allGatherWait(world, rank, stateBuffers):
-    _check(lib.smith_allgather_wait(ctx(), world, rank, (_p * world)(*stateBuffers)), "allgather_wait")
+def allGatherWait(stateBuffer, yBuffer, M, nTotal):
+    _check(lib.smith_allgather_wait(ctx(), stateBuffer, yBuffer, M, nTotal), "allgather_wait")
 
 
 def qmatmulMulti(kind, aBuffer, bBuffers, cBuffers, Ns, M, K, groups):

@@ -104,9 +104,11 @@ class FusedGather:
     Owns this rank's row buffer (two halves used alternately) and its 16-byte control block,
     and holds IPC mappings of the other ranks' buffers.
 
-    ``deferred=True``: a launch does not wait for the peers' tiles; the next ``enqueue`` does, after
-    its weights have begun to stream (the NVLink round trip hides behind the stream), and
-    ``finish()`` closes the chain -- call it before reading the last row."""
+    ``deferred=True``: the low-latency form.  Outputs travel as 8-byte {value, step tag} stores (the
+    row buffers hold such pairs), nothing is fenced, signalled or awaited at the end of a launch; the
+    next ``enqueue`` polls the previous row's tags after its weights have begun to stream (the NVLink
+    latency hides behind the stream), and ``finish()`` closes the chain -- call it before reading
+    the last row."""
     capturable = True
     kernels_per_call = 0    # the gather is part of the matmul launch
 
@@ -116,10 +118,11 @@ class FusedGather:
         self.deferred = deferred
         self._last = None
         self.spans = [column_shard(N, world, r) for r in range(world)]
-        self.y = D.alloc(2 * M * N * 4, D.PRIVATE)
+        self.elem = 8 if deferred else 4
+        self.y = D.alloc(2 * M * N * self.elem, D.PRIVATE)
         self.state = D.alloc(256, D.PRIVATE)
         D.upload(self.state, np.zeros(64, np.uint32))
-        D.upload(self.y, np.zeros(2 * M * N, np.float32))
+        D.upload(self.y, np.zeros(2 * M * N * self.elem // 4, np.uint32))
         self.ys, self.states = [None] * world, [None] * world
         self.ys[rank], self.states[rank] = self.y, self.state
         if world > 1:
@@ -129,7 +132,7 @@ class FusedGather:
             dist.all_gather_object(handles, mine, group=group)
             for r in range(world):
                 if r != rank:
-                    self.ys[r] = D.ipcImport(handles[r][0], 2 * M * N * 4)
+                    self.ys[r] = D.ipcImport(handles[r][0], 2 * M * N * self.elem)
                     self.states[r] = D.ipcImport(handles[r][1], 256)
             dist.barrier(group=group)     # everyone has mapped everyone before the first store
         self.calls = 0
@@ -145,13 +148,15 @@ class FusedGather:
             self._targets[key] = sum(tiles)
         return self._targets[key]
 
-    def enqueue(self, kind, a_buf, packed_shard_buf, K):
-        """Asynchronous fused matmul + all-gather; returns which half of the row buffer it fills."""
+    def enqueue(self, kind, a_buf, packed_shard_buf, K, from_previous=False):
+        """Asynchronous fused matmul + all-gather; returns which half of the row buffer it fills.
+        ``from_previous`` (deferred form, K == N): the activations are the row the previous call gathered."""
         from . import device as D
         n0, n1 = self.spans[self.rank]
         D.qmatmulAllGather(kind, a_buf, packed_shard_buf, self.M, self.N, n0, n1 - n0, K, K // 32, self.world,
                            self.rank, self.ys, self.states, self.target(kind, K),
-                           D.GATHER_DEFER if self.deferred else 0)
+                           (D.GATHER_DEFER | (D.GATHER_INPUT_IS_PREVIOUS_ROW if from_previous else 0))
+                           if self.deferred else 0)
         self._last = (kind, K)
         half = self.calls & 1
         self.calls += 1
@@ -161,12 +166,15 @@ class FusedGather:
         """Deferred mode: enqueue the wait that makes the last step's row whole on this rank."""
         from . import device as D
         if self.deferred and self._last:
-            D.allGatherWait(self.world, self.rank, self.states)
+            D.allGatherWait(self.state, self.y, self.M, self.N)
 
     def read(self, half):
         """The gathered rows [M, N] of one half (after ``finish()`` in deferred mode, and a synchronize)."""
         from . import device as D
         n = self.M * self.N
+        if self.deferred:                 # {value, tag} pairs
+            pairs = D.download(self.y, n * 8, np.float32, offset=half * n * 8).reshape(n, 2)
+            return np.ascontiguousarray(pairs[:, 0]).reshape(self.M, self.N)
         return D.download(self.y, n * 4, np.float32, offset=half * n * 4).reshape(self.M, self.N)
 
     def close(self):

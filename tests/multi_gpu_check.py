@@ -58,7 +58,7 @@ def main():
         dist.barrier()
     # ---- a real chain: each launch reads the row the launch before it gathered (no host round trip)
     K = N = 4096
-    steps = 6
+    steps = 24
     rng = np.random.default_rng(99)
     ws = [(rng.standard_normal((K, N)) * 0.02).astype(np.float32) for _ in range(2)]
     packs = [O.quantize_q4(w) for w in ws]
@@ -69,15 +69,11 @@ def main():
         D.upload(sh, P.slice_packed_columns(pk, K // 32, N, 24, n0, n1))
         shards.append(sh)
     fg = P.FusedGather(1, N, world, rank, deferred=True)
-    base = D.devicePtr(fg.y)
-    halves = [D.wrapDeviceMemory(base + h * N * 4, N * 4) for h in range(2)]
     x0 = rng.standard_normal((1, K)).astype(np.float32)
     x_dev = D.alloc(K * 4, D.PRIVATE)
     D.upload(x_dev, x0)
-    src = x_dev
     for i in range(steps):                                   # enqueued back to back
-        half = fg.enqueue(4, src, shards[i & 1], K)
-        src = halves[half]
+        fg.enqueue(4, x_dev, shards[i & 1], K, from_previous=i > 0)
     fg.finish()
     D.synchronize()
     assert D.kernelStatus() == 0, "a bounded device-side wait gave up"

@@ -355,6 +355,31 @@ def test_fused_gather_deferred_chain_world_of_one():
         b.free()
 
 
+def test_fused_gather_deferred_chain_reads_its_previous_row():
+    # each launch takes the row gathered by the launch before it as its activations, on the device
+    from smith_b200.parallel import FusedGather
+    K = N = 1024
+    rng = np.random.default_rng(24)
+    packs = [O.quantize_q4((rng.standard_normal((K, N)) * 0.05).astype(np.float32)) for _ in range(2)]
+    pbs = [DevBuf.of(p) for p in packs]
+    x0 = rng.standard_normal((1, K)).astype(np.float32)
+    xb = DevBuf.of(x0)
+    fg = FusedGather(1, N, 1, 0, deferred=True)
+    steps = 5
+    for i in range(steps):
+        fg.enqueue(4, xb.handle, pbs[i & 1].handle, K, from_previous=i > 0)
+    fg.finish()
+    device.synchronize()
+    assert device.kernelStatus() == 0
+    want = x0
+    for i in range(steps):
+        want = matmul_on_device(want, packs[i & 1], K, N, "q4", device.PATH_GEMV)
+    assert bits_equal(fg.read((steps - 1) & 1), want)
+    fg.close()
+    for b in pbs + [xb]:
+        b.free()
+
+
 def test_fused_gather_two_shards_emulated_on_one_gpu():
     # Two ranks' launches run one after the other on this GPU, each storing its column slice into
     # both ranks' rows.  The first launch is told to expect only its own tiles (its peer has not run
