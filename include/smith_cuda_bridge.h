@@ -226,13 +226,14 @@ int32_t smith_qgemv_tiles(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
 /* Fused GEMV + all-reduce for weights sharded along K (M <= 4; the Wo / down projections of a
  * tensor-parallel layer).  This rank multiplies its K-slice: a = [M, k_local] activations, b = its
  * groups_local = k_local / 32 group-rows of all N columns (a contiguous byte range of the packed
- * matrix).  Each CTA stores its tile of partial sums into this rank's partial buffer
- * partial_bufs[rank] (2*M*N floats), flags the tile in every rank's state_bufs[r]
- * (smith_qmatmul_allreduce_state_bytes bytes, zero-initialised once; local or IPC-imported), waits
- * -- bounded, ~0.2 s -- for the same tile of all ranks, adds the partial tiles in rank order
- * (identical bits on every rank) and writes the sum to out [M, N].  If a peer never arrives
- * smith_kernel_status reports it.  Every rank must make the same sequence of calls.  Asynchronous;
- * may be captured in a graph. */
+ * matrix).  partial_bufs[r] is rank r's slot array: 2 * world * M * N pairs of {value, step tag}
+ * (8 bytes each, zero-initialised once; local or IPC-imported).  Every thread pushes its partial sums
+ * into this rank's slot on every rank with single 8-byte stores -- no fence: a pair is valid
+ * exactly when it carries the step's tag -- then polls (bounded, ~0.2 s) the same elements of all
+ * slots in its own memory, adds them in rank order (identical bits on every rank) and writes the sum
+ * to out [M, N].  state_bufs[r]: smith_qmatmul_allreduce_state_bytes bytes, zero-initialised once.
+ * If a peer never arrives smith_kernel_status reports it.  Every rank must make the same sequence
+ * of calls.  Asynchronous; may be captured in a graph. */
 int32_t smith_qmatmul_allreduce(void* ctx, uint32_t kind, void* a, void* b, void* out, uint64_t M, uint64_t N,
                                 uint64_t k_local, uint64_t groups_local, uint32_t world, uint32_t rank,
                                 void* const* partial_bufs, void* const* state_bufs);

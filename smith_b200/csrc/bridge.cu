@@ -981,7 +981,7 @@ int32_t smith_qmatmul_allreduce(void* p, uint32_t kind, void* a, void* b, void* 
   for (uint32_t r = 0; r < world; r++) {
     Buffer *by = as_buf(partial_bufs[r]), *bs = as_buf(state_bufs[r]);
     if (!by || !bs || !by->dev || !bs->dev) return fail("smith_qmatmul_allreduce: rank %u buffers have no device side", r);
-    if (by->bytes < 2 * M * N * 4 || bs->bytes < smith_qmatmul_allreduce_state_bytes(kind, M, N, k_local))
+    if (by->bytes < 2 * (uint64_t)world * M * N * 8 || bs->bytes < smith_qmatmul_allreduce_state_bytes(kind, M, N, k_local))
       return fail("smith_qmatmul_allreduce: rank %u buffers too small", r);
     g.y[r] = (float*)by->dev;
     g.state[r] = (unsigned*)bs->dev;
@@ -995,7 +995,7 @@ int32_t smith_qmatmul_allreduce(void* p, uint32_t kind, void* a, void* b, void* 
 uint64_t smith_qmatmul_allreduce_state_bytes(uint32_t kind, uint64_t M, uint64_t N, uint64_t k_local) {
   const int tiles = qgemv_tiles((int)kind, M, N, k_local);
   if (tiles < 0) return 0;
-  return 16 + (uint64_t)2 * tiles * 8 * 4;      // control words + flags [2][tiles][8]
+  return 16;                                      // control words {step, ticket}
 }
 
 // ---------------------------------------------------------------- graphs

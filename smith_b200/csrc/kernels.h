@@ -58,9 +58,9 @@ struct GemvGather {
   int world, rank;
   int64_t n0, n_total;
   unsigned target;      // CTAs (tiles) arriving per step, summed over ranks
-  // reduce != 0: weights are sharded along K instead; y[r] are the ranks' partial rows [2][M][N],
-  // state[r] continues with flags [2][tiles][8] after the four control words, and C receives the
-  // sum over ranks (n0 = 0, n_total = N, target unused).
+  // reduce != 0: weights are sharded along K instead; y[r] are rank r's slots [2][world][M][N] of
+  // {value, step + 1} pairs (one slot per contributing rank) and C receives the sum over ranks
+  // (n0 = 0, n_total = N, target unused).
   int reduce;
   // all-gather only, deferred form: y[r] are arrays [2][M][n_total] of 8-byte {value, step + 1}
   // pairs; the launch neither fences nor signals nor waits, and the next launch on the same state

@@ -55,15 +55,15 @@
 //    because its step cannot complete without the other's arrivals), and the
 //    step number lives in device memory so that a captured graph can be replayed.
 //
-//    With weights sharded along K the same kernel ends in a fused all-reduce: a CTA stores its
-//    tile of partial sums into this rank's partial buffer, writes "tile t of step s is there" flags
-//    into every rank's flag array (remote stores), waits -- bounded -- for the flags of the same tile
-//    from all ranks (the ranks tile N identically), then reads the peers' partial tiles over NVLink,
-//    adds them in rank order (so every rank gets the same bits) and writes the finished tile.
-//    Tile-level flags mean a CTA waits only for the CTAs that work on its columns elsewhere, which
-//    run at the same time.  Partial buffers and flags are double-buffered by step parity; a rank
-//    writes them only after its previous launch has completed (griddepcontrol.wait), so it cannot
-//    run further than one step ahead of a peer that still reads them.
+//    With weights sharded along K the same kernel ends in a fused all-reduce: every thread pushes
+//    its partial sums as tagged pairs into this rank's slot on every rank (remote 8-byte stores),
+//    polls -- bounded -- the same elements of all ranks' slots in its own memory, adds them in rank
+//    order (so every rank gets the same bits) and writes the finished outputs.  The ranks tile N
+//    identically, so a CTA waits only for the CTAs that work on its columns elsewhere, which run at
+//    the same time.  Slots are double-buffered by step parity; a rank writes them only after its
+//    previous launch has completed (griddepcontrol.wait), so it cannot run further than one step
+//    ahead of a peer that still reads them.  No system-scope fence anywhere: on this part one costs
+//    several microseconds per CTA.
 //
 // Waits are time-bounded as in pipeline.cuh.
 #include <cuda.h>
@@ -112,8 +112,8 @@ struct Params {
   unsigned* state[kMaxPeers];
   int world, rank, n0, n_total;
   unsigned target;  // tiles that arrive per step, summed over all ranks
-  // Fused all-reduce instead (weights sharded along K): y[r] holds rank r's PARTIAL rows [2][M][N],
-  // state[r] continues after its four control words with flags [2][tiles][kMaxPeers]; C gets the sum.
+  // Fused all-reduce instead (weights sharded along K): y[r] holds rank r's slots [2][world][M][N] of
+  // {value, step + 1} pairs, one slot per contributing rank; C gets the sum.
   int reduce;
   // All-gather only, deferred form.  A system-scope fence per CTA costs 4-6 us per launch on this
   // part (measured, even with local memory only), so this form has none: every output travels as
@@ -514,58 +514,46 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   const unsigned par = step & 1u;
   if (p.reduce) {
     // -------------------------------------------- fused all-reduce over peer memory
-    const size_t half = (size_t)par * p.M * Nm;
-    float* mine_y = p.y[p.rank] + half;
-    for (int i = tid; i < p.M * tn; i += nwarps * 32) {
+    // y[r]: rank r's slots [2][world][M][N] of {value, step + 1} pairs.  Each thread pushes its partial
+    // sums into this rank's slot on every rank (one 8-byte store each: no fence is needed, a pair is
+    // valid exactly when its tag is this step's), then polls the same elements of all slots in its
+    // OWN memory and adds them in rank order, so every rank ends with the same bits.
+    const size_t slot = (size_t)p.M * Nm;
+    for (int i = tid; i < p.M * tn; i += nwarps * 32) {       // push everything first
       const int m = i / tn, c = i - m * tn;
       float sum = 0.f;
       for (int ph = 0; ph < p.phases; ph++) sum += red[((size_t)ph * MR + m) * p.TN + c];
-      mine_y[(size_t)m * Nm + col0 + c] = sum;
+      const size_t mine_at = ((size_t)par * p.world + p.rank) * slot + (size_t)m * Nm + col0 + c;
+      for (int r = 0; r < p.world; r++)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2*>(p.y[r]) + mine_at),
+                     "r"(__float_as_uint(sum)), "r"(step + 1u)
+                     : "memory");
     }
-    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));  // the partial tile is stored
-    const size_t flag_at = 4 + ((size_t)par * gridDim.x + blockIdx.x) * kMaxPeers;
-    int* wait_ok = reinterpret_cast<int*>(smem + 2 * kMaxStages * 8 + 8);
-    if (tid == 0) *wait_ok = 1;
-    if (tid < p.world) {
-      __threadfence_system();                             // partial tile before the flag, system-wide
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.state[tid] + flag_at + p.rank), "r"(step + 1u)
-                   : "memory");
-      // this rank's flags from rank `tid`, polled in local memory
-      const unsigned* f = p.state[p.rank] + flag_at + tid;
-      const long long t0 = clock64();
-      bool there = false;
-      for (unsigned spin = 0;; spin++) {
-        unsigned seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-        if (seen >= step + 1u) {
-          there = true;
-          break;
+    bool there = true;
+    const long long t0 = clock64();
+    for (int i = tid; i < p.M * tn && there; i += nwarps * 32) {  // then collect
+      const int m = i / tn, c = i - m * tn;
+      const uint2* local = reinterpret_cast<const uint2*>(p.y[p.rank]) + (size_t)par * p.world * slot +
+                           (size_t)m * Nm + col0 + c;
+      float total = 0.f;
+      for (int r = 0; r < p.world && there; r++) {
+        unsigned v = 0, t;
+        for (unsigned spin = 0;; spin++) {
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(t) : "l"(local + (size_t)r * slot) : "memory");
+          if (t == step + 1u) break;
+          if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) {
+            there = false;                                // a peer never arrived: the result is not valid
+            break;
+          }
         }
-        if ((spin & 63u) == 63u && clock64() - t0 > kWaitLimitCycles) break;
+        total += __uint_as_float(v);
       }
-      if (!there) {
-        *wait_ok = 0;
-        atomicExch(p.status, 1);                          // a peer never arrived: the result is not valid
-      }
+      if (there) Cm[(size_t)m * Nm + col0 + c] = total;
     }
-    asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
-    if (*reinterpret_cast<volatile int*>(wait_ok)) {
-      for (int i = tid; i < p.M * tn; i += nwarps * 32) {
-        const int m = i / tn, c = i - m * tn;
-        const size_t at = half + (size_t)m * Nm + col0 + c;
-        float sum = 0.f;
-        for (int r = 0; r < p.world; r++) {
-          float v;                                        // volatile: never a line cached two steps ago
-          asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p.y[r] + at) : "memory");
-          sum += v;
-        }
-        Cm[(size_t)m * Nm + col0 + c] = sum;
-      }
-    }
+    if (!there) atomicExch(p.status, 1);
     asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32));
     if (tid == 0) {
       unsigned* mine = p.state[p.rank];
-      __threadfence();
       const unsigned ticket = atomicAdd(mine + 1, 1u);
       if (ticket == gridDim.x - 1) {                      // last CTA of this rank's grid
         mine[1] = 0u;

@@ -190,12 +190,13 @@ class FusedGather:
 
 class FusedReduce:
     """Sum over ranks of K-sharded partial products, formed by the GEMV kernel itself (M <= 4): every
-    rank's kernel flags each finished tile of partial sums in every rank's flag array, then reads
-    the peers' tiles through peer-mapped memory and adds them in rank order.  No NCCL call on the
-    data path; capturable in a CUDA graph; every rank ends with the same bits.
+    rank's kernel pushes its partial sums as {value, step tag} pairs into its slot on every rank
+    (8-byte stores through peer-mapped memory, no fences), polls all ranks' slots in its own memory
+    and adds them in rank order.  No NCCL call on the data path; capturable in a CUDA graph; every
+    rank ends with the same bits.
 
-    Owns this rank's partial buffer (two halves used alternately) and its state block, and holds
-    IPC mappings of the other ranks'."""
+    Owns this rank's slot array (2 x world x M x N pairs) and its state block, and holds IPC mappings
+    of the other ranks'."""
     capturable = True
     kernels_per_call = 0    # the reduction is part of the matmul launch
 
@@ -205,10 +206,11 @@ class FusedReduce:
         sbytes = D.qmatmulAllReduceStateBytes(kind, M, N, k_local)
         if sbytes == 0:
             raise D.SmithError("smith: the GEMV kernel does not take this shard shape")
-        self.partial = D.alloc(2 * M * N * 4, D.PRIVATE)
-        self.state = D.alloc(sbytes, D.PRIVATE)
-        D.upload(self.state, np.zeros(sbytes // 4, np.uint32))
-        D.upload(self.partial, np.zeros(2 * M * N, np.float32))
+        self.pbytes = 2 * world * M * N * 8
+        self.partial = D.alloc(self.pbytes, D.PRIVATE)
+        self.state = D.alloc(max(sbytes, 256), D.PRIVATE)
+        D.upload(self.state, np.zeros(max(sbytes, 256) // 4, np.uint32))
+        D.upload(self.partial, np.zeros(self.pbytes // 4, np.uint32))
         self.partials, self.states = [None] * world, [None] * world
         self.partials[rank], self.states[rank] = self.partial, self.state
         if world > 1:
@@ -218,8 +220,8 @@ class FusedReduce:
             dist.all_gather_object(handles, mine, group=group)
             for r in range(world):
                 if r != rank:
-                    self.partials[r] = D.ipcImport(handles[r][0], 2 * M * N * 4)
-                    self.states[r] = D.ipcImport(handles[r][1], sbytes)
+                    self.partials[r] = D.ipcImport(handles[r][0], self.pbytes)
+                    self.states[r] = D.ipcImport(handles[r][1], max(sbytes, 256))
             dist.barrier(group=group)     # everyone has mapped everyone before the first flag is written
 
     def enqueue(self, a_buf, packed_shard_buf, out_buf):

@@ -471,10 +471,11 @@ def test_fused_reduce_world_of_one_and_alternating_halves():
 
 
 def test_fused_reduce_two_k_shards_with_a_preseeded_peer():
-    # Rank 0 of a world of two runs alone on this GPU.  Its peer's partial rows and "tile is there"
-    # flags are written by the host beforehand, so the launch never waits on another launch (two
-    # kernels that wait on each other must never share a GPU); what is checked is rank 0's side of
-    # the protocol: partial tile stored, flags written to both ranks, peers' partials added in rank order.
+    # Rank 0 of a world of two runs alone on this GPU.  Its peer's slot (tagged partial sums for the
+    # first two steps) is written by the host beforehand, so the launch never waits on another launch
+    # (two kernels that wait on each other must never share a GPU); what is checked is rank 0's side
+    # of the protocol: its partials pushed with the step's tag into its slot on both ranks, the
+    # slots added in rank order.
     from smith_b200 import parallel as P
     K, N, M, world = 2048, 1536, 3, 2
     rng = np.random.default_rng(32)
@@ -486,15 +487,14 @@ def test_fused_reduce_two_k_shards_with_a_preseeded_peer():
     h0, h1 = P.group_shard(G, world, 1)
     kl = (g1 - g0) * 32
     peer_partial = O.matmul(a[:, h0 * 32:h1 * 32], P.slice_packed_groups(packed, G, N, 34, h0, h1), (h1 - h0) * 32, N, "q8")
-    sbytes = device.qmatmulAllReduceStateBytes(8, M, N, kl)
-    tiles = device.qgemvTiles(8, M, N, kl)
-    assert sbytes == 16 + 2 * tiles * 8 * 4
-    mine_state = np.zeros(sbytes // 4, np.uint32)
-    flags = mine_state[4:].reshape(2, tiles, 8)
-    flags[:, :, 1] = 0x7fffffff                             # the peer's tiles of every step "are there"
-    partials = [DevBuf.of(np.zeros(2 * M * N, np.float32)),
-                DevBuf.of(np.concatenate([peer_partial.reshape(-1), peer_partial.reshape(-1)]).astype(np.float32))]
-    states = [DevBuf.of(mine_state), DevBuf.of(np.zeros(sbytes // 4, np.uint32))]
+    assert device.qmatmulAllReduceStateBytes(8, M, N, kl) == 16
+    # slots [2][world][M][N] of (value bits, tag): the peer's slot of half h carries tag h + 1
+    slots = np.zeros((2, world, M * N, 2), np.uint32)
+    for h in range(2):
+        slots[h, 1, :, 0] = peer_partial.reshape(-1).view(np.uint32)
+        slots[h, 1, :, 1] = h + 1
+    partials = [DevBuf.of(slots), DevBuf.of(np.zeros_like(slots))]
+    states = [DevBuf.of(np.zeros(64, np.uint32)), DevBuf.of(np.zeros(64, np.uint32))]
     ab = DevBuf.of(np.ascontiguousarray(a[:, g0 * 32:g1 * 32]))
     shard = DevBuf.of(P.slice_packed_groups(packed, G, N, 34, g0, g1))
     out = DevBuf.of(np.zeros(M * N, np.float32))
@@ -507,11 +507,12 @@ def test_fused_reduce_two_k_shards_with_a_preseeded_peer():
         got = out.get(np.float32).reshape(M, N)
         ok, worst = within_tolerance(got, want, a, packed, K, N, "q8", REL)
         assert ok, (call, worst)
-        own = partials[0].get(np.float32).reshape(2, M, N)[call]
+        mine = partials[0].get(np.uint32).reshape(2, world, M * N, 2)
+        own = mine[call, 0, :, 0].copy().view(np.float32).reshape(M, N)
+        assert (mine[call, 0, :, 1] == call + 1).all()      # own partials carry this step's tag
         assert np.array_equal(got, own + peer_partial)      # rank order: own partial first, then the peer's
-        peer_flags = states[1].get(np.uint32)[4:].reshape(2, tiles, 8)
-        assert (peer_flags[call, :, 0] == call + 1).all()   # rank 0 announced every tile of this step to its peer
-        assert (states[0].get(np.uint32)[4:].reshape(2, tiles, 8)[call, :, 0] == call + 1).all()
+        at_peer = partials[1].get(np.uint32).reshape(2, world, M * N, 2)
+        assert np.array_equal(at_peer[call, 0], mine[call, 0])   # ... and went to the peer's memory too
     assert states[0].get(np.uint32)[0] == 2                 # two steps completed
     for b in partials + states + [ab, shard, out]:
         b.free()
