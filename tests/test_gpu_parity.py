@@ -110,8 +110,13 @@ def test_matmul_each_path_where_supported(kind, path):
               device.PATH_DECODE: [(1, 4096, 1024), (5, 1024, 256), (16, 2048, 640), (8, 4096, 104), (7, 4128, 136), (13, 96, 8),
                                    (9, 14336, 256), (24, 4096, 512), (32, 1024, 264), (20, 2048, 96), (17, 8192, 128)],
               device.PATH_GEMV: [(1, 4096, 1024), (2, 1024, 256), (4, 2048, 640), (3, 4096, 104), (1, 14336, 512),
-                                 (1, 64, 8), (2, 28672, 64)],
-              device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384), (300, 1056, 72)]}[path]
+                                 (1, 64, 8), (2, 28672, 64),
+                                 # tensor-map boxes (narrow tiles, >= 192 group-rows) with ragged edges:
+                                 # partial last stage, partial last tile, Q8's 8-column quantum
+                                 (3, 6176, 1000), (1, 8192, 8200), (4, 6208, 2056)],
+              device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384), (300, 1056, 72),
+                                   # two k-blocks per hand-off with a zero tail, narrow column tiles, ragged N
+                                   (33, 1024, 48), (100, 4160, 1024), (130, 1056, 1000)]}[path]
     for M, K, N in shapes:
         a, w = _data(M + K + N + path, M, K, N)
         packed = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
