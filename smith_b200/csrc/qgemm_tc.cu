@@ -36,7 +36,7 @@
 //                nibbles pair up in a 32-bit word); convert_activations stores
 //                the activations' k in the same order, so the dot products
 //                are unchanged and no byte shuffles are needed.
-//     warps 1-3, 16  epilogue: tcgen05.ld their 32-lane quarter of each
+//     warps 1-3, 16 and 5-7, 20  epilogue (even and odd chunks): tcgen05.ld their 32-lane quarter of each
 //                accumulator, 32 columns at a time, and store C rows.
 //   Weights of a tile are dequantised once and feed MT row tiles, so for
 //   M >= 256 the CUDA-core dequantisation stays below the tensor time.
@@ -503,8 +503,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
     }
   }
   // ---------------------------------------------------------------- epilogue
-  // Warps 1-3 (after their dequant work) and warp 16 read TMEM lane quarters 1-3 and 0.
-  if (warp == kEpilogueWarp0 || (warp >= 1 && warp <= 3)) {
+  // Two warps per TMEM lane quarter (a warp may read the quarter warp % 4): warps 1-3 and 16 take
+  // the even 32-column chunks, warps 5-7 and 20 the odd ones, each after its dequant work.
+  const int eset = (warp == kEpilogueWarp0 || (warp >= 1 && warp <= 3)) ? 0
+                   : (warp == kEpilogueWarp0 + 4 || (warp >= 5 && warp <= 7)) ? 1 : -1;
+  if (eset >= 0) {
     // warp-uniform: the TMEM loads below are warp-collective
     const bool got = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status));
     tc_fence_after();
@@ -516,14 +519,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_tc_kernel(const __grid_cons
       // turns the 32 x 32 chunk around in shared memory (the tile ring is idle by now) and stores
       // four whole 128-byte row segments per instruction.
       constexpr int kPitch = 36;                       // floats per staged row: 16-byte aligned, conflict-free
-      float* stage = reinterpret_cast<float*>(tiles) + q * (32 * kPitch);
+      float* stage = reinterpret_cast<float*>(tiles) + (eset * 4 + q) * (32 * kPitch);
       const int sr = lane >> 3, sc = (lane & 7) * 4;   // this lane's row (of each 4) and column in the read-back
 #pragma unroll 1
       for (int t = 0; t < MT; t++) {
         const int rbase = row0 + t * kBM + q * 32;
         const float inv = (KIND == 8 && rbase + lane < p.M) ? p.row_inv[rbase + lane] : 1.f;
 #pragma unroll 1
-        for (int c = 0; c < p.BN; c += 32) {
+        for (int c = eset * 32; c < p.BN; c += 64) {
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
           tmem_ld_wait();
