@@ -197,8 +197,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
     // ------------------------------------------------------------ producer warp
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    auto issue_weights = [&](int st) {
-      const int slot = st % p.stages;
+    auto issue_weights = [&](int st, int slot) {
       const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
       const uint32_t bar = smem_u32(&full[slot]);
       if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
@@ -208,8 +207,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
       for (int rr = lane; rr < rows; rr += 32)
         bulk_load(dst + rr * p.row_pitch, src + (size_t)rr * p.N * BB, row_bytes, bar, policy);
     };
-    auto issue_digits = [&](int st) {
-      const int slot = st % p.stages;
+    auto issue_digits = [&](int st, int slot) {
       const int rows = min(p.stage_rows, p.G - st * p.stage_rows);
       const uint32_t bar = smem_u32(&full[slot]);
       // bulk copies move multiples of 16 bytes: the scale span is rounded up (the scratch has slack)
@@ -224,20 +222,22 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
     };
     // weights of the first ring-full go out before anything waits on the previous launch
     const int first = min(nst, p.stages);
-    for (int st = 0; st < first; st++) issue_weights(st);
+    for (int st = 0; st < first; st++) issue_weights(st, st);      // first <= stages: slot == st
     if (!resident) {
       asm volatile("griddepcontrol.wait;" ::: "memory");   // quantise_rows has finished: the digits exist
-      for (int st = 0; st < first; st++) issue_digits(st);
+      for (int st = 0; st < first; st++) issue_digits(st, st);
     }
     bool live = true;
-    for (int st = first; st < nst && live; st++) {
-      const int slot = st % p.stages;
+    // slot and parity are carried along (no division by the run-time ring depth in the loop)
+    int slot = 0;
+    uint32_t par = 1;                               // second pass over the ring
+    for (int st = first; st < nst && live; st++, slot = (slot + 1 == p.stages) ? 0 : slot + 1, par ^= (slot == 0)) {
       int okw = 1;
-      if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag, p.status);
+      if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), par ^ 1u, abort_flag, p.status);
       live = __shfl_sync(0xffffffffu, okw, 0) != 0;
       if (!live) break;
-      issue_weights(st);
-      if (!resident) issue_digits(st);
+      issue_weights(st, slot);
+      if (!resident) issue_digits(st, slot);
     }
     return;  // consumers observe every full barrier, so the copies land before the CTA ends
   }
@@ -273,9 +273,10 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) qdecode_kerne
   const uint32_t res_dig_s = smem_u32(res_dig), res_sc_s = smem_u32(res_sc);
 
   bool ok = true;
-  for (int st = 0; st < nst && ok; st++) {
-    const int slot = st % p.stages;
-    ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag, p.status);
+  int slot = 0;
+  uint32_t par = 0;
+  for (int st = 0; st < nst && ok; st++, slot = (slot + 1 == p.stages) ? 0 : slot + 1, par ^= (slot == 0)) {
+    ok = mbar_wait(smem_u32(&full[slot]), par, abort_flag, p.status);
     if (ok && has_cols) {
       // 32-bit shared addresses: a per-thread constant part plus a per-row base that advances by a stride
       const uint32_t stage = ring_s + (uint32_t)slot * (uint32_t)p.stage_bytes;

@@ -367,11 +367,14 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     bool live = true;
-    for (int st = 0; st < nst && live; st++) {
-      const int slot = st % p.stages;
+    // slot and parity are carried along: a division by the run-time ring depth costs more
+    // instructions than the rest of the loop body
+    int slot = 0;
+    uint32_t par = 0;                               // parity of this pass over the ring
+    for (int st = 0; st < nst && live; st++, slot = (slot + 1 == p.stages) ? 0 : slot + 1, par ^= (slot == 0)) {
       if (st >= p.stages) {
         int okw = 1;
-        if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), ((st / p.stages) - 1) & 1, abort_flag, p.status);
+        if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), par ^ 1u, abort_flag, p.status);
         live = __shfl_sync(0xffffffffu, okw, 0) != 0;
         if (!live) break;
       }
@@ -457,9 +460,10 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   for (int m = 0; m < MR; m++) acc[m] = 0.f;
 
   bool ok = true;
-  for (int st = 0; st < nst && ok; st++) {
-    const int slot = st % p.stages;
-    ok = mbar_wait(smem_u32(&full[slot]), (st / p.stages) & 1, abort_flag, p.status);
+  int slot = 0;
+  uint32_t ring_par = 0;
+  for (int st = 0; st < nst && ok; st++, slot = (slot + 1 == p.stages) ? 0 : slot + 1, ring_par ^= (slot == 0)) {
+    ok = mbar_wait(smem_u32(&full[slot]), ring_par, abort_flag, p.status);
     if (ok && active) {
       const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
       const int g0 = st * p.stage_rows + phase;
