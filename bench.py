@@ -55,6 +55,11 @@ WORKLOADS = {
     # BASELINE configs[3]: every Q4 projection of an 8B-Llama-shaped decode step (32 layers + lm_head, 5.63 GB)
     "q4_llama8b_step_m1": dict(kind=4, M=1, step=dict(layers=32, dim=4096, kv=1024, ffn=14336, vocab=128256), std=0.02,
                                K=4096, N=14336),
+    "q4_llama8b_step_m16": dict(kind=4, M=16, step=dict(layers=32, dim=4096, kv=1024, ffn=14336, vocab=128256), std=0.02,
+                                K=4096, N=14336),       # configs[3] at batch 16 (single GPU)
+    # BASELINE configs[4]: the projections of a 70B-Llama-shaped decode step (80 layers + lm_head, 52.1 GB)
+    "q4_llama70b_step_m1": dict(kind=4, M=1, step=dict(layers=80, dim=8192, kv=1024, ffn=28672, vocab=128256), std=0.015,
+                                K=8192, N=28672),
 }
 DEFAULT = "q4_decode_gemv_4096x14336_m1"
 L2_BYTES = 126e6
@@ -218,6 +223,8 @@ def run_step_workload(args, wl):
     from smith_b200 import device as D
     from smith_b200 import parallel as P
     kind, M, st = wl["kind"], wl["M"], wl["step"]
+    if M > 4 and world > 1:
+        raise SystemExit("the step workloads shard over GPUs with the GEMV kernel's fused collectives (M <= 4)")
     dim, kv, ffn, vocab, layers = st["dim"], st["kv"], st["ffn"], st["vocab"], st["layers"]
     bb = 24
     D.ctx()
@@ -378,7 +385,8 @@ def run_step_workload(args, wl):
                        "sharding": ("tensor parallel over %d GPUs: wq/wk/wv/gate/up column-sharded, wo/down K-sharded "
                                     "with the all-reduce fused into the GEMV kernel, lm_head column-sharded with the "
                                     "all-gather fused into the GEMV kernel" % world) if world > 1 else "single GPU",
-                       "l2": "every launch reads its own packed matrix; one step's weights are 45 x the 126 MB L2",
+                       "l2": "every launch reads its own packed matrix; one step's weights are %d x the 126 MB L2"
+                             % (weight_bytes * world // L2_BYTES),
                        "timing": "CUDA events on the launch stream around replays of one CUDA graph per step, "
                                  "max over ranks"},
             "e2e": {"value": alg_all / (e2e_s / e2e_steps) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * M * dim * world,
@@ -391,14 +399,14 @@ def run_step_workload(args, wl):
                          else "fallback (no MEASURED_PEAKS.json)",
                          "peak_kind": "copy bandwidth", "frac_of_nominal": ach / 8000.0,
                          "algorithmic_per_launch": alg_bytes / len(ops),
-                         "note": "all %d launches of a step taken together (the GEMV kernel throughout)" % len(ops)},
+                         "note": "all %d launches of a step taken together" % len(ops)},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
             per_call, threads, ckind, sample = cpu_run(kind, M, dim, ffn, seconds=args.cpu_seconds)
             gate_bytes = algorithmic(kind, M, dim, ffn)[0]
             line["cpu_baseline"] = {"value": gate_bytes / per_call / 1e9, "unit": "GB/s", "cores": threads, "kind": ckind,
-                                    "sample": "the step's gate projection (4096 x 14336): " + sample}
+                                    "sample": "the step's gate projection (%d x %d): " % (dim, ffn) + sample}
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))
