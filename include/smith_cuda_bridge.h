@@ -207,9 +207,10 @@ int32_t smith_qmatmul_allgather(void* ctx, uint32_t kind, void* a, void* b, uint
  * costs several microseconds per launch, so this form has none: every output travels as one 8-byte
  * store {value bits, step + 1}, y_bufs[r] are then arrays of 2*M*n_total such pairs (zero-initialised
  * once), and a reader accepts a pair only when it carries the tag of the step it expects.  The launch
- * neither signals nor waits; the next smith_qmatmul_allgather_ex call on the same state polls the
- * tags of the previous row before it reads its activations -- by then its weights are already
- * streaming, so the NVLink latency is hidden -- and a chain of such calls is closed by
+ * neither signals nor waits; the next smith_qmatmul_allgather_ex call on the same state checks the
+ * tags of the previous row -- before it reads its activations if that row is its input (its
+ * weights are streaming by then, so the NVLink latency is hidden), otherwise after its main loop
+ * and before its own stores (a rank never runs further ahead than that) -- and a chain of such calls is closed by
  * smith_allgather_wait (asynchronous, bounded like the others), after which the last row is whole
  * on this rank: pair i of half (k % 2) after the k-th call holds element i of the row.  `target`
  * is not used in this form. */

@@ -120,8 +120,9 @@ struct Params {
   // one 8-byte store {value bits, step + 1} into y[r] (then [2][M][n_total] such pairs), which a
   // reader accepts only when the tag is the step it expects.  No counters, no arrivals, no wait at
   // the end of the launch.  The NEXT launch on the same state (or the closing wait kernel) polls
-  // the tags of the previous row before it reads its activations -- after its producer has begun
-  // to stream weights, so the NVLink latency hides behind the stream.
+  // the tags of the previous row: before it reads its activations if that row is its input (its
+  // producer streams weights meanwhile, so the NVLink latency hides behind the stream), else
+  // after its main loop and before its own stores.
   int defer;
   int a_prev;             // deferred form: the activations ARE the previous step's gathered row (K == n_total)
 };
@@ -403,9 +404,9 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
   asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned step = 0;
   if (COLL && p.world > 0) step = *reinterpret_cast<volatile unsigned*>(p.state[p.rank]);  // advanced by the previous launch
-  if (COLL && p.world > 0 && p.defer && step > 0) {
-    // the previous step's gathered row (which may be this launch's input) must be whole: every
-    // pair of it carries the tag `step`
+  if (COLL && p.world > 0 && p.defer && step > 0 && p.a_prev) {
+    // the previous step's gathered row is this launch's input and must be whole: every pair of it
+    // carries the tag `step`
     const unsigned prev = step - 1u;
     const uint2* row = reinterpret_cast<const uint2*>(p.y[p.rank]) + (size_t)(prev & 1u) * p.M * p.n_total;
     if (!wait_tags(row, p.M * p.n_total, step, tid, nwarps * 32)) atomicExch(p.status, 1);
@@ -490,6 +491,15 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_ke
     if ((tid & 31) == 0) mbar_arrive(smem_u32(&empty[slot]));
   }
 
+  if (COLL && p.world > 0 && p.defer && step > 0 && !p.a_prev) {
+    // This launch does not read the previous step's row, but its own stores below may only go out
+    // once that row is whole everywhere it is still being read: a rank must not run further ahead
+    // than that.  Checked here rather than at the start, the tags have long arrived and the check
+    // costs one pass over the row instead of a wait for the peers.
+    const unsigned prev = step - 1u;
+    const uint2* row = reinterpret_cast<const uint2*>(p.y[p.rank]) + (size_t)(prev & 1u) * p.M * p.n_total;
+    if (!wait_tags(row, p.M * p.n_total, step, tid, nwarps * 32)) atomicExch(p.status, 1);
+  }
   if (COLL && p.world > 0 && p.defer && tid == 0) {
     // Count this CTA as past its main loop.  The last one to get here knows that every CTA of the
     // launch has read `step`, so it may already advance it for the next launch (which reads it only
