@@ -323,8 +323,10 @@ __device__ __forceinline__ void tma_box_2d(uint32_t dst, const CUtensorMap* map,
 // COLL: the multi-GPU epilogues and waits are compiled only into the instantiations that use them;
 // inside the plain kernel they cost registers and broke the batching of the activation loads
 // (measured: 9.44 -> 9.73 us at 4096 x 14336, 11.35 -> 12.74 us for Q8).
-template <int KIND, int MR, int RPP, bool COLL>
-__global__ void __launch_bounds__(kMaxConsumerThreads + 32, kCtasPerSm) qgemv_kernel(const Params p,
+// WIDE (collective instantiations only): a CTA whose ring takes more than half an SM runs alone
+// there anyway, so its threads may use up to 128 registers; at 64 the collective code spills.
+template <int KIND, int MR, int RPP, bool COLL, bool WIDE>
+__global__ void __launch_bounds__(kMaxConsumerThreads + 32, WIDE ? 1 : kCtasPerSm) qgemv_kernel(const Params p,
                                                                                      const __grid_constant__ TensorMaps tm) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -739,12 +741,12 @@ void make_tensor_maps(Plan& pl, int kind, TensorMaps& tm) {
   if (!enc) pl.p.use_tma = 0;
 }
 
-template <int KIND, int MR, int RPP, bool COLL>
+template <int KIND, int MR, int RPP, bool COLL, bool WIDE>
 cudaError_t launch_one_mode(Plan& pl, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
-        cudaFuncSetAttribute(qgemv_kernel<KIND, MR, RPP, COLL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(qgemv_kernel<KIND, MR, RPP, COLL, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured = true;
   }
@@ -761,14 +763,16 @@ cudaError_t launch_one_mode(Plan& pl, cudaStream_t s) {
   cfg.numAttrs = 1;
   TensorMaps tm{};
   make_tensor_maps(pl, KIND, tm);
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR, RPP, COLL>, pl.p, tm);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_kernel<KIND, MR, RPP, COLL, WIDE>, pl.p, tm);
   count_launch();
   return e;
 }
 
 template <int KIND, int MR, int RPP>
 cudaError_t launch_one(Plan& pl, cudaStream_t s) {
-  return pl.p.world > 0 ? launch_one_mode<KIND, MR, RPP, true>(pl, s) : launch_one_mode<KIND, MR, RPP, false>(pl, s);
+  if (pl.p.world == 0) return launch_one_mode<KIND, MR, RPP, false, false>(pl, s);
+  return pl.smem > 113 * 1024 ? launch_one_mode<KIND, MR, RPP, true, true>(pl, s)
+                              : launch_one_mode<KIND, MR, RPP, true, false>(pl, s);
 }
 
 }  // namespace
