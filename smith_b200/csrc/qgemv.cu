@@ -35,8 +35,12 @@
 //    bytes / 8] 64-bit words; rows past the end are zero-filled).
 //  * The phases of a column are summed through shared memory in fixed order
 //    and each output is written once.  No atomics, no global scratch.
-//  * Tiles are sized so that two CTAs share an SM (more warps in flight, and
-//    one CTA's start-up and tail overlap the other's stream), and the kernel
+//  * One CTA per SM with a deep ring (about 190 KB) where the matrix fits one wave
+//    of tiles, two per SM (more warps in flight, one CTA's start-up and tail
+//    overlap the other's stream) where tiles come in several waves, and a
+//    half-SM footprint where a tile's whole K-slice fits it.  Up to four
+//    matrices that share the activations run as one launch (each owns a range
+//    of the grid's tiles).  The kernel
 //    is launched with programmatic stream serialisation: it lets its successor
 //    start as CTAs retire (griddepcontrol.launch_dependents at entry), and
 //    itself waits for its predecessor (griddepcontrol.wait) only before it
@@ -45,7 +49,7 @@
 //    decode step's layer stack) thus overlap launch gap, ramp-up and tail.
 //
 //  * Multi-GPU (weights sharded along N): the same kernel can end in a fused
-//    all-gather.  Instead of writing its columns to a local C, each CTA stores
+//    all-gather, in two forms.  Counted form: instead of writing its columns to a local C, each CTA stores
 //    them into every rank's gathered row through peer-mapped pointers (plain
 //    stores over NVLink), fences, and adds one arrival to every rank's counter.
 //    The last CTA of the grid to finish then waits -- bounded -- until its own
@@ -54,6 +58,9 @@
 //    are used alternately (a rank can run at most one step ahead of another,
 //    because its step cannot complete without the other's arrivals), and the
 //    step number lives in device memory so that a captured graph can be replayed.
+//    Low-latency form: every output travels as one 8-byte {value, step tag} store, nothing is
+//    fenced, counted or awaited at the end of a launch, and the next launch on the same state checks
+//    the tags of the previous row (see Params::defer).
 //
 //    With weights sharded along K the same kernel ends in a fused all-reduce: every thread pushes
 //    its partial sums as tagged pairs into this rank's slot on every rank (remote 8-byte stores),
