@@ -166,7 +166,6 @@ int32_t smith_q8_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
 #define SMITH_PATH_GEMV 4
 int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint64_t M, uint64_t N,
                       uint64_t K, uint64_t groups, uint32_t path);
-/* Which path 0 would resolve to for a shape (for tests and reports). */
 /* No counterpart in the reference, whose callers issue one matmul per weight matrix
  * (src/gguf_cache.js:121-171: wq, wk, wv on the same input; gate and up on the same input).
  * c_bufs[i] [M, n_list[i]] = a [M, K] x dequant(b_bufs[i]) for 1 to 4 packed matrices of the same K
@@ -175,7 +174,45 @@ int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint6
  * back to one launch per matrix.  Results are those of smith_qmatmul per matrix. */
 int32_t smith_qmatmul_multi(void* ctx, uint32_t kind, void* a, uint32_t count, void* const* b_bufs,
                             void* const* c_bufs, const uint64_t* n_list, uint64_t M, uint64_t K, uint64_t groups);
+/* Which path 0 would resolve to for a shape (for tests and reports). */
 int32_t smith_qmatmul_path(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
+/* No counterpart in the reference, whose decode step issues one matmul per weight matrix and one
+ * dispatch per pointwise op between them (src/gguf_cache.js:121-171: rmsnorm, wq/wk/wv, ..., wo, add,
+ * rmsnorm, gate, up, swiglu, down, add).  A LIST of GEMV-shaped products (M <= 4, one kind) that run
+ * as ONE persistent launch: one CTA per SM walks the list with its ring of weight stages never
+ * draining between matrices, so the start-up and tail every separate launch pays (2.7 of 9.0 us at
+ * 4096 x 14336) are paid once per list.  Item i computes
+ *     x   = gamma ? rmsnorm(a, gamma, eps) : a          (shaders/rmsnorm.metal:15-49; a is f32 [M,K])
+ *     p   = x * dequant(b)                              (shaders/matmul_q4.metal:34-65 / matmul_q8.metal:20-57)
+ *     p   = b2 ? silu(p) * (x * dequant(b2)) : p        (shaders/swiglu.metal:12-22; b = gate, b2 = up)
+ *     c   = residual ? residual + p : p                 (A.add, src/gguf_cache.js:153,165)
+ * Operands are buffers with a device side plus byte offsets, so rows of one arena can be chained.
+ * Items may read what earlier items write (and overwrite what earlier items read or wrote): such
+ * hazards are found when the list is created, from the operands' address ranges, and resolved on the
+ * device (the consumer of a hazard waits -- bounded -- for the producer's tiles; weights keep
+ * streaming meanwhile).  c must not overlap the item's own a; residual may be c itself.
+ * At most four mutually independent earlier items may conflict with one item.
+ * Results per item are those of smith_qmatmul on the GEMV path, with the pointwise operations in
+ * f32.  smith_qmatmul_list_create allocates device memory (not during capture);
+ * smith_qmatmul_list_run is asynchronous on the context's stream, allocates nothing and may be
+ * captured in a graph; runs of one list must not overlap on the GPU.  A bounded wait that gives up
+ * shows in smith_kernel_status; the list is usable again afterwards. */
+typedef struct SmithListItem {
+  void* a;          uint64_t a_offset;         /* f32 [M,K] */
+  void* b;          uint64_t b_offset;         /* packed [K/32][N][24 or 34 bytes] */
+  void* b2;         uint64_t b2_offset;        /* NULL, or the `up` matrix of a gate/up pair (same N, K) */
+  void* c;          uint64_t c_offset;         /* f32 [M,N] */
+  void* gamma;                                 /* NULL, or f32 [K] */
+  void* residual;   uint64_t residual_offset;  /* NULL, or f32 [M,N] */
+  uint64_t N, K;
+  float eps;                                   /* RMSNorm epsilon (used when gamma is set) */
+  uint32_t reserved;
+} SmithListItem;
+void* smith_qmatmul_list_create(void* ctx, uint32_t kind, uint64_t M, const SmithListItem* items, uint32_t count);
+int32_t smith_qmatmul_list_run(void* ctx, void* list);
+void smith_qmatmul_list_destroy(void* list);
+/* 1 if an item of this shape can be part of a list. */
+int32_t smith_qmatmul_list_supports(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
 /* Device-side waits in these kernels (on a shared-memory barrier, a peer's
  * flag) are bounded; one that gives up marks the launch's result invalid.
  * Returns 1 if that happened on this context's device since the last call

@@ -24,9 +24,22 @@ Q4_GROUP, Q4_BYTES = 32, 24
 Q8_GROUP, Q8_BYTES = 32, 34
 
 
+def reference_dir():
+    """Where a checkout of the reference lies: $SMITH_REFERENCE_DIR, else a directory named
+    `reference` beside this repository; None when there is none (then only a prebuilt
+    oracle/_ref is used)."""
+    cands = [os.environ.get("SMITH_REFERENCE_DIR"),
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "shaders", "matmul_q4.metal")):
+            return c
+    return None
+
+
 def build(quiet=True):
     """Compile the checkers with the recipe in oracle/Makefile."""
-    subprocess.run(["make", "-C", _HERE], check=True,
+    ref_dir = reference_dir()
+    subprocess.run(["make", "-C", _HERE] + ([f"REF={ref_dir}"] if ref_dir else []), check=True,
                    stdout=subprocess.DEVNULL if quiet else None)
 
 
@@ -63,6 +76,10 @@ def lib():
             f.restype = None
             f.argtypes = [p, p, p, i64, i64, i64, i64, i64, i64, C.c_int]
         _lib.oracle_max_threads.restype = C.c_int
+        _lib.oracle_rmsnorm.restype = None
+        _lib.oracle_rmsnorm.argtypes = [p, p, p, i64, i64, C.c_float]
+        _lib.oracle_swiglu.restype = None
+        _lib.oracle_swiglu.argtypes = [p, p, p, i64]
     return _lib
 
 
@@ -81,6 +98,11 @@ def ref():
             f.restype = None
             f.argtypes = [p, p, p, i64, i64, i64, i64, i64, i64, C.c_int]
         _ref.ref_max_threads.restype = C.c_int
+        if hasattr(_ref, "ref_rmsnorm"):
+            _ref.ref_rmsnorm.restype = None
+            _ref.ref_rmsnorm.argtypes = [p, p, p, i64, i64, C.c_float]
+            _ref.ref_swiglu.restype = None
+            _ref.ref_swiglu.argtypes = [p, p, p, i64]
     return _ref
 
 
@@ -154,6 +176,56 @@ def ref_matmul(a, packed, K, N, kind, groups=None, cols=None, threads=1):
     if r is None:
         raise RuntimeError("oracle/_ref/libsmith_ref.so has not been built")
     return _matmul(getattr(r, "ref_matmul_" + kind), a, packed, K, N, groups, cols, threads)
+
+
+def _rmsnorm(fn, x, gamma, eps):
+    x = _f32_2d(x)
+    gamma = np.ascontiguousarray(gamma, dtype=np.float32)
+    assert gamma.shape == (x.shape[1],)
+    out = np.zeros_like(x)
+    fn(_ptr(x), _ptr(gamma), _ptr(out), x.shape[0], x.shape[1], float(eps))
+    return out
+
+
+def rmsnorm(x, gamma, eps=1e-5):
+    """shaders/rmsnorm.metal:15-49 restated: x [rows, cols] * rsqrt(mean(x^2) + eps) * gamma."""
+    return _rmsnorm(lib().oracle_rmsnorm, x, gamma, eps)
+
+
+def ref_rmsnorm(x, gamma, eps=1e-5):
+    """Same call served by the reference's compiled shader source."""
+    return _rmsnorm(ref().ref_rmsnorm, x, gamma, eps)
+
+
+def _swiglu(fn, gate, up):
+    gate = np.ascontiguousarray(gate, dtype=np.float32)
+    up = np.ascontiguousarray(up, dtype=np.float32)
+    assert gate.shape == up.shape
+    out = np.zeros_like(gate)
+    fn(_ptr(gate), _ptr(up), _ptr(out), gate.size)
+    return out
+
+
+def swiglu(gate, up):
+    """shaders/swiglu.metal:12-22 restated: silu(gate) * up."""
+    return _swiglu(lib().oracle_swiglu, gate, up)
+
+
+def ref_swiglu(gate, up):
+    return _swiglu(ref().ref_swiglu, gate, up)
+
+
+def have_ref_glue():
+    r = ref()
+    return r is not None and hasattr(r, "ref_rmsnorm")
+
+
+def host_threads():
+    """Cores this process may run on (what OpenMP would use if nothing capped it)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def max_threads():

@@ -12,6 +12,8 @@
  *   oracle_from_float16  src/dtype.js:60-79
  *   oracle_matmul_q4     shaders/matmul_q4.metal:24-28,34-65
  *   oracle_matmul_q8     shaders/matmul_q8.metal:20-57
+ *   oracle_rmsnorm       shaders/rmsnorm.metal:15-49, src/ops/rmsnorm.js:19-38
+ *   oracle_swiglu        shaders/swiglu.metal:12-22
  *   oracle_quantize_q8   NO reference counterpart ("parity unpinned"): the
  *                        reference has no producer for the layout that
  *                        matmul_q8 consumes.  The rule frozen here is written
@@ -268,6 +270,41 @@ void oracle_matmul_q8(const float *A, const uint8_t *B, float *C, int64_t M, int
       }
       for (int64_t c = cb; c < ce; c++) C[row * N + c] = acc[c - cb];
     }
+  }
+}
+
+/* ---- rmsnorm_forward: shaders/rmsnorm.metal:15-49 ------------------------ */
+/* One threadgroup of tpg threads per row (tpg = the power of two >= min(cols, 256),
+ * at least 2: src/ops/rmsnorm.js:26).  Thread tid sums x[i]^2 over i = tid, tid + tpg, ...;
+ * the partials are added pairwise by the halving tree of the shader (stride tpg/2, tpg/4, ... 1);
+ * rms = 1/sqrt(sum / cols + eps); out[i] = x[i] * rms * gamma[i].  Every operation is rounded to
+ * f32, in the shader's order (the GPU's own rsqrt is an approximation; 1/sqrtf stands in for it). */
+void oracle_rmsnorm(const float *x, const float *gamma, float *out, int64_t rows, int64_t cols, float eps) {
+  int64_t lim = cols < 256 ? cols : 256;
+  if (lim < 2) lim = 2;
+  int64_t tpg = 1;
+  while (tpg < lim) tpg <<= 1;
+  for (int64_t r = 0; r < rows; r++) {
+    const float *xr = x + r * cols;
+    float part[256];
+    for (int64_t t = 0; t < tpg; t++) {
+      float ss = 0.0f;
+      for (int64_t i = t; i < cols; i += tpg) ss += xr[i] * xr[i];
+      part[t] = ss;
+    }
+    for (int64_t s = tpg / 2; s > 0; s >>= 1)
+      for (int64_t t = 0; t < s; t++) part[t] += part[t + s];
+    float rms = 1.0f / sqrtf(part[0] / (float)cols + eps);
+    for (int64_t i = 0; i < cols; i++) out[r * cols + i] = xr[i] * rms * gamma[i];
+  }
+}
+
+/* ---- swiglu_forward: shaders/swiglu.metal:12-22 -------------------------- */
+void oracle_swiglu(const float *gate, const float *up, float *out, int64_t n) {
+  for (int64_t i = 0; i < n; i++) {
+    float g = gate[i];
+    float silu = g / (1.0f + expf(-g));
+    out[i] = silu * up[i];
   }
 }
 

@@ -841,6 +841,108 @@ uint64_t smith_launch_count(void* p) {
   return c ? c->launches : 0;
 }
 
+// ---------------------------------------------------------------- a list of products as one launch
+namespace {
+struct ListHandle {
+  uint32_t magic = 0x534D4C53;  // "SMLS"
+  Context* ctx = nullptr;
+  ListProgram* prog = nullptr;
+  uint32_t count = 0;
+};
+
+// Device address of `bytes` bytes at `offset` inside a buffer's device side (nullptr + message on failure).
+const uint8_t* list_operand(void* handle, uint64_t offset, uint64_t bytes, uint32_t item, const char* what) {
+  Buffer* b = as_buf(handle);
+  if (!b) return nullptr;
+  if (!b->dev) {
+    fail("smith_qmatmul_list_create: item %u: %s has no device side", item, what);
+    return nullptr;
+  }
+  if (offset + bytes > b->bytes) {
+    fail("smith_qmatmul_list_create: item %u: %s needs %llu bytes at offset %llu of a %llu-byte buffer", item, what,
+         (unsigned long long)bytes, (unsigned long long)offset, (unsigned long long)b->bytes);
+    return nullptr;
+  }
+  return static_cast<const uint8_t*>(b->dev) + offset;
+}
+}  // namespace
+
+void* smith_qmatmul_list_create(void* p, uint32_t kind, uint64_t M, const SmithListItem* items, uint32_t count) {
+  Context* c = as_ctx(p);
+  if (!c) return nullptr;
+  if (!items || count == 0) {
+    fail("smith_qmatmul_list_create: empty list");
+    return nullptr;
+  }
+  if (kind != 4 && kind != 8) {
+    fail("kind must be 4 or 8, got %u", kind);
+    return nullptr;
+  }
+  if (c->capturing) {
+    fail("smith_qmatmul_list_create allocates device memory: create the list before graph capture");
+    return nullptr;
+  }
+  const uint64_t blk = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  std::vector<ListItemDesc> descs(count);
+  for (uint32_t i = 0; i < count; i++) {
+    const SmithListItem& it = items[i];
+    ListItemDesc& d = descs[i];
+    if (it.K == 0 || (it.K % 32) != 0) {
+      fail("smith_qmatmul_list_create: item %u: K = %llu is not a multiple of 32", i, (unsigned long long)it.K);
+      return nullptr;
+    }
+    const uint64_t wbytes = (it.K / 32) * it.N * blk;
+    d.N = (int64_t)it.N, d.K = (int64_t)it.K, d.eps = it.eps;
+    d.A = reinterpret_cast<const float*>(list_operand(it.a, it.a_offset, M * it.K * 4, i, "a"));
+    d.B = list_operand(it.b, it.b_offset, wbytes, i, "b");
+    d.C = reinterpret_cast<float*>(const_cast<uint8_t*>(list_operand(it.c, it.c_offset, M * it.N * 4, i, "c")));
+    if (!d.A || !d.B || !d.C) return nullptr;
+    d.B2 = nullptr, d.gamma = nullptr, d.residual = nullptr;
+    if (it.b2 && !(d.B2 = list_operand(it.b2, it.b2_offset, wbytes, i, "b2"))) return nullptr;
+    if (it.gamma && !(d.gamma = reinterpret_cast<const float*>(list_operand(it.gamma, 0, it.K * 4, i, "gamma")))) return nullptr;
+    if (it.residual && !(d.residual = reinterpret_cast<const float*>(
+                             list_operand(it.residual, it.residual_offset, M * it.N * 4, i, "residual"))))
+      return nullptr;
+  }
+  const char* why = "";
+  ListProgram* prog = qgemv_list_create((int)kind, (int64_t)M, descs.data(), (int)count, &why);
+  if (!prog) {
+    fail("smith_qmatmul_list_create: %s", why);
+    return nullptr;
+  }
+  c->held += list_device_bytes(prog);
+  ListHandle* h = new ListHandle();
+  h->ctx = c, h->prog = prog, h->count = count;
+  return h;
+}
+
+int32_t smith_qmatmul_list_run(void* p, void* list) {
+  Context* c = as_ctx(p);
+  ListHandle* h = static_cast<ListHandle*>(list);
+  if (!c) return 1;
+  if (!h || h->magic != 0x534D4C53 || h->ctx != c) return fail("smith_qmatmul_list_run: not a list of this context");
+  cudaError_t e = qgemv_list_launch(h->prog, c->stream);
+  return e == cudaSuccess ? 0 : fail("list launch failed: %s", cudaGetErrorString(e));
+}
+
+void smith_qmatmul_list_destroy(void* list) {
+  ListHandle* h = static_cast<ListHandle*>(list);
+  if (!h || h->magic != 0x534D4C53) return;
+  Context* c = h->ctx;
+  if (c && c->magic == kCtxMagic) {
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    c->held -= list_device_bytes(h->prog);
+  }
+  qgemv_list_destroy(h->prog);
+  h->magic = 0;
+  delete h;
+}
+
+int32_t smith_qmatmul_list_supports(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
+  return qgemv_list_supports((int)kind, (int64_t)M, (int64_t)N, (int64_t)K) ? 1 : 0;
+}
+
 // For callers that must not allocate device memory at the time of the call: code
 // running after its memory budget is fixed (a serving process that hands every
 // byte to its own arena at start-up), inside a region where cudaMalloc would

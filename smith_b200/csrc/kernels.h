@@ -82,6 +82,30 @@ cudaError_t launch_qgemv_multi(int kind, const float* A, int count, const uint8_
 // Grid size the GEMV uses for a shape (-1 if it does not take it).
 int qgemv_tiles(int kind, int64_t M, int64_t N, int64_t K);
 
+// qgemv_list.cu : a list of GEMV-shaped products (M <= 4) as one persistent launch, with the
+// decode step's pointwise glue folded in.  Raw device pointers; every item of a list has the same
+// kind and M.
+struct ListItemDesc {
+  const float* A;          // activations f32 [M, K]
+  const uint8_t* B;        // packed weights [K/32][N][block]
+  const uint8_t* B2;       // null, or the `up` matrix of a gate/up pair: C = silu(A x B) * (A x B2)
+  float* C;                // output f32 [M, N]
+  const float* gamma;      // null, or RMSNorm weights [K]: the product reads rmsnorm(A) * gamma
+  const float* residual;   // null, or f32 [M, N] added to the product (may be C)
+  int64_t N, K;
+  float eps;               // RMSNorm epsilon
+};
+struct ListProgram;
+bool qgemv_list_supports(int kind, int64_t M, int64_t N, int64_t K);
+// Plans the list for the current device and uploads it (allocates device memory).  nullptr with
+// *why set on failure.
+ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, int count, const char** why);
+cudaError_t qgemv_list_launch(const ListProgram* lp, cudaStream_t s);
+void qgemv_list_destroy(ListProgram* lp);
+size_t list_device_bytes(const ListProgram* lp);
+int list_grid(const ListProgram* lp);
+uint64_t qgemv_list_weight_bytes(const ListProgram* lp);
+
 // Same computation with the scratch in a fixed array inside the library image (no allocation).
 cudaError_t launch_qgemm_tc_static(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,
                                    int64_t K, int64_t groups, cudaStream_t s, const char** why);

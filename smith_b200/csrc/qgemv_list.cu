@@ -1,0 +1,734 @@
+// qgemv_list.cu -- a list of GEMV-shaped quantized matmuls (M <= 4) as ONE persistent launch.
+//
+// A decode step is a fixed sequence of such products (src/gguf_cache.js:121-171: per layer wq, wk,
+// wv, wo, gate, up, down, then the output projection).  Launched one by one, each pays a start-up
+// (barrier set-up, the first copies' trip to HBM and back) and a tail (the last stage's dot
+// products, the phase reduction, the CTAs leaving their SMs) during which HBM idles: at
+// 4096 x 14336 that is 2.7 of every 9.0 us.  Here one grid of one CTA per SM walks the whole list:
+//
+//  * Every CTA keeps ONE ring of shared-memory stages alive for the whole launch.  Its producer
+//    warp issues the bulk copies of item i + 1's first stages while the consumer warps still work
+//    on item i, so the stream of packed weights from HBM never drains between matrices.
+//  * Item i is cut into tiles of TN_i columns x all of K_i; tile t runs on CTA
+//    (first_cta_i + t) mod grid, where first_cta_i continues where item i - 1 stopped, so items
+//    whose tile count is not a multiple of the grid still load the SMs evenly.
+//  * The arithmetic is the GEMV kernel's (qgemv_common.cuh): activations in block fixed point as
+//    two int8 digits, dp4a against the codes, exact integer group sums, f32 scale-and-add.
+//  * Hazards between items are resolved on the device.  An item that reads what an earlier item
+//    writes (or writes what one reads or writes) waits -- bounded -- until that item's counter of
+//    outstanding output warps has reached zero.  Only the consumers wait: the producer keeps
+//    filling the ring with the dependent item's weights, which no item writes.
+//  * The pointwise glue of the step is folded in (src/gguf_cache.js:121,156-163):
+//      - RMSNorm on the way in (shaders/rmsnorm.metal:15-49): y = x * rsqrt(mean(x^2) + eps) * gamma
+//        is applied while the activations are turned into digits;
+//      - SwiGLU on the way out (shaders/swiglu.metal:12-22): an item with two packed matrices
+//        (gate, up) accumulates both products for its columns and stores silu(g) * u;
+//      - the residual add (A.add(x, projected)): C = residual + product.
+//
+// Counters: done[i] starts a launch at the number of warps that will store outputs of item i and
+// each such warp decrements it after its stores (fence, then atomic).  The last CTA to leave
+// restores all counters, also after a give-up, so the next launch starts clean.
+//
+// Every wait is bounded (pipeline.cuh); one that gives up raises the status word.
+#include <cuda.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "kernels.h"
+#include "pipeline.cuh"
+#include "qgemv_common.cuh"
+
+namespace smith {
+namespace {
+
+constexpr int kListMaxThreads = 448;   // consumer threads per CTA
+constexpr int kListMaxStages = 8;
+constexpr int kListHeader = 256;       // barriers + abort flag
+constexpr int kListSmem = 226 * 1024;     // dynamic part; the kernel's static shared memory takes up to 1 KB of the 227
+constexpr int kListMaxDeps = 4;
+constexpr int kListMaxTN = 112;        // 4 phases x 112 columns = 448 threads
+
+// What the kernel needs to know about one item: exactly 32 words.
+struct alignas(128) ItemHot {
+  const float* A;
+  const uint8_t* B0;
+  const uint8_t* B1;        // second packed matrix of a gate/up pair, else null
+  float* C;
+  const float* gamma;       // RMSNorm weights [K], or null
+  const float* residual;    // [M, N] added to the product, or null (may be C itself)
+  int N, K, G, TN;
+  int tiles, first_cta, phases, rpp;
+  int stage_rows, row_pitch, nst, use_tma;
+  int nB, a_id;             // a_id: items with equal a_id read the same activations in the same state
+  float eps;
+  int ndeps;
+  int dep[kListMaxDeps];    // earlier items that must be complete before this one touches its operands
+};
+static_assert(sizeof(ItemHot) == 128, "ItemHot is loaded as eight 16-byte words");
+
+struct ListParams {
+  const ItemHot* items;
+  const CUtensorMap* maps;  // [2 * nitems]
+  unsigned* done;           // [nitems] outstanding output warps per item
+  const unsigned* done_init;  // [nitems]
+  unsigned* ticket;         // CTAs that have left
+  int* status;
+  int nitems;
+  int M;
+  int nwarps;               // consumer warps per CTA
+  int slots, slot_bytes;
+  int xdig_off, xsc_off, rms_off, red_off, red_half, ring_off;  // byte offsets in dynamic shared memory
+};
+
+// Field by field, so that the item lives in registers (a copy through its address would put it in
+// local memory).
+__device__ __forceinline__ ItemHot load_item(const ItemHot* p) {
+  const uint4* s = reinterpret_cast<const uint4*>(p);
+  uint4 w[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) w[i] = __ldg(s + i);
+  auto ptr = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
+  ItemHot it;
+  it.A = reinterpret_cast<const float*>(ptr(w[0].x, w[0].y));
+  it.B0 = reinterpret_cast<const uint8_t*>(ptr(w[0].z, w[0].w));
+  it.B1 = reinterpret_cast<const uint8_t*>(ptr(w[1].x, w[1].y));
+  it.C = reinterpret_cast<float*>(ptr(w[1].z, w[1].w));
+  it.gamma = reinterpret_cast<const float*>(ptr(w[2].x, w[2].y));
+  it.residual = reinterpret_cast<const float*>(ptr(w[2].z, w[2].w));
+  it.N = (int)w[3].x, it.K = (int)w[3].y, it.G = (int)w[3].z, it.TN = (int)w[3].w;
+  it.tiles = (int)w[4].x, it.first_cta = (int)w[4].y, it.phases = (int)w[4].z, it.rpp = (int)w[4].w;
+  it.stage_rows = (int)w[5].x, it.row_pitch = (int)w[5].y, it.nst = (int)w[5].z, it.use_tma = (int)w[5].w;
+  it.nB = (int)w[6].x, it.a_id = (int)w[6].y, it.eps = __uint_as_float(w[6].z), it.ndeps = (int)w[6].w;
+  it.dep[0] = (int)w[7].x, it.dep[1] = (int)w[7].y, it.dep[2] = (int)w[7].z, it.dep[3] = (int)w[7].w;
+  return it;
+}
+
+// Bounded wait until item `dep` is complete everywhere (its counter of outstanding warps is zero).
+__device__ __forceinline__ bool wait_item(const unsigned* counter, const int* status) {
+  const long long t0 = clock64();
+  for (unsigned spin = 0;; spin++) {
+    unsigned seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (seen == 0u) return true;
+    if ((spin & 63u) == 63u) {
+      if (*reinterpret_cast<const volatile int*>(status)) return false;   // someone else gave up: do not sit out the limit
+      if (clock64() - t0 > kWaitLimitCycles) return false;
+    }
+  }
+}
+
+// Barrier over the consumer threads that also tells every one of them whether any has given up, so
+// that they all leave together and none is left waiting at a later barrier.
+__device__ __forceinline__ bool consumers_sync_any(int nct, bool mine) {
+  uint32_t any;
+  asm volatile(
+      "{\n.reg .pred p, q;\n"
+      "setp.ne.u32 q, %2, 0;\n"
+      "bar.red.or.pred p, 1, %1, q;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(any)
+      : "r"(nct), "r"(mine ? 1u : 0u)
+      : "memory");
+  return any != 0;
+}
+
+template <int KIND, int MR, int RPP>
+__device__ __forceinline__ void consume_stage(const uint8_t* stage, int st, int stage_rows, int G, int phases,
+                                              int phase, int col, int row_pitch, const uint4* xdig,
+                                              const float2* xsc, float (&acc)[MR]) {
+  constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
+  const int g0 = st * stage_rows + phase;
+  if (st * stage_rows + stage_rows <= G) {
+#pragma unroll
+    for (int rr = 0; rr < RPP; rr++) {
+      const uint32_t off = (uint32_t)(phase + rr * phases) * row_pitch + (uint32_t)col * BB;
+      const int g = g0 + rr * phases;
+      block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
+    }
+  } else {
+    for (int rr = 0; rr < RPP; rr++) {
+      const int g = g0 + rr * phases;
+      if (g < G) {
+        const uint32_t off = (uint32_t)(phase + rr * phases) * row_pitch + (uint32_t)col * BB;
+        block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
+      }
+    }
+  }
+}
+
+template <int KIND, int MR>
+__global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(const ListParams p) {
+  constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kListMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kListMaxStages * 8);
+  uint4* xdig = reinterpret_cast<uint4*>(smem + p.xdig_off);     // [MR][G][4] uint4
+  float2* xsc = reinterpret_cast<float2*>(smem + p.xsc_off);     // [MR][G]
+  float* rms_part = reinterpret_cast<float*>(smem + p.rms_off);  // [MR][nwarps]
+  uint8_t* ring = smem + p.ring_off;
+
+  const int tid = threadIdx.x;
+  const int nwarps = p.nwarps;
+  const int ncta = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int nct = nwarps * 32;                    // consumer threads
+
+  if (tid == 0) {
+    for (int s = 0; s < p.slots; s++) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), nwarps);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (tid >= nct) {
+    // ------------------------------------------------------------ producer warp
+    // Walks items, tiles and stages in the consumers' order, one ring slot per stage, and never
+    // waits for anything but a free slot.
+    const int lane = tid & 31;
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    bool live = true;
+    int slot = 0;
+    uint32_t par = 0;                               // parity of this pass over the ring
+    int issued = 0;                                 // stages issued so far, saturating at the ring depth
+    ItemHot nxt = load_item(p.items);
+    for (int i = 0; i < p.nitems && live; i++) {
+      const ItemHot it = nxt;
+      if (i + 1 < p.nitems) nxt = load_item(p.items + i + 1);
+      int t = cta - it.first_cta;
+      if (t < 0) t += ncta;
+      for (; t < it.tiles && live; t += ncta) {
+        const int col0 = t * it.TN;
+        const int tn = min(it.TN, it.N - col0);
+        const uint32_t row_bytes = (uint32_t)tn * BB;
+        for (int bi = 0; bi < it.nB && live; bi++) {
+          const uint8_t* __restrict__ Bm = bi ? it.B1 : it.B0;
+          const CUtensorMap* map = p.maps + 2 * i + bi;
+          for (int st = 0; st < it.nst; st++) {
+            if (issued >= p.slots) {
+              int okw = 1;
+              if (lane == 0) okw = mbar_wait(smem_u32(&empty[slot]), par ^ 1u, abort_flag, p.status);
+              live = __shfl_sync(0xffffffffu, okw, 0) != 0;
+              if (!live) break;
+            } else {
+              issued++;
+            }
+            const int rows = min(it.stage_rows, it.G - st * it.stage_rows);
+            const uint32_t bar = smem_u32(&full[slot]);
+            const uint32_t dst = smem_u32(ring + (size_t)slot * p.slot_bytes);
+            if (it.use_tma) {
+              // the box is always stage_rows x TN blocks: what lies beyond N or the last group-row is zero-filled
+              if (lane == 0) {
+                mbar_expect_tx(bar, (uint32_t)it.stage_rows * (uint32_t)it.row_pitch);
+                tma_box_2d(dst, map, (col0 * BB) >> 3, st * it.stage_rows, bar, policy);
+              }
+            } else {
+              if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
+              __syncwarp();
+              const uint8_t* src = Bm + ((size_t)st * it.stage_rows * it.N + col0) * BB;
+              for (int rr = lane; rr < rows; rr += 32)
+                bulk_load(dst + rr * it.row_pitch, src + (size_t)rr * it.N * BB, row_bytes, bar, policy);
+            }
+            slot = (slot + 1 == p.slots) ? 0 : slot + 1;
+            par ^= (slot == 0);
+          }
+        }
+      }
+    }
+    // consumers observe every full barrier they were promised, so all copies have landed before the CTA ends
+  } else {
+    // -------------------------------------------------------------- consumers
+    // `ok` is a thread's own view (a wait of its warp gave up); `quit` is what all consumers learn
+    // together at a barrier, so that every barrier below is reached by all of them or by none.
+    const int lane = tid & 31, warp = tid >> 5;
+    bool ok = true, quit = false;
+    int slot = 0;
+    uint32_t par = 0;
+    int cur_a = -1;                                 // a_id whose digits are in shared memory
+    int red_buf = 0;
+    ItemHot nxt = load_item(p.items);
+    for (int i = 0; i < p.nitems && !quit; i++) {
+      const ItemHot it = nxt;
+      if (i + 1 < p.nitems) nxt = load_item(p.items + i + 1);
+      int t = cta - it.first_cta;
+      if (t < 0) t += ncta;
+      if (t >= it.tiles) continue;                  // no tile of this item runs here
+      // ---- hazards: every earlier item this one depends on must be complete everywhere
+      if (it.ndeps > 0 && ok) {
+        int okw = 1;
+        if (lane == 0) {
+#pragma unroll
+          for (int d = 0; d < kListMaxDeps; d++)
+            if (d < it.ndeps && okw) okw = wait_item(p.done + it.dep[d], p.status) ? 1 : 0;
+        }
+        __syncwarp();
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) {
+          *abort_flag = 1;
+          atomicExch(p.status, 1);
+          ok = false;
+        }
+      }
+      // ---- activations -> digit words (skipped when the previous item left the same ones)
+      if (it.a_id != cur_a) {
+        cur_a = it.a_id;
+        float inv[MR];
+#pragma unroll
+        for (int m = 0; m < MR; m++) inv[m] = 1.f;
+        if (it.gamma) {
+          // RMSNorm (shaders/rmsnorm.metal:33-43): rms = 1 / sqrt(mean(x^2) + eps), summed in a fixed
+          // order so that every CTA normalises with the same bits
+          float ss[MR];
+#pragma unroll
+          for (int m = 0; m < MR; m++) ss[m] = 0.f;
+          for (int q = tid; q < it.K / 4; q += nct) {
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(it.A + (size_t)m * it.K) + q);
+              ss[m] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < MR; m++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+            if (lane == 0) rms_part[m * nwarps + warp] = ss[m];
+          }
+          quit = consumers_sync_any(nct, !ok);
+          if (quit) break;
+#pragma unroll
+          for (int m = 0; m < MR; m++) {
+            float tot = 0.f;
+            for (int w = 0; w < nwarps; w++) tot += rms_part[m * nwarps + w];
+            inv[m] = 1.0f / sqrtf(tot / (float)it.K + it.eps);
+          }
+        }
+        // (row, group) pairs are laid out as [MR][G], which is also the order of A's 32-element chunks
+        const int total = (MR * it.G * 8 + 31) & ~31, last = MR * it.G - 1;
+        for (int i0 = tid; i0 < total; i0 += 4 * nct) {
+          float4 tv[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const int q = i0 + u * nct;
+            if (q < total)       // clamp keeps whole warps in the shuffles; duplicates rewrite equal bytes
+              tv[u] = __ldcg(reinterpret_cast<const float4*>(it.A + (size_t)min(q >> 3, last) * 32) + (q & 7));
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const int q = i0 + u * nct;             // warp-uniform: total and nct are multiples of 32
+            if (q < total) {
+              const int grp = min(q >> 3, last);
+              float4 v = tv[u];
+              if (it.gamma) {
+                const int row = grp / it.G, g = grp - row * it.G;
+                const float4 gm = __ldg(reinterpret_cast<const float4*>(it.gamma + (size_t)g * 32) + (q & 7));
+                float r = inv[0];
+#pragma unroll
+                for (int m = 1; m < MR; m++) r = (row == m) ? inv[m] : r;
+                v = make_float4(v.x * r * gm.x, v.y * r * gm.y, v.z * r * gm.z, v.w * r * gm.w);
+              }
+              quantise_quarter<KIND>(v, q & 7, reinterpret_cast<uint8_t*>(xdig + (size_t)grp * 4), xsc + grp);
+            }
+          }
+        }
+        quit = consumers_sync_any(nct, !ok);
+        if (quit) break;
+      }
+
+      for (; t < it.tiles && !quit; t += ncta) {
+        const int col0 = t * it.TN;
+        const int tn = min(it.TN, it.N - col0);
+        const bool active = tid < tn * it.phases;
+        const int col = active ? (tid % tn) : 0;
+        const int phase = active ? (tid / tn) : 0;
+        float acc[MR], gate[MR];
+#pragma unroll
+        for (int m = 0; m < MR; m++) acc[m] = 0.f, gate[m] = 0.f;
+        for (int bi = 0; bi < it.nB && ok; bi++) {
+          if (bi == 1) {
+#pragma unroll
+            for (int m = 0; m < MR; m++) gate[m] = acc[m], acc[m] = 0.f;
+          }
+          for (int st = 0; st < it.nst && ok; st++) {
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full[slot]), par, abort_flag, p.status));   // warp-uniform
+            if (ok && active) {
+              const uint8_t* stage = ring + (size_t)slot * p.slot_bytes;
+              if (it.rpp == 4)
+                consume_stage<KIND, MR, 4>(stage, st, it.stage_rows, it.G, it.phases, phase, col, it.row_pitch, xdig, xsc, acc);
+              else
+                consume_stage<KIND, MR, 3>(stage, st, it.stage_rows, it.G, it.phases, phase, col, it.row_pitch, xdig, xsc, acc);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
+            slot = (slot + 1 == p.slots) ? 0 : slot + 1;
+            par ^= (slot == 0);
+          }
+        }
+        // ---- sum the phases in fixed order; the scratch alternates between tiles, so one barrier per tile
+        float* red = reinterpret_cast<float*>(smem + p.red_off + red_buf * p.red_half);   // [nB][phases][MR][TN]
+        red_buf ^= 1;
+        const int plane = it.phases * MR * it.TN;
+        if (active) {
+#pragma unroll
+          for (int m = 0; m < MR; m++) {
+            red[(phase * MR + m) * it.TN + col] = acc[m];
+            if (it.nB == 2) red[plane + (phase * MR + m) * it.TN + col] = gate[m];
+          }
+        }
+        quit = consumers_sync_any(nct, !ok);
+        if (quit) break;
+        if (tid < p.M * tn) {
+          const int m = tid / tn, c = tid - m * tn;
+          float v = 0.f;
+          for (int ph = 0; ph < it.phases; ph++) v += red[(ph * MR + m) * it.TN + c];
+          if (it.nB == 2) {
+            // SwiGLU (shaders/swiglu.metal:18-20): the first matrix is the gate, the second is up
+            float g = 0.f;
+            for (int ph = 0; ph < it.phases; ph++) g += red[plane + (ph * MR + m) * it.TN + c];
+            v = (g / (1.0f + expf(-g))) * v;
+          }
+          const size_t at = (size_t)m * it.N + col0 + c;
+          if (it.residual) v = __ldcg(it.residual + at) + v;
+          it.C[at] = v;
+        }
+        __syncwarp();
+        if (lane == 0 && warp * 32 < p.M * tn) {
+          __threadfence();                            // this warp's stores before the count
+          atomicSub(p.done + i, 1u);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------ leave: the last CTA restores the counters
+  __syncthreads();
+  __shared__ unsigned last_flag;
+  if (tid == 0) {
+    __threadfence();
+    last_flag = (atomicAdd(p.ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (last_flag) {
+    __threadfence();
+    for (int j = tid; j < p.nitems; j += blockDim.x) p.done[j] = p.done_init[j];
+    if (tid == 0) *p.ticket = 0u;
+  }
+}
+
+// ---------------------------------------------------------------------------------------- host side
+
+struct Tuning {
+  int tma;        // -1 by rule, 0 never, 1 wherever a box fits
+  int rpp;        // group-rows per phase and stage
+  int max_tn;
+};
+
+Tuning tuning() {
+  Tuning t{-1, 4, kListMaxTN};
+  if (const char* v = getenv("SMITH_LIST_TMA")) t.tma = atoi(v);
+  if (const char* v = getenv("SMITH_LIST_RPP")) t.rpp = (atoi(v) == 3) ? 3 : 4;
+  if (const char* v = getenv("SMITH_LIST_MAX_TN")) t.max_tn = max(8, min(kListMaxTN, atoi(v)));
+  return t;
+}
+
+bool overlap(const void* a, size_t an, const void* b, size_t bn) {
+  if (!a || !b || !an || !bn) return false;
+  const uintptr_t a0 = (uintptr_t)a, b0 = (uintptr_t)b;
+  return a0 < b0 + bn && b0 < a0 + an;
+}
+
+int list_fail(const char** why, const char* fmt, ...) {
+  static thread_local char buf[256];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (why) *why = buf;
+  return 1;
+}
+
+// Tiling of one item for a grid of `ncta` CTAs.
+void plan_item(int kind, int M, const ListItemDesc& d, int ncta, int rpp, const Tuning& tu, ItemHot& h) {
+  const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  const int64_t q = (kind == 4) ? 2 : 8;          // a tile's group-row span starts and ends on 16 bytes
+  h.N = (int)d.N, h.K = (int)d.K, h.G = (int)(d.K / 32);
+  int TN = 0;
+  for (int64_t waves = 1;; waves++) {
+    TN = (int)(q * ((d.N + q * ncta * waves - 1) / (q * ncta * waves)));
+    if (TN <= tu.max_tn) break;
+  }
+  h.TN = TN;
+  h.tiles = (int)((d.N + TN - 1) / TN);
+  int phases = (kListMaxThreads / TN) & ~3;
+  if (phases < 4) phases = 4;
+  while (phases > 4 && phases * rpp > h.G * 2) phases -= 4;   // short K: do not over-split
+  h.phases = phases;
+  h.rpp = rpp;
+  h.stage_rows = phases * rpp;
+  h.row_pitch = TN * BB;
+  h.nst = (h.G + h.stage_rows - 1) / h.stage_rows;
+  // One 2-D box per stage instead of one bulk copy per group-row pays where the row segments are
+  // short and many (a box side holds at most 256 elements of 8 bytes).
+  const bool fits = h.row_pitch <= 2048 && h.stage_rows <= 256 && (h.row_pitch % 16) == 0;
+  h.use_tma = fits && (tu.tma == 1 || (tu.tma == -1 && h.row_pitch <= 1408 && h.G >= 192)) ? 1 : 0;
+  h.nB = d.B2 ? 2 : 1;
+  (void)M;
+}
+
+}  // namespace
+
+struct ListProgram {
+  int kind = 0, M = 0, nitems = 0, ncta = 0, device = 0;
+  size_t smem = 0;
+  int threads = 0;
+  ListParams p{};
+  void* dev_block = nullptr;    // one allocation: items, maps, counters
+  size_t dev_bytes = 0;
+  uint64_t weight_bytes = 0;
+};
+
+size_t list_device_bytes(const ListProgram* lp) { return lp ? lp->dev_bytes : 0; }
+int list_grid(const ListProgram* lp) { return lp ? lp->ncta : 0; }
+
+namespace {
+
+template <int KIND, int MR>
+cudaError_t launch_list_as(const ListProgram* lp, cudaStream_t s) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    e = cudaFuncSetAttribute(qgemv_list_kernel<KIND, MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kListSmem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)lp->ncta);
+  cfg.blockDim = dim3((unsigned)lp->threads);
+  cfg.dynamicSmemBytes = lp->smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;   // the CTAs wait on one another: all of them must be resident
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, qgemv_list_kernel<KIND, MR>, lp->p);
+  count_launch();
+  return e;
+}
+
+}  // namespace
+
+bool qgemv_list_supports(int kind, int64_t M, int64_t N, int64_t K) {
+  if (kind != 4 && kind != 8) return false;
+  if (M < 1 || M > 4) return false;
+  if (N < 8 || (N % 8) != 0) return false;
+  if (K < 32 || (K % 32) != 0 || K > (1 << 22) || N > (1 << 30)) return false;
+  return (size_t)M * (K / 32) * 72 <= 96 * 1024;   // the activations' digit form must leave room for the ring
+}
+
+ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, int count, const char** why) {
+  if (why) *why = "";
+  if (count < 1 || count > 65536) {
+    list_fail(why, "a list holds 1 to 65536 items, got %d", count);
+    return nullptr;
+  }
+  if (kind != 4 && kind != 8) {
+    list_fail(why, "kind must be 4 or 8, got %d", kind);
+    return nullptr;
+  }
+  int dev = 0, sms = 0, coop = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess || sms < 1 || !coop) {
+    cudaGetLastError();
+    list_fail(why, "no device with cooperative launch");
+    return nullptr;
+  }
+  const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
+  const Tuning tu = tuning();
+  for (int i = 0; i < count; i++) {
+    const ListItemDesc& d = items[i];
+    if (!qgemv_list_supports(kind, M, d.N, d.K)) {
+      list_fail(why, "item %d: M=%lld N=%lld K=%lld is not a shape the list kernel takes (M <= 4, N %% 8 == 0, K %% 32 == 0)", i,
+                (long long)M, (long long)d.N, (long long)d.K);
+      return nullptr;
+    }
+    if (!d.A || !d.B || !d.C) {
+      list_fail(why, "item %d: null operand", i);
+      return nullptr;
+    }
+    if (((uintptr_t)d.A & 15) || ((uintptr_t)d.B & 15) || ((uintptr_t)d.B2 & 15) || ((uintptr_t)d.gamma & 15)) {
+      list_fail(why, "item %d: activations, weights and norm weights must be 16-byte aligned", i);
+      return nullptr;
+    }
+    if (overlap(d.A, (size_t)M * d.K * 4, d.C, (size_t)M * d.N * 4)) {
+      list_fail(why, "item %d: output overlaps its own activations", i);
+      return nullptr;
+    }
+  }
+  ListProgram* lp = new ListProgram();
+  lp->kind = kind, lp->M = (int)M, lp->nitems = count, lp->ncta = sms, lp->device = dev;
+  std::vector<ItemHot> hot(count);
+  int rpp = tu.rpp;
+  int slots = 0, slot_bytes = 0, nthreads = 0, ring_off = 0, xdig_off = 0, xsc_off = 0, rms_off = 0, red_off = 0, red_half = 0;
+  for (int attempt = 0; attempt < 2; attempt++, rpp = 3) {
+    int gmax = 0, red_max = 0;
+    slot_bytes = 0, nthreads = 0;
+    for (int i = 0; i < count; i++) {
+      ItemHot& h = hot[i];
+      memset(&h, 0, sizeof h);
+      plan_item(kind, (int)M, items[i], sms, rpp, tu, h);
+      gmax = max(gmax, h.G);
+      slot_bytes = max(slot_bytes, ((h.stage_rows * h.row_pitch + 127) / 128) * 128);
+      nthreads = max(nthreads, h.TN * h.phases);
+      red_max = max(red_max, h.phases * (int)M * h.TN * 4 * h.nB);
+    }
+    xdig_off = kListHeader;
+    xsc_off = xdig_off + (int)M * gmax * 64;
+    rms_off = xsc_off + (int)M * gmax * 8;
+    red_off = rms_off + 4 * 16 * 4;
+    red_half = (red_max + 15) & ~15;
+    ring_off = ((red_off + 2 * red_half + 1023) / 1024) * 1024;
+    slots = (kListSmem - 64 - ring_off) / slot_bytes;   // 64: the Q8 dot reads whole words around a block
+    if (slots > kListMaxStages) slots = kListMaxStages;
+    if (slots >= 4 || rpp == 3) break;
+  }
+  if (slots < 2 || nthreads > kListMaxThreads) {
+    list_fail(why, "the list does not fit shared memory (%d ring slots of %d bytes, %d threads)", slots, slot_bytes, nthreads);
+    delete lp;
+    return nullptr;
+  }
+  // ---- operands, activation versions, rotation of the tiles over the grid
+  int next_cta = 0, a_id = 0;
+  for (int i = 0; i < count; i++) {
+    const ListItemDesc& d = items[i];
+    ItemHot& h = hot[i];
+    h.A = d.A, h.B0 = d.B, h.B1 = d.B2, h.C = d.C, h.gamma = d.gamma, h.residual = d.residual, h.eps = d.eps;
+    h.first_cta = next_cta;
+    next_cta = (next_cta + h.tiles) % sms;
+    bool same = i > 0 && items[i - 1].A == d.A && items[i - 1].K == d.K && items[i - 1].gamma == d.gamma &&
+                items[i - 1].eps == d.eps &&
+                !overlap(items[i - 1].C, (size_t)M * items[i - 1].N * 4, d.A, (size_t)M * d.K * 4);
+    if (!same) a_id++;
+    h.a_id = a_id;
+    lp->weight_bytes += (uint64_t)h.G * d.N * BB * h.nB;
+  }
+  // ---- hazards.  closure[i] = every item known to be complete once item i is.
+  const int words = (count + 63) / 64;
+  std::vector<uint64_t> closure((size_t)count * words, 0);
+  auto bit = [&](int i, int j) -> bool { return (closure[(size_t)i * words + j / 64] >> (j % 64)) & 1; };
+  for (int i = 0; i < count; i++) {
+    const ListItemDesc& d = items[i];
+    const size_t an = (size_t)M * d.K * 4, cn = (size_t)M * d.N * 4;
+    ItemHot& h = hot[i];
+    uint64_t* mine = &closure[(size_t)i * words];
+    for (int j = i - 1; j >= 0; j--) {
+      if (bit(i, j)) continue;                     // already implied by a dependency taken
+      const ListItemDesc& e = items[j];
+      const size_t ean = (size_t)M * e.K * 4, ecn = (size_t)M * e.N * 4;
+      const bool raw = overlap(e.C, ecn, d.A, an) || overlap(e.C, ecn, d.residual, cn);
+      const bool war = overlap(d.C, cn, e.A, ean) || overlap(d.C, cn, e.residual, ecn);
+      const bool waw = overlap(d.C, cn, e.C, ecn);
+      if (!(raw || war || waw)) continue;
+      if (h.ndeps == kListMaxDeps) {
+        list_fail(why, "item %d conflicts with more than %d earlier items that do not imply one another", i, kListMaxDeps);
+        delete lp;
+        return nullptr;
+      }
+      h.dep[h.ndeps++] = j;
+      mine[j / 64] |= 1ull << (j % 64);
+      const uint64_t* theirs = &closure[(size_t)j * words];
+      for (int w = 0; w < words; w++) mine[w] |= theirs[w];
+    }
+  }
+  // ---- device block: items | maps | done_init | done | ticket
+  const size_t items_bytes = (size_t)count * sizeof(ItemHot);
+  const size_t maps_bytes = (size_t)count * 2 * sizeof(CUtensorMap);
+  const size_t cnt_bytes = (((size_t)count * 4 + 127) / 128) * 128;
+  lp->dev_bytes = items_bytes + maps_bytes + 2 * cnt_bytes + 128;
+  std::vector<uint8_t> host(lp->dev_bytes, 0);
+  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(host.data() + items_bytes);
+  unsigned* init = reinterpret_cast<unsigned*>(host.data() + items_bytes + maps_bytes);
+  unsigned* done = reinterpret_cast<unsigned*>(host.data() + items_bytes + maps_bytes + cnt_bytes);
+  EncodeTiledFn enc = encode_fn();
+  for (int i = 0; i < count; i++) {
+    ItemHot& h = hot[i];
+    if (h.use_tma) {
+      // each packed matrix as [G][N * block bytes / 8] 64-bit words, box = one stage of one tile
+      const cuuint64_t dims[2] = {(cuuint64_t)h.N * BB / 8, (cuuint64_t)h.G};
+      const cuuint64_t strides[1] = {(cuuint64_t)h.N * BB};
+      const cuuint32_t box[2] = {(cuuint32_t)h.row_pitch / 8, (cuuint32_t)h.stage_rows};
+      const cuuint32_t estr[2] = {1, 1};
+      bool good = enc != nullptr;
+      for (int b = 0; b < h.nB && good; b++)
+        good = enc(&maps[2 * i + b], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(b ? h.B1 : h.B0), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+      if (!good) h.use_tma = 0;                   // plain bulk copies
+    }
+    unsigned warps = 0;
+    for (int t = 0; t < h.tiles; t++) warps += (unsigned)(((int)M * min(h.TN, h.N - t * h.TN) + 31) / 32);
+    init[i] = done[i] = warps;
+  }
+  memcpy(host.data(), hot.data(), items_bytes);
+  if (cudaMalloc(&lp->dev_block, lp->dev_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    list_fail(why, "device allocation of %zu bytes for the list failed", lp->dev_bytes);
+    delete lp;
+    return nullptr;
+  }
+  if (cudaMemcpy(lp->dev_block, host.data(), lp->dev_bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(lp->dev_block);
+    list_fail(why, "upload of the list failed");
+    delete lp;
+    return nullptr;
+  }
+  uint8_t* base = static_cast<uint8_t*>(lp->dev_block);
+  ListParams& p = lp->p;
+  p.items = reinterpret_cast<const ItemHot*>(base);
+  p.maps = reinterpret_cast<const CUtensorMap*>(base + items_bytes);
+  p.done_init = reinterpret_cast<const unsigned*>(base + items_bytes + maps_bytes);
+  p.done = reinterpret_cast<unsigned*>(base + items_bytes + maps_bytes + cnt_bytes);
+  p.ticket = reinterpret_cast<unsigned*>(base + items_bytes + maps_bytes + 2 * cnt_bytes);
+  p.nitems = count, p.M = (int)M;
+  p.nwarps = (nthreads + 31) / 32;
+  p.slots = slots, p.slot_bytes = slot_bytes;
+  p.xdig_off = xdig_off, p.xsc_off = xsc_off, p.rms_off = rms_off, p.red_off = red_off, p.red_half = red_half;
+  p.ring_off = ring_off;
+  lp->threads = p.nwarps * 32 + 32;
+  lp->smem = (size_t)ring_off + (size_t)slots * slot_bytes + 64;
+  return lp;
+}
+
+cudaError_t qgemv_list_launch(const ListProgram* lp, cudaStream_t s) {
+  if (!lp) return cudaErrorInvalidValue;
+  ListProgram* m = const_cast<ListProgram*>(lp);
+  m->p.status = kernel_status_ptr();
+  if (!m->p.status) return cudaErrorUnknown;
+#define SMITH_LIST_CASE(KD, MRV) \
+  if (lp->kind == KD && lp->M == MRV) return launch_list_as<KD, MRV>(lp, s);
+  SMITH_LIST_CASE(4, 1) SMITH_LIST_CASE(4, 2) SMITH_LIST_CASE(4, 3) SMITH_LIST_CASE(4, 4)
+  SMITH_LIST_CASE(8, 1) SMITH_LIST_CASE(8, 2) SMITH_LIST_CASE(8, 3) SMITH_LIST_CASE(8, 4)
+#undef SMITH_LIST_CASE
+  return cudaErrorInvalidValue;
+}
+
+void qgemv_list_destroy(ListProgram* lp) {
+  if (!lp) return;
+  if (lp->dev_block) cudaFree(lp->dev_block);
+  delete lp;
+}
+
+uint64_t qgemv_list_weight_bytes(const ListProgram* lp) { return lp ? lp->weight_bytes : 0; }
+
+}  // namespace smith

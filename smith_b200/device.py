@@ -36,6 +36,13 @@ class SmithTiming(C.Structure):
     _fields_ = [("gpu_start", C.c_double), ("gpu_end", C.c_double), ("gpu_ms", C.c_double)]
 
 
+class SmithListItem(C.Structure):
+    """include/smith_cuda_bridge.h: one product of a list (smith_qmatmul_list_create)."""
+    _fields_ = [("a", _p), ("a_offset", _u64), ("b", _p), ("b_offset", _u64), ("b2", _p), ("b2_offset", _u64),
+                ("c", _p), ("c_offset", _u64), ("gamma", _p), ("residual", _p), ("residual_offset", _u64),
+                ("N", _u64), ("K", _u64), ("eps", C.c_float), ("reserved", _u32)]
+
+
 # name -> (restype, argtypes).  Part 1 is the table of src/device.js:10-50.
 SYMBOLS = {
     "smith_init": (_p, []),
@@ -84,6 +91,10 @@ SYMBOLS = {
     "smith_q8_pack": (_i32, [_p, _p, _p, _u64, _u64]),
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
+    "smith_qmatmul_list_create": (_p, [_p, _u32, _u64, C.POINTER(SmithListItem), _u32]),
+    "smith_qmatmul_list_run": (_i32, [_p, _p]),
+    "smith_qmatmul_list_destroy": (None, [_p]),
+    "smith_qmatmul_list_supports": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_qmatmul_static": (_i32, [_u32, _p, _p, _p, _u64, _u64, _u64, _u64, _p]),
     "smith_ipc_export": (_i32, [_p, _p]),
     "smith_ipc_import": (_p, [_p, _p, _u64]),
@@ -433,6 +444,34 @@ def qmatmulMulti(kind, aBuffer, bBuffers, cBuffers, Ns, M, K, groups):
     n = len(bBuffers)
     _check(lib.smith_qmatmul_multi(ctx(), kind, aBuffer, n, (_p * n)(*bBuffers), (_p * n)(*cBuffers),
                                    (_u64 * n)(*[int(x) for x in Ns]), M, K, groups), "qmatmul_multi")
+
+
+def listItem(a, b, c, N, K, b2=None, gamma=None, residual=None, eps=1e-5, aOffset=0, bOffset=0, b2Offset=0,
+             cOffset=0, residualOffset=0):
+    """One product of a list: c = [residual +] (b2 ? silu(x b) * (x b2) : x b), x = gamma ? rmsnorm(a) * gamma : a."""
+    return SmithListItem(a, aOffset, b, bOffset, b2, b2Offset, c, cOffset, gamma, residual, residualOffset, N, K,
+                         eps, 0)
+
+
+def qmatmulListCreate(kind, M, items):
+    """A list of GEMV-shaped products that runs as one persistent launch (see the header)."""
+    arr = (SmithListItem * len(items))(*items)
+    h = lib.smith_qmatmul_list_create(ctx(), kind, M, arr, len(items))
+    if not h:
+        _raise("qmatmul_list_create")
+    return h
+
+
+def qmatmulListRun(handle):
+    _check(lib.smith_qmatmul_list_run(ctx(), handle), "qmatmul_list_run")
+
+
+def qmatmulListDestroy(handle):
+    lib.smith_qmatmul_list_destroy(handle)
+
+
+def qmatmulListSupports(kind, M, N, K):
+    return bool(lib.smith_qmatmul_list_supports(kind, M, N, K))
 
 
 def qmatmulAllReduce(kind, aBuffer, bBuffer, outBuffer, M, N, kLocal, groupsLocal, world, rank, partialBuffers,
