@@ -25,9 +25,12 @@
 //        (gate, up) accumulates both products for its columns and stores silu(g) * u;
 //      - the residual add (A.add(x, projected)): C = residual + product.
 //
-// Counters: done[i] starts a launch at the number of warps that will store outputs of item i and
-// each such warp decrements it after its stores (fence, then atomic).  The last CTA to leave
-// restores all counters, also after a give-up, so the next launch starts clean.
+// Counters: done[i] starts a launch at the number of tiles of item i and drops by one per finished
+// tile.  The fence that must separate a tile's stores from that count, and the atomic itself,
+// cost the consumer warps a microsecond per tile when they issue them (measured: 8.2 -> 6.8 us per
+// 4096 x 14336 matrix without them), so a warp of its own does it: the consumers hand each
+// finished tile to it through a small mailbox ring of mbarriers and go on with the next tile.
+// The last CTA to leave restores all counters, also after a give-up, so the next launch starts clean.
 //
 // Every wait is bounded (pipeline.cuh); one that gives up raises the status word.
 #include <cuda.h>
@@ -47,9 +50,10 @@ namespace {
 
 constexpr int kListMaxThreads = 448;   // consumer threads per CTA
 constexpr int kListMaxStages = 8;
-constexpr int kListHeader = 256;       // barriers + abort flag
+constexpr int kListHeader = 512;       // barriers, abort flag, mailbox of finished tiles
 constexpr int kListSmem = 226 * 1024;     // dynamic part; the kernel's static shared memory takes up to 1 KB of the 227
 constexpr int kListMaxDeps = 4;
+constexpr int kListSigSlots = 4;       // finished tiles in flight to the signalling warp
 constexpr int kListMaxTN = 112;        // 4 phases x 112 columns = 448 threads
 
 // What the kernel needs to know about one item: exactly 32 words.
@@ -62,7 +66,8 @@ struct alignas(128) ItemHot {
   const float* residual;    // [M, N] added to the product, or null (may be C itself)
   int N, K, G, TN;
   int tiles, first_cta, phases, rpp;
-  int stage_rows, row_pitch, nst, use_tma;
+  int stage_rows, row_pitch, nst;
+  int c0;                   // 0: one bulk copy per group-row; else stages arrive as tensor-map boxes and c0 = columns of the first panel
   int nB, a_id;             // a_id: items with equal a_id read the same activations in the same state
   float eps;
   int ndeps;
@@ -72,8 +77,8 @@ static_assert(sizeof(ItemHot) == 128, "ItemHot is loaded as eight 16-byte words"
 
 struct ListParams {
   const ItemHot* items;
-  const CUtensorMap* maps;  // [2 * nitems]
-  unsigned* done;           // [nitems] outstanding output warps per item
+  const CUtensorMap* maps;  // [4 * nitems]: per item {B0 panel 0, B0 panel 1, B1 panel 0, B1 panel 1}
+  unsigned* done;           // [nitems] outstanding tiles per item
   const unsigned* done_init;  // [nitems]
   unsigned* ticket;         // CTAs that have left
   int* status;
@@ -101,13 +106,13 @@ __device__ __forceinline__ ItemHot load_item(const ItemHot* p) {
   it.residual = reinterpret_cast<const float*>(ptr(w[2].z, w[2].w));
   it.N = (int)w[3].x, it.K = (int)w[3].y, it.G = (int)w[3].z, it.TN = (int)w[3].w;
   it.tiles = (int)w[4].x, it.first_cta = (int)w[4].y, it.phases = (int)w[4].z, it.rpp = (int)w[4].w;
-  it.stage_rows = (int)w[5].x, it.row_pitch = (int)w[5].y, it.nst = (int)w[5].z, it.use_tma = (int)w[5].w;
+  it.stage_rows = (int)w[5].x, it.row_pitch = (int)w[5].y, it.nst = (int)w[5].z, it.c0 = (int)w[5].w;
   it.nB = (int)w[6].x, it.a_id = (int)w[6].y, it.eps = __uint_as_float(w[6].z), it.ndeps = (int)w[6].w;
   it.dep[0] = (int)w[7].x, it.dep[1] = (int)w[7].y, it.dep[2] = (int)w[7].z, it.dep[3] = (int)w[7].w;
   return it;
 }
 
-// Bounded wait until item `dep` is complete everywhere (its counter of outstanding warps is zero).
+// Bounded wait until item `dep` is complete everywhere (its counter of outstanding tiles is zero).
 __device__ __forceinline__ bool wait_item(const unsigned* counter, const int* status) {
   const long long t0 = clock64();
   for (unsigned spin = 0;; spin++) {
@@ -136,24 +141,33 @@ __device__ __forceinline__ bool consumers_sync_any(int nct, bool mine) {
   return any != 0;
 }
 
-template <int KIND, int MR, int RPP>
-__device__ __forceinline__ void consume_stage(const uint8_t* stage, int st, int stage_rows, int G, int phases,
-                                              int phase, int col, int row_pitch, const uint4* xdig,
+// One stage against the digits: this thread's column (at byte `base` of a stage row of its panel,
+// rows `pitch` bytes apart), group-rows phase, phase + phases, ... of the stage.
+template <int KIND, int MR>
+__device__ __forceinline__ void consume_stage(const uint8_t* stage, int st, int stage_rows, int rpp, int G, int phases,
+                                              int phase, uint32_t base, uint32_t pitch, const uint4* xdig,
                                               const float2* xsc, float (&acc)[MR]) {
-  constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   const int g0 = st * stage_rows + phase;
   if (st * stage_rows + stage_rows <= G) {
+    int rr = 0;
+    for (; rr + 4 <= rpp; rr += 4) {
 #pragma unroll
-    for (int rr = 0; rr < RPP; rr++) {
-      const uint32_t off = (uint32_t)(phase + rr * phases) * row_pitch + (uint32_t)col * BB;
+      for (int u = 0; u < 4; u++) {
+        const uint32_t off = base + (uint32_t)(phase + (rr + u) * phases) * pitch;
+        const int g = g0 + (rr + u) * phases;
+        block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
+      }
+    }
+    for (; rr < rpp; rr++) {
+      const uint32_t off = base + (uint32_t)(phase + rr * phases) * pitch;
       const int g = g0 + rr * phases;
       block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
     }
   } else {
-    for (int rr = 0; rr < RPP; rr++) {
+    for (int rr = 0; rr < rpp; rr++) {
       const int g = g0 + rr * phases;
       if (g < G) {
-        const uint32_t off = (uint32_t)(phase + rr * phases) * row_pitch + (uint32_t)col * BB;
+        const uint32_t off = base + (uint32_t)(phase + rr * phases) * pitch;
         block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
       }
     }
@@ -161,12 +175,15 @@ __device__ __forceinline__ void consume_stage(const uint8_t* stage, int st, int 
 }
 
 template <int KIND, int MR>
-__global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(const ListParams p) {
+__global__ void __launch_bounds__(kListMaxThreads + 64, 1) qgemv_list_kernel(const ListParams p) {
   constexpr int BB = (KIND == 4) ? kQ4Bytes : kQ8Bytes;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + kListMaxStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kListMaxStages * 8);
+  uint64_t* sig_full = reinterpret_cast<uint64_t*>(smem + 256);                 // a finished tile is posted
+  uint64_t* sig_empty = sig_full + kListSigSlots;                               // ... and has been counted
+  volatile int* sig_item = reinterpret_cast<volatile int*>(smem + 256 + 2 * kListSigSlots * 8);
   uint4* xdig = reinterpret_cast<uint4*>(smem + p.xdig_off);     // [MR][G][4] uint4
   float2* xsc = reinterpret_cast<float2*>(smem + p.xsc_off);     // [MR][G]
   float* rms_part = reinterpret_cast<float*>(smem + p.rms_off);  // [MR][nwarps]
@@ -182,12 +199,37 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
       mbar_init(smem_u32(&full[s]), 1);
       mbar_init(smem_u32(&empty[s]), nwarps);
     }
+    for (int s = 0; s < kListSigSlots; s++) {
+      mbar_init(smem_u32(&sig_full[s]), nwarps);
+      mbar_init(smem_u32(&sig_empty[s]), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
-  if (tid >= nct) {
+  if (tid >= nct + 32) {
+    // ------------------------------------------------------------ signalling warp
+    // Counts finished tiles: waits for the consumers to post one, fences (their stores to C become
+    // visible device-wide before the count) and decrements the item's counter.  An item index of -1
+    // ends it.
+    if ((tid & 31) == 0) {
+      int slot = 0;
+      uint32_t par = 0;
+      for (;;) {
+        if (!mbar_wait(smem_u32(&sig_full[slot]), par, abort_flag, p.status)) break;
+        const int item = sig_item[slot];
+        if (item >= 0) {
+          __threadfence();
+          atomicSub(p.done + item, 1u);
+        }
+        mbar_arrive(smem_u32(&sig_empty[slot]));
+        if (item < 0) break;
+        slot = (slot + 1 == kListSigSlots) ? 0 : slot + 1;
+        par ^= (slot == 0);
+      }
+    }
+  } else if (tid >= nct) {
     // ------------------------------------------------------------ producer warp
     // Walks items, tiles and stages in the consumers' order, one ring slot per stage, and never
     // waits for anything but a free slot.
@@ -210,7 +252,7 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
         const uint32_t row_bytes = (uint32_t)tn * BB;
         for (int bi = 0; bi < it.nB && live; bi++) {
           const uint8_t* __restrict__ Bm = bi ? it.B1 : it.B0;
-          const CUtensorMap* map = p.maps + 2 * i + bi;
+          const CUtensorMap* map = p.maps + 4 * i + 2 * bi;
           for (int st = 0; st < it.nst; st++) {
             if (issued >= p.slots) {
               int okw = 1;
@@ -223,12 +265,16 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
             const int rows = min(it.stage_rows, it.G - st * it.stage_rows);
             const uint32_t bar = smem_u32(&full[slot]);
             const uint32_t dst = smem_u32(ring + (size_t)slot * p.slot_bytes);
-            if (it.use_tma) {
-              // the box is always stage_rows x TN blocks: what lies beyond N or the last group-row is zero-filled
-              if (lane == 0) {
-                mbar_expect_tx(bar, (uint32_t)it.stage_rows * (uint32_t)it.row_pitch);
-                tma_box_2d(dst, map, (col0 * BB) >> 3, st * it.stage_rows, bar, policy);
-              }
+            if (it.c0) {
+              // One box per panel, always stage_rows x panel columns: what lies beyond N or the last
+              // group-row is zero-filled.  The second panel starts on the next 128 bytes.
+              if (lane == 0) mbar_expect_tx(bar, (uint32_t)it.stage_rows * (uint32_t)it.row_pitch);
+              __syncwarp();
+              const int c1 = it.TN - it.c0;
+              if (lane == 0) tma_box_2d(dst, map, (col0 * BB) >> 3, st * it.stage_rows, bar, policy);
+              if (lane == 1 && c1 > 0)
+                tma_box_2d(dst + (((uint32_t)it.stage_rows * it.c0 * BB + 127u) & ~127u), map + 1, ((col0 + it.c0) * BB) >> 3,
+                           st * it.stage_rows, bar, policy);
             } else {
               if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
               __syncwarp();
@@ -253,6 +299,22 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
     uint32_t par = 0;
     int cur_a = -1;                                 // a_id whose digits are in shared memory
     int red_buf = 0;
+    int sig_slot = 0, sig_used = 0;                 // mailbox slot of the next finished tile
+    uint32_t sig_par = 0;
+    // Hands a finished tile (or the end mark) to the signalling warp.  Thread 0 first makes sure the
+    // slot's previous tile has been counted; its warp's arrival is the last a phase can get, so the
+    // item index is in place when the phase completes.
+    auto post = [&](int item) {
+      if (tid == 0) {
+        if (sig_used >= kListSigSlots) mbar_wait(smem_u32(&sig_empty[sig_slot]), sig_par ^ 1u, abort_flag, p.status);
+        sig_item[sig_slot] = item;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sig_full[sig_slot]));
+      if (sig_used < kListSigSlots) sig_used++;
+      sig_slot = (sig_slot + 1 == kListSigSlots) ? 0 : sig_slot + 1;
+      sig_par ^= (sig_slot == 0);
+    };
     ItemHot nxt = load_item(p.items);
     for (int i = 0; i < p.nitems && !quit; i++) {
       const ItemHot it = nxt;
@@ -348,6 +410,15 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
         const bool active = tid < tn * it.phases;
         const int col = active ? (tid % tn) : 0;
         const int phase = active ? (tid / tn) : 0;
+        // where this thread's column sits in a stage: boxes land as one or two dense panels
+        uint32_t base = (uint32_t)col * BB, pitch = (uint32_t)it.row_pitch;
+        if (it.c0) {
+          pitch = (uint32_t)it.c0 * BB;
+          if (col >= it.c0) {
+            base = (((uint32_t)it.stage_rows * it.c0 * BB + 127u) & ~127u) + (uint32_t)(col - it.c0) * BB;
+            pitch = (uint32_t)(it.TN - it.c0) * BB;
+          }
+        }
         float acc[MR], gate[MR];
 #pragma unroll
         for (int m = 0; m < MR; m++) acc[m] = 0.f, gate[m] = 0.f;
@@ -360,10 +431,7 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full[slot]), par, abort_flag, p.status));   // warp-uniform
             if (ok && active) {
               const uint8_t* stage = ring + (size_t)slot * p.slot_bytes;
-              if (it.rpp == 4)
-                consume_stage<KIND, MR, 4>(stage, st, it.stage_rows, it.G, it.phases, phase, col, it.row_pitch, xdig, xsc, acc);
-              else
-                consume_stage<KIND, MR, 3>(stage, st, it.stage_rows, it.G, it.phases, phase, col, it.row_pitch, xdig, xsc, acc);
+              consume_stage<KIND, MR>(stage, st, it.stage_rows, it.rpp, it.G, it.phases, phase, base, pitch, xdig, xsc, acc);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
@@ -398,13 +466,10 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
           if (it.residual) v = __ldcg(it.residual + at) + v;
           it.C[at] = v;
         }
-        __syncwarp();
-        if (lane == 0 && warp * 32 < p.M * tn) {
-          __threadfence();                            // this warp's stores before the count
-          atomicSub(p.done + i, 1u);
-        }
+        post(i);
       }
     }
+    post(-1);
   }
 
   // ------------------------------------------------ leave: the last CTA restores the counters
@@ -424,16 +489,20 @@ __global__ void __launch_bounds__(kListMaxThreads + 32, 1) qgemv_list_kernel(con
 
 // ---------------------------------------------------------------------------------------- host side
 
+// Planner knobs, overridable from the environment for measurements.
 struct Tuning {
-  int tma;        // -1 by rule, 0 never, 1 wherever a box fits
-  int rpp;        // group-rows per phase and stage
+  int tma;          // 1: stages arrive as tensor-map boxes (default), 0: one bulk copy per group-row
+  int stage_bytes;  // target size of a stage
   int max_tn;
 };
 
 Tuning tuning() {
-  Tuning t{-1, 4, kListMaxTN};
-  if (const char* v = getenv("SMITH_LIST_TMA")) t.tma = atoi(v);
-  if (const char* v = getenv("SMITH_LIST_RPP")) t.rpp = (atoi(v) == 3) ? 3 : 4;
+  // Measured on B200 with a stand-alone ring (no arithmetic), 4096 x 14336 tiles: 16 bulk copies of
+  // 2.3 KB per 37 KB stage, 5 slots: 6.1 TB/s; the same stage as two boxes: 6.2-6.4; 74 KB stages of
+  // two boxes, 2-3 slots: 6.6-6.8.  Per-row bulk copies of 656 bytes: 2.4-2.9 TB/s; boxes: 6.4-6.8.
+  Tuning t{1, 72 * 1024, kListMaxTN};
+  if (const char* v = getenv("SMITH_LIST_TMA")) t.tma = atoi(v) ? 1 : 0;
+  if (const char* v = getenv("SMITH_LIST_STAGE_BYTES")) t.stage_bytes = max(4096, min(100 * 1024, atoi(v)));
   if (const char* v = getenv("SMITH_LIST_MAX_TN")) t.max_tn = max(8, min(kListMaxTN, atoi(v)));
   return t;
 }
@@ -455,7 +524,7 @@ int list_fail(const char** why, const char* fmt, ...) {
 }
 
 // Tiling of one item for a grid of `ncta` CTAs.
-void plan_item(int kind, int M, const ListItemDesc& d, int ncta, int rpp, const Tuning& tu, ItemHot& h) {
+void plan_item(int kind, int M, const ListItemDesc& d, int ncta, int stage_bytes, const Tuning& tu, ItemHot& h) {
   const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
   const int64_t q = (kind == 4) ? 2 : 8;          // a tile's group-row span starts and ends on 16 bytes
   h.N = (int)d.N, h.K = (int)d.K, h.G = (int)(d.K / 32);
@@ -466,18 +535,31 @@ void plan_item(int kind, int M, const ListItemDesc& d, int ncta, int rpp, const 
   }
   h.TN = TN;
   h.tiles = (int)((d.N + TN - 1) / TN);
-  int phases = (kListMaxThreads / TN) & ~3;
-  if (phases < 4) phases = 4;
-  while (phases > 4 && phases * rpp > h.G * 2) phases -= 4;   // short K: do not over-split
+  // K-phases: as many as fill the consumer threads, no more than there are group-rows
+  int phases = kListMaxThreads / TN;
+  if (phases > 4) phases &= ~3;
+  if (phases > h.G) phases = h.G;
+  if (phases < 1) phases = 1;
   h.phases = phases;
+  h.row_pitch = TN * BB;
+  // group-rows per phase and stage: large stages stream best, but none larger than K needs
+  int rpp = stage_bytes / (phases * h.row_pitch);
+  const int need = (h.G + phases - 1) / phases;
+  if (rpp > need) rpp = need;
+  if (rpp * phases > 256) rpp = 256 / phases;     // a box side holds at most 256 rows
+  if (rpp < 1) rpp = 1;
   h.rpp = rpp;
   h.stage_rows = phases * rpp;
-  h.row_pitch = TN * BB;
   h.nst = (h.G + h.stage_rows - 1) / h.stage_rows;
-  // One 2-D box per stage instead of one bulk copy per group-row pays where the row segments are
-  // short and many (a box side holds at most 256 elements of 8 bytes).
-  const bool fits = h.row_pitch <= 2048 && h.stage_rows <= 256 && (h.row_pitch % 16) == 0;
-  h.use_tma = fits && (tu.tma == 1 || (tu.tma == -1 && h.row_pitch <= 1408 && h.G >= 192)) ? 1 : 0;
+  // Boxes: a box side holds at most 256 elements of 8 bytes, so tiles wider than 2 KB arrive as two
+  // panels; each panel's first column must start on 16 bytes (any even column for 24-byte blocks, a
+  // multiple of 8 for 34-byte blocks).
+  h.c0 = 0;
+  if (tu.tma) {
+    int c0 = TN;
+    if (c0 * BB > 2048) c0 = (int)(q * ((TN / 2 + q - 1) / q));
+    if (c0 * BB <= 2048 && (TN - c0) * BB <= 2048) h.c0 = c0;
+  }
   h.nB = d.B2 ? 2 : 1;
   (void)M;
 }
@@ -578,18 +660,22 @@ ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, i
   ListProgram* lp = new ListProgram();
   lp->kind = kind, lp->M = (int)M, lp->nitems = count, lp->ncta = sms, lp->device = dev;
   std::vector<ItemHot> hot(count);
-  int rpp = tu.rpp;
   int slots = 0, slot_bytes = 0, nthreads = 0, ring_off = 0, xdig_off = 0, xsc_off = 0, rms_off = 0, red_off = 0, red_half = 0;
-  for (int attempt = 0; attempt < 2; attempt++, rpp = 3) {
+  // Three slots of the target stage size where they fit beside the activations' digit form;
+  // smaller stages otherwise.
+  for (int stage_bytes = tu.stage_bytes; stage_bytes >= 4096; stage_bytes = stage_bytes * 3 / 4) {
     int gmax = 0, red_max = 0;
     slot_bytes = 0, nthreads = 0;
     for (int i = 0; i < count; i++) {
       ItemHot& h = hot[i];
       memset(&h, 0, sizeof h);
-      plan_item(kind, (int)M, items[i], sms, rpp, tu, h);
+      plan_item(kind, (int)M, items[i], sms, stage_bytes, tu, h);
       gmax = max(gmax, h.G);
-      slot_bytes = max(slot_bytes, ((h.stage_rows * h.row_pitch + 127) / 128) * 128);
-      nthreads = max(nthreads, h.TN * h.phases);
+      int bytes = h.stage_rows * h.row_pitch;
+      if (h.c0 && h.c0 < h.TN)
+        bytes = ((h.stage_rows * h.c0 * BB + 127) & ~127) + h.stage_rows * (h.TN - h.c0) * BB;
+      slot_bytes = max(slot_bytes, ((bytes + 127) / 128) * 128);
+      nthreads = max(nthreads, max(h.TN * h.phases, (int)M * h.TN));   // the epilogue gives every output its own thread
       red_max = max(red_max, h.phases * (int)M * h.TN * 4 * h.nB);
     }
     xdig_off = kListHeader;
@@ -600,7 +686,7 @@ ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, i
     ring_off = ((red_off + 2 * red_half + 1023) / 1024) * 1024;
     slots = (kListSmem - 64 - ring_off) / slot_bytes;   // 64: the Q8 dot reads whole words around a block
     if (slots > kListMaxStages) slots = kListMaxStages;
-    if (slots >= 4 || rpp == 3) break;
+    if (slots >= 3) break;
   }
   if (slots < 2 || nthreads > kListMaxThreads) {
     list_fail(why, "the list does not fit shared memory (%d ring slots of %d bytes, %d threads)", slots, slot_bytes, nthreads);
@@ -652,7 +738,7 @@ ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, i
   }
   // ---- device block: items | maps | done_init | done | ticket
   const size_t items_bytes = (size_t)count * sizeof(ItemHot);
-  const size_t maps_bytes = (size_t)count * 2 * sizeof(CUtensorMap);
+  const size_t maps_bytes = (size_t)count * 4 * sizeof(CUtensorMap);
   const size_t cnt_bytes = (((size_t)count * 4 + 127) / 128) * 128;
   lp->dev_bytes = items_bytes + maps_bytes + 2 * cnt_bytes + 128;
   std::vector<uint8_t> host(lp->dev_bytes, 0);
@@ -662,22 +748,28 @@ ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, i
   EncodeTiledFn enc = encode_fn();
   for (int i = 0; i < count; i++) {
     ItemHot& h = hot[i];
-    if (h.use_tma) {
-      // each packed matrix as [G][N * block bytes / 8] 64-bit words, box = one stage of one tile
+    if (h.c0) {
+      // each packed matrix as [G][N * block bytes / 8] 64-bit words; box = one stage of one panel of a tile
       const cuuint64_t dims[2] = {(cuuint64_t)h.N * BB / 8, (cuuint64_t)h.G};
       const cuuint64_t strides[1] = {(cuuint64_t)h.N * BB};
-      const cuuint32_t box[2] = {(cuuint32_t)h.row_pitch / 8, (cuuint32_t)h.stage_rows};
       const cuuint32_t estr[2] = {1, 1};
       bool good = enc != nullptr;
       for (int b = 0; b < h.nB && good; b++)
-        good = enc(&maps[2 * i + b], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(b ? h.B1 : h.B0), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-      if (!good) h.use_tma = 0;                   // plain bulk copies
+        for (int pn = 0; pn < 2 && good; pn++) {
+          const int cols = pn ? h.TN - h.c0 : h.c0;
+          if (cols == 0) continue;
+          const cuuint32_t box[2] = {(cuuint32_t)(cols * BB / 8), (cuuint32_t)h.stage_rows};
+          good = enc(&maps[4 * i + 2 * b + pn], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(b ? h.B1 : h.B0), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        }
+      if (!good) {
+        list_fail(why, "item %d: the driver refused the tensor map of a %d x %d tile", i, h.stage_rows, h.TN);
+        delete lp;
+        return nullptr;
+      }
     }
-    unsigned warps = 0;
-    for (int t = 0; t < h.tiles; t++) warps += (unsigned)(((int)M * min(h.TN, h.N - t * h.TN) + 31) / 32);
-    init[i] = done[i] = warps;
+    init[i] = done[i] = (unsigned)h.tiles;
   }
   memcpy(host.data(), hot.data(), items_bytes);
   if (cudaMalloc(&lp->dev_block, lp->dev_bytes) != cudaSuccess) {
@@ -705,7 +797,7 @@ ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, i
   p.slots = slots, p.slot_bytes = slot_bytes;
   p.xdig_off = xdig_off, p.xsc_off = xsc_off, p.rms_off = rms_off, p.red_off = red_off, p.red_half = red_half;
   p.ring_off = ring_off;
-  lp->threads = p.nwarps * 32 + 32;
+  lp->threads = p.nwarps * 32 + 64;              // consumers, producer warp, signalling warp
   lp->smem = (size_t)ring_off + (size_t)slots * slot_bytes + 64;
   return lp;
 }
