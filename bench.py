@@ -5,10 +5,14 @@
 
 A "step" is one pass of the hot path over R distinct, device-resident packed
 weight matrices of the workload's shape (R chosen so that R x bytes is at least
-four times the 126 MB L2: consecutive launches never find their weights in
-cache).  The R launches of a step are captured once in a CUDA graph and
-replayed, the way a decode engine replays its layer stack.  Timing is CUDA
-events on the launching stream, max over ranks, between barriers.
+four times the 126 MB L2: consecutive products never find their weights in
+cache).  For GEMV shapes (M <= 4) on one GPU the R products of a step run as ONE
+persistent launch (smith_qmatmul_list), the way a decode engine runs its layer
+stack; `config.form` says so and `config.per_call` gives the same R products as
+R separate launches replayed from a CUDA graph.  Other shapes, and several GPUs,
+use the graph of separate launches.  Timing is CUDA events on the launching
+stream, max over ranks, between barriers.  Before anything is timed, a column
+window of one output is compared with the CPU oracle (`parity`).
 
 `value`  : algorithmic bytes (M <= 16) or FLOPs (M >= 64) of all launches / device time.
 `e2e`    : the same quantity through the operator API (smith_b200.matmulQ4 /
@@ -42,22 +46,22 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     # name: kind, M, K, N, weight std
-    "q4_decode_gemv_4096x14336_m1": dict(kind=4, M=1, K=4096, N=14336, std=0.02),   # configs[2], M=1 (the 70 % target)
+    "q4_decode_gemv_4096x14336_m1": dict(kind=4, M=1, K=4096, N=14336, std=0.02),   # the decode GEMV the 70 % HBM target is quoted on
     "q4_decode_4096x14336_m4": dict(kind=4, M=4, K=4096, N=14336, std=0.02),
     "q4_decode_4096x14336_m16": dict(kind=4, M=16, K=4096, N=14336, std=0.02),
     "q4_prefill_4096x14336_m64": dict(kind=4, M=64, K=4096, N=14336, std=0.02),
     "q4_prefill_4096x14336_m256": dict(kind=4, M=256, K=4096, N=14336, std=0.02),
-    "q4_prefill_4096x14336_m512": dict(kind=4, M=512, K=4096, N=14336, std=0.02),   # the 50 % tensor target
-    "q8_prefill_gemm_4096x11008_m512": dict(kind=8, M=512, K=4096, N=11008, std=0.02),  # configs[1]
-    "q4_gemv_4096x4096_m1": dict(kind=4, M=1, K=4096, N=4096, std=0.02),            # configs[0]
+    "q4_prefill_4096x14336_m512": dict(kind=4, M=512, K=4096, N=14336, std=0.02),   # the prefill GEMM the 50 % tensor target is quoted on
+    "q8_prefill_gemm_4096x11008_m512": dict(kind=8, M=512, K=4096, N=11008, std=0.02),  # Q8 prefill GEMM 512 x 4096 x 11008
+    "q4_gemv_4096x4096_m1": dict(kind=4, M=1, K=4096, N=4096, std=0.02),            # the single Q4 GEMV a CPU can also run in full
     "q4_lm_head_4096x128256_m1": dict(kind=4, M=1, K=4096, N=128256, std=0.02),
     "q8_decode_gemv_4096x14336_m1": dict(kind=8, M=1, K=4096, N=14336, std=0.02),
-    # BASELINE configs[3]: every Q4 projection of an 8B-Llama-shaped decode step (32 layers + lm_head, 5.63 GB)
+    # every Q4 projection of an 8B-Llama-shaped decode step (32 layers + lm_head, 5.63 GB)
     "q4_llama8b_step_m1": dict(kind=4, M=1, step=dict(layers=32, dim=4096, kv=1024, ffn=14336, vocab=128256), std=0.02,
                                K=4096, N=14336),
     "q4_llama8b_step_m16": dict(kind=4, M=16, step=dict(layers=32, dim=4096, kv=1024, ffn=14336, vocab=128256), std=0.02,
-                                K=4096, N=14336),       # configs[3] at batch 16 (single GPU)
-    # BASELINE configs[4]: the projections of a 70B-Llama-shaped decode step (80 layers + lm_head, 52.1 GB)
+                                K=4096, N=14336),       # the same step at batch 16 (single GPU)
+    # the projections of a 70B-Llama-shaped decode step (80 layers + lm_head, 52.1 GB)
     "q4_llama70b_step_m1": dict(kind=4, M=1, step=dict(layers=80, dim=8192, kv=1024, ffn=28672, vocab=128256), std=0.015,
                                 K=8192, N=28672),
 }
@@ -133,7 +137,7 @@ def cpu_run(kind, M, K, N, seconds, threads=None):
     import numpy as np
     from oracle import oracle as O
     knd = "q4" if kind == 4 else "q8"
-    threads = threads or O.max_threads()
+    threads = threads or O.host_threads()      # not omp_get_max_threads(): launchers export OMP_NUM_THREADS=1
     use_ref = O.have_ref()
     fn = O.ref_matmul if use_ref else O.matmul
     rng = np.random.default_rng(0)
@@ -189,7 +193,7 @@ def run_reference_arm(args, wl, name):
         "impl": "reference", "metric": metric_name(wl["M"]), "value": value, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_call * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "launches_per_step": 1,
+        "config": {"workload": name, "kind": f"q{wl['kind']}", "M": wl["M"], "K": wl["K"], "N": wl["N"],
                    "note": "the reference's own CPU implementation of the path (its matmul shader source compiled "
                            "as C++ when oracle/_ref is built, else the C restatement), all host threads; "
                            "the reference's Metal path is unavailable on this box"},
@@ -201,6 +205,167 @@ def run_reference_arm(args, wl, name):
 
 
 # ----------------------------------------------------------------------------- decode-step workload
+def run_step_list(args, wl):
+    """One GPU, M <= 4: the whole decode step's projections as ONE persistent launch with the
+    reference's pointwise glue folded in (src/gguf_cache.js:121-171): per layer
+        q, k, v = rmsnorm(x, ln1) W{q,k,v};   x2 = x + attn Wo;
+        h = silu(rmsnorm(x2, ln2) Wgate) * (rmsnorm(x2, ln2) Wup);   x = x2 + h Wdown
+    then logits = rmsnorm(x, lnF) Wlm_head.  Attention itself is outside the path: a fixed synthetic
+    row stands in for its output.  Hazards between the items (x, x2, h are written and read by
+    consecutive items) are resolved on the device."""
+    import numpy as np
+    import torch
+    import smith_b200 as smith
+    from oracle import oracle as O
+    from smith_b200 import device as D
+    kind, M, st = wl["kind"], wl["M"], wl["step"]
+    dim, kv, ffn, vocab, layers = st["dim"], st["kv"], st["ffn"], st["vocab"], st["layers"]
+    bb, eps = 24, 1e-5
+    torch.cuda.set_device(0)
+    D.ctx()
+    stream = torch.cuda.ExternalStream(D.stream())
+    steps = min(args.steps, 200)
+    warm = max(min(args.warmup, 10), 3)
+    wtmp = D.alloc(max(dim * ffn, dim * vocab) * 4, D.PRIVATE)
+    seed = [17]
+    weight_bytes, alg_bytes = [0], [0]
+
+    def make(k, n):
+        D.fillNormal(wtmp, k * n, seed[0], wl["std"])
+        seed[0] += 1
+        pk = D.alloc((k // 32) * n * bb, D.PRIVATE)
+        D.q4Pack(wtmp, pk, k, n)
+        weight_bytes[0] += (k // 32) * n * bb
+        alg_bytes[0] += (k // 32) * n * bb + 4 * M * k + 4 * M * n
+        return pk
+
+    def vec(n, sd, value):
+        b = D.alloc(n * 4, D.PRIVATE)
+        D.fillNormal(b, n, sd, 0.05)
+        v = D.download(b, n * 4, np.float32) + value
+        D.upload(b, v.astype(np.float32))
+        return b
+
+    xs = [D.alloc(M * dim * 4, D.PRIVATE) for _ in range(2)]
+    x2, attn = D.alloc(M * dim * 4, D.PRIVATE), D.alloc(M * dim * 4, D.PRIVATE)
+    q, k_, v_, h = (D.alloc(M * n * 4, D.PRIVATE) for n in (dim, kv, kv, ffn))
+    logits = D.alloc(M * vocab * 4, D.PRIVATE)
+    x0 = D.alloc(M * dim * 4, D.PRIVATE)
+    D.fillNormal(x0, M * dim, 7, 1.0)
+    D.fillNormal(attn, M * dim, 8, 1.0)
+    items = []
+    for l in range(layers):
+        ln1, ln2 = vec(dim, 100 + 2 * l, 1.0), vec(dim, 101 + 2 * l, 1.0)
+        x_in, x_out = (x0 if l == 0 else xs[l & 1]), xs[(l + 1) & 1]
+        items += [D.listItem(x_in, make(dim, dim), q, dim, dim, gamma=ln1, eps=eps),
+                  D.listItem(x_in, make(dim, kv), k_, kv, dim, gamma=ln1, eps=eps),
+                  D.listItem(x_in, make(dim, kv), v_, kv, dim, gamma=ln1, eps=eps),
+                  D.listItem(attn, make(dim, dim), x2, dim, dim, residual=x_in),
+                  D.listItem(x2, make(dim, ffn), h, ffn, dim, b2=make(dim, ffn), gamma=ln2, eps=eps),
+                  D.listItem(h, make(ffn, dim), x_out, dim, ffn, residual=x2)]
+    lnf = vec(dim, 99, 1.0)
+    x_last = xs[layers & 1]
+    head = make(dim, vocab)
+    items.append(D.listItem(x_last, head, logits, vocab, dim, gamma=lnf, eps=eps))
+    D.synchronize()
+    D.releaseBuffer(wtmp)
+    lst = D.qmatmulListCreate(kind, M, items)
+
+    def sync():
+        D.synchronize()
+        torch.cuda.synchronize()
+
+    D.qmatmulListRun(lst)
+    sync()
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up during warm-up")
+    # ---- parity before timing: a window of the logits against the oracle on the device's own final row
+    xf = D.download(x_last, M * dim * 4, np.float32).reshape(M, dim)
+    gf = D.download(lnf, dim * 4, np.float32)
+    c0 = (vocab // 2) // 8 * 8
+    cols = np.concatenate([D.download(head, 48 * bb, np.uint8, offset=(g * vocab + c0) * bb) for g in range(dim // 32)])
+    nrm = O.rmsnorm(xf, gf, eps)
+    want = O.matmul(nrm, cols, dim, 48, "q4", threads=O.host_threads())
+    got = D.download(logits, M * vocab * 4, np.float32).reshape(M, vocab)
+    bound = O.tolerance_bound(nrm, O.dequant(cols, dim, 48, "q4"), 1e-3)
+    worst = float((np.abs(got[:, c0:c0 + 48].astype(np.float64) - want) / np.maximum(bound, 1e-300)).max())
+    parity = {"checked": True, "worst_err_over_bound": worst, "ok": bool(worst <= 1.0 and np.all(np.isfinite(got))),
+              "what": "48 logits of the step (rmsnorm + lm_head on the residual row the device produced through "
+                      "all layers) against the CPU oracle; bound = 1e-3 * ||x_m|| * ||w_deq[:,n]||"}
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed before timing: {parity}")
+    for _ in range(warm):
+        D.qmatmulListRun(lst)
+    sync()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(max(0, int(0.25 / 1.2e-3)) if layers <= 32 else 30):      # settle: clocks sampled under load
+        D.qmatmulListRun(lst)
+    e0.record(stream)
+    for _ in range(steps):
+        D.qmatmulListRun(lst)
+    e1.record(stream)
+    sync()
+    ms = e0.elapsed_time(e1)
+    # ---- end to end: the step's input row from page-locked host memory, the launch, the logits back
+    x_np = D.download(x0, M * dim * 4, np.float32)
+
+    def e2e_pass():
+        D.upload(x0, x_np)
+        D.qmatmulListRun(lst)
+        D.synchronize()
+        return D.download(logits, M * vocab * 4, np.float32)
+
+    for _ in range(2):
+        e2e_pass()
+    e2e_steps = max(3, min(steps, 50))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up: results invalid")
+    step_s = ms * 1e-3 / steps
+    peaks = measured_peaks()
+    ach = alg_bytes[0] / step_s / 1e9
+    line = {
+        "metric": "Q4 decode step HBM GB/s (algorithmic bytes of all projections / time)",
+        "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_NOTE["gemv"], "data": "synthetic",
+        "config": {"workload": args.workload, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv, "ffn": ffn,
+                   "vocab": vocab, "matmuls_per_step": 7 * layers + 1, "launches_per_step": 1, "items_per_launch": len(items),
+                   "form": "list: every projection of the step in ONE persistent launch; RMSNorm folded into the "
+                           "q/k/v, gate/up and lm_head items, SwiGLU into the gate/up item, the residual adds into the "
+                           "wo and down items; hazards between items resolved on the device",
+                   "packed_bytes_per_gpu": weight_bytes[0], "tokens_per_s": M / step_s, "sharding": "single GPU",
+                   "l2": "every item reads its own packed matrix; one step's weights are %d x the 126 MB L2"
+                         % (weight_bytes[0] // L2_BYTES),
+                   "timing": "CUDA events on the launch stream around the timed launches"},
+        "parity": parity,
+        "e2e": {"value": alg_bytes[0] / (e2e_s / e2e_steps) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * M * dim,
+                "d2h_bytes_per_step": 4 * M * vocab, "steps": e2e_steps,
+                "note": "per step: H2D of the input row from page-locked memory, the launch, wait, D2H of the logits"},
+        "gpu_launches": int(steps + e2e_steps + warm + 3),
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s", "frac": ach / peaks["hbm"],
+                     "traffic": None,
+                     "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
+                     else "fallback (no MEASURED_PEAKS.json)",
+                     "peak_kind": "copy bandwidth", "frac_of_nominal": ach / 8000.0,
+                     "algorithmic_per_launch": alg_bytes[0], "launch_us": step_s * 1e6},
+        "clocks": clocks,
+    }
+    if not args.no_cpu:
+        per_call, threads, ckind, sample = cpu_run(kind, M, dim, ffn, seconds=args.cpu_seconds)
+        gate_bytes = algorithmic(kind, M, dim, ffn)[0]
+        line["cpu_baseline"] = {"value": gate_bytes / per_call / 1e9, "unit": "GB/s", "cores": threads, "kind": ckind,
+                                "sample": "the step's gate projection (%d x %d): " % (dim, ffn) + sample}
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line))
+
+
 def run_step_workload(args, wl):
     """One decode step's projection list (no pointwise glue): per layer wq, wk, wv, wo, gate, up, down,
     then lm_head: 225 matmuls over 5.63 GB of distinct packed weights (larger than L2 by itself),
@@ -215,6 +380,8 @@ def run_step_workload(args, wl):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if world == 1 and wl["M"] <= 4 and not args.no_list:
+        return run_step_list(args, wl)
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -378,7 +545,7 @@ def run_step_workload(args, wl):
             "metric": "Q4 decode step HBM GB/s (algorithmic bytes of all projections / time)",
             "value": alg_all / step_s / 1e9, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32 accumulate over u4 codes", "data": "synthetic",
+            "dtype": DTYPE_NOTE["gemv" if M <= 4 else "decode"], "data": "synthetic",
             "config": {"workload": args.workload, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv,
                        "ffn": ffn, "vocab": vocab, "matmuls_per_step": 7 * layers + 1, "launches_per_step": len(ops),
                        "packed_bytes_per_gpu": weight_bytes, "tokens_per_s": M / step_s,
@@ -415,50 +582,68 @@ def run_step_workload(args, wl):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=4000)
-    ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
-    if args.impl == "reference":
-        return run_reference_arm(args, wl, args.workload)
-    if "step" in wl:
-        return run_step_workload(args, wl)
+DTYPE_NOTE = {
+    "gemv": "f32 accumulate; activations rounded to 15-bit block fixed point (two int8 digits per group of 32), "
+            "integer-exact group sums over u4/i8 codes",
+    "decode": "f32 accumulate; activations rounded to 15-bit block fixed point, integer mma.sync over u4/i8 codes",
+    "tensor4": "f32 accumulate (TMEM) over bf16 activations and bf16 de-quantised u4 weights",
+    "tensor8": "f32 accumulate (TMEM) over f16 activations and f16 de-quantised i8 weights",
+    "generic": "f32 sequential accumulate over u4/i8 codes",
+}
 
+
+def parity_window(D, O, kind, M, K, Nl, a_dev, pack, read_out, c0=None, width=48):
+    """Compares columns [c0, c0 + width) of one product with the CPU oracle (same f32 activations, the
+    packed bytes of those columns brought back from the device).  Returns worst err / bound, where
+    bound = 1e-3 * ||a_m|| * ||w_deq[:, n]||."""
+    import numpy as np
+    bb = 24 if kind == 4 else 34
+    G = K // 32
+    c0 = ((Nl // 2) // 8 * 8) if c0 is None else c0
+    c1 = min(Nl, c0 + width)
+    cols = np.empty((G, (c1 - c0) * bb), np.uint8)
+    for g in range(G):
+        cols[g] = D.download(pack, (c1 - c0) * bb, np.uint8, offset=(g * Nl + c0) * bb)
+    cols = cols.reshape(-1)
+    a = D.download(a_dev, M * K * 4, np.float32).reshape(M, K)
+    knd = "q4" if kind == 4 else "q8"
+    want = O.matmul(a, cols, K, c1 - c0, knd, threads=O.host_threads())
+    got = read_out(c0, c1)
+    bound = O.tolerance_bound(a, O.dequant(cols, K, c1 - c0, knd), 1e-3)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    return float((err / np.maximum(bound, 1e-300)).max())
+
+
+def settle_steps(step_s, world, torch, dist):
+    """How many untimed steps make about a quarter of a second of load before the timed region, so
+    that the clock samples (one per 100 ms) are taken under load even when the timed region is short."""
+    n = int(min(20000, max(0, 0.25 / max(step_s, 1e-7))))
+    if world > 1:
+        t = torch.tensor([n], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        n = int(t.item())
+    return n
+
+
+def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, with_e2e=True, sampler_on=True):
+    """One workload of R products of one shape; returns the JSON line as a dict (rank 0) or None."""
     import numpy as np
     import torch
     import torch.distributed as dist
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
     import smith_b200 as smith
+    from oracle import oracle as O
     from smith_b200 import device as D
     from smith_b200 import parallel as P
-
+    world, rank, local, stream = ctxinfo
     kind, M, K, N = wl["kind"], wl["M"], wl["K"], wl["N"]
-    warm = max(args.warmup, 3)
     bb = 24 if kind == 4 else 34
     G = K // 32
     n0, n1 = P.column_shard(N, world, rank)      # this rank's output columns
     Nl = n1 - n0
     wbytes_full = G * N * bb
     R = max(2, int(-(-4 * L2_BYTES // wbytes_full)))
-    D.ctx()
-    stream = torch.cuda.ExternalStream(D.stream())
+    if M <= 4:
+        R = max(R, 16)                           # a list of at least 16 products per step
 
     # ---- synthetic weights: generated and packed on the device, shard by shard
     wtmp = D.alloc(K * Nl * 4, D.PRIVATE)
@@ -478,9 +663,12 @@ def main():
         fused = M <= 4 and all(D.qgemvTiles(kind, M, b - a, K) > 0
                                for a, b in (P.column_shard(N, world, r) for r in range(world)))
         gather = P.FusedGather(M, N, world, rank, deferred=True) if fused else P.OutputGather(M, N, world, rank)
-    c_dev = D.alloc(M * Nl * 4, D.PRIVATE) if (not gather or fused) else gather.local_buf
+    use_list = world == 1 and M <= 4 and D.qmatmulListSupports(kind, M, Nl, K) and not args.no_list
+    outs = [D.alloc(M * Nl * 4, D.PRIVATE) for _ in range(R)] if use_list else []
+    c_dev = (outs[0] if use_list else D.alloc(M * Nl * 4, D.PRIVATE)) if (not gather or fused) else gather.local_buf
+    lst = D.qmatmulListCreate(kind, M, [D.listItem(a_dev, pk, c, Nl, K) for pk, c in zip(packs, outs)]) if use_list else None
 
-    def one_pass():
+    def launches_pass():
         for pk in packs:
             if fused:
                 gather.enqueue(kind, a_dev, pk, K)
@@ -491,21 +679,26 @@ def main():
         if fused:
             gather.finish()                       # the last launch's row is whole when the pass ends
 
-    one_pass()                                    # sizes scratch before capture
+    launches_pass()                               # sizes scratch before capture
     D.synchronize()
     if D.kernelStatus() != 0:
         raise SystemExit("a bounded device-side wait gave up during warm-up")
     graph = None
     if not gather or gather.capturable:
         D.graphBegin()
-        one_pass()
+        launches_pass()
         graph = D.graphEnd()
 
-    def step():
+    def per_call_step():
         if graph:
             D.graphLaunch(graph)
         else:
-            one_pass()
+            launches_pass()
+
+    def list_step():
+        D.qmatmulListRun(lst)
+
+    step = list_step if use_list else per_call_step
 
     def barrier():
         D.synchronize()
@@ -513,71 +706,126 @@ def main():
         if world > 1:
             dist.barrier()
 
+    # ---- parity before timing: a column window of the last product of a step against the oracle
+    step()
+    barrier()
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up")
+    parity = None
+    if rank == 0:
+        if gather and fused:
+            # the gathered row (all ranks' slices): this rank's window lies inside its own slice
+            row = gather.read((gather.calls - 1) & 1)
+            worst = parity_window(D, O, kind, M, K, Nl, a_dev, packs[-1], lambda c0, c1: row[:, n0 + c0:n0 + c1])
+            whole = bool(np.all(np.isfinite(row)))
+        elif gather:
+            row = gather.full.cpu().numpy()
+            worst = parity_window(D, O, kind, M, K, Nl, a_dev, packs[-1], lambda c0, c1: row[:, n0 + c0:n0 + c1])
+            whole = bool(np.all(np.isfinite(row)))
+        else:
+            last = outs[-1] if use_list else c_dev
+            full = D.download(last, M * Nl * 4, np.float32).reshape(M, Nl)
+            worst = parity_window(D, O, kind, M, K, Nl, a_dev, packs[-1], lambda c0, c1: full[:, c0:c1])
+            whole = bool(np.all(np.isfinite(full)))
+        parity = {"checked": True, "worst_err_over_bound": worst, "ok": bool(worst <= 1.0 and whole),
+                  "what": "48 columns of the last product of a step"
+                          + (" (read from the gathered row)" if gather else "") + " against the CPU oracle; "
+                          "bound = 1e-3 * ||a_m|| * ||w_deq[:,n]||"}
+        if not parity["ok"]:
+            raise SystemExit(f"parity check failed before timing: {parity}")
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     for _ in range(warm):
         step()
     barrier()
+    est = timed(step, 3) / 3 * 1e-3
     sampler = ClockSampler(local)
-    if rank == 0:
+    if rank == 0 and sampler_on:
         sampler.start()
-    launches0 = D.launchCount()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
+    settle = settle_steps(est, world, torch, dist)
+    for _ in range(settle):
         step()
-    e1.record(stream)
     barrier()
-    ms = e0.elapsed_time(e1)
-    launches_value = (D.launchCount() - launches0) or (args.steps * R * (2 if gather else 1))
-    if graph:
-        launches_value = args.steps * R * ((1 + gather.kernels_per_call) if gather else 1)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    launches0 = D.launchCount()
+    ms = timed(step, steps)
+    launches_value = D.launchCount() - launches0
+    if not use_list and graph:
+        launches_value = steps * R * ((1 + gather.kernels_per_call) if gather else 1)
+    # the same products as one launch each (graph replay), for comparison with the list form
+    per_call = None
+    if use_list:
+        for _ in range(3):
+            per_call_step()
+        barrier()
+        n_pc = max(3, min(steps, 200))
+        ms_pc = timed(per_call_step, n_pc)
+        launches_value += (3 + n_pc) * R
+        pc_s = ms_pc * 1e-3 / (n_pc * R)
+        per_call = {"us_per_matmul": pc_s * 1e6, "value": metric_of(kind, M, K, N, pc_s)[0],
+                    "note": "the same R products as R launches replayed from one CUDA graph"}
 
     # ---- end to end through the operator API, host-resident activations and outputs
-    a_host = smith.tensorFrom(D.download(a_dev, M * K * 4, np.float32), [M, K])
-    wqs = [smith.ops.quantize.Quantized(buffer=pk, K=K, N=Nl, groups=G, totalBytes=G * Nl * bb) for pk in packs]
-    mm = smith.matmulQ4 if kind == 4 else smith.matmulQ8
+    e2e = None
+    launches_e2e = 0
+    if with_e2e:
+        a_host = smith.tensorFrom(D.download(a_dev, M * K * 4, np.float32), [M, K])
+        wqs = [smith.ops.quantize.Quantized(buffer=pk, K=K, N=Nl, groups=G, totalBytes=G * Nl * bb) for pk in packs]
+        mm = smith.matmulQ4 if kind == 4 else smith.matmulQ8
+        sharded = [P.ShardedMatmul(kind, K, N, pk, M, world, rank) for pk in packs] if world > 1 else None
+        a_np = smith.toNumpy(a_host)
 
-    sharded = [P.ShardedMatmul(kind, K, N, pk, M, world, rank) for pk in packs] if world > 1 else None
-    a_np = smith.toNumpy(a_host)
+        def e2e_pass():
+            if sharded:                       # multi-GPU: upload, shard matmul, all-gather, download full rows
+                for sm in sharded:
+                    sm.forward(a_np)
+            else:                             # the reference's operator call
+                for wq in wqs:
+                    smith.dispose(mm(a_host, wq))
 
-    def e2e_pass():
-        if sharded:                       # multi-GPU: upload, shard matmul, all-gather, download full rows
-            for sm in sharded:
-                sm.forward(a_np)
-        else:                             # the reference's operator call
-            for wq in wqs:
-                smith.dispose(mm(a_host, wq))
-
-    for _ in range(2):
-        e2e_pass()
-    barrier()
-    launches1 = D.launchCount()
-    e2e_steps = max(3, min(args.steps, 100))
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_pass()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    launches_e2e = D.launchCount() - launches1
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
-
-    status = D.kernelStatus()
-    if status != 0:
+        for _ in range(2):
+            e2e_pass()
+        barrier()
+        launches1 = D.launchCount()
+        e2e_steps = max(3, min(steps, 100))
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_pass()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        launches_e2e = D.launchCount() - launches1
+        if world > 1:
+            t = torch.tensor([e2e_s], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e_value, e2e_unit = metric_of(kind, M, K, N, e2e_s / (e2e_steps * R))
+        e2e = {"value": e2e_value, "unit": e2e_unit, "h2d_bytes_per_step": R * 4 * M * K * world,
+               "d2h_bytes_per_step": R * 4 * M * (N if world > 1 else Nl) * world, "steps": e2e_steps,
+               "us_per_call": e2e_s / (e2e_steps * R) * 1e6,
+               "note": "operator API per call (matmulQ4 / matmulQ8 on host tensors): H2D activations from page-locked "
+                       "memory, kernel, D2H result, wait"}
+    clocks = sampler.stop() if (rank == 0 and sampler_on) else None
+    if D.kernelStatus() != 0:
         raise SystemExit("a bounded device-side wait gave up: results invalid")
 
+    line = None
     if rank == 0:
-        per_launch_s = ms * 1e-3 / (args.steps * R)
+        per_launch_s = ms * 1e-3 / (steps * R)         # per product
         value, unit = metric_of(kind, M, K, N, per_launch_s)
-        e2e_value, _ = metric_of(kind, M, K, N, e2e_s / (e2e_steps * R))
         peaks = measured_peaks()
-        nbytes_l, flops_l = algorithmic(kind, M, K, Nl)       # what this rank's kernel moves per launch
+        nbytes_l, flops_l = algorithmic(kind, M, K, Nl)       # what this rank's kernel moves per product
         sustained = False
         if M <= 64:
             ach, peak, runit, bound = nbytes_l / per_launch_s / 1e9, peaks["hbm"], "GB/s", "hbm"
@@ -587,41 +835,120 @@ def main():
             sustained = ms > 100.0
             ach, peak, runit, bound = (flops_l / per_launch_s / 1e12,
                                        peaks["tensor_sustained"] if sustained else peaks["tensor"], "TFLOP/s", "tensor")
-        path = {0: "auto", 1: "generic", 2: "decode_mma", 3: "tensor_tcgen05", 4: "gemv_dp4a"}[D.qmatmulPath(kind, M, Nl, K)]
+        pid = D.qmatmulPath(kind, M, Nl, K)
+        path = {0: "auto", 1: "generic", 2: "decode_mma", 3: "tensor_tcgen05", 4: "gemv_dp4a"}[pid]
+        dtype = DTYPE_NOTE[{1: "generic", 2: "decode", 3: "tensor4" if kind == 4 else "tensor8", 4: "gemv"}.get(pid, "generic")]
+        per_kernel = R if use_list else 1                        # products one launch of the dominant kernel covers
         line = {
-            "metric": metric_name(M), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32 accumulate over u4/i8 codes" if kind == 4 else "f32 accumulate over i8 codes",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "kind": f"q{kind}", "M": M, "K": K, "N": N,
-                       "launches_per_step": R, "kernel": path,
+            "metric": metric_name(M), "value": value, "unit": unit, "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": name, "kind": f"q{kind}", "M": M, "K": K, "N": N,
+                       "products_per_step": R, "launches_per_step": 1 if use_list else R,
+                       "form": ("list: the R products of a step run as ONE persistent launch (smith_qmatmul_list), "
+                                "the ring of weight stages never drains between matrices") if use_list
+                               else "one launch per product, R launches replayed from one CUDA graph",
+                       "kernel": ("gemv_list_dp4a" if use_list else path), "per_call": per_call,
                        "sharding": (f"N-sharded over {world} GPU(s), all-gather of outputs "
                                     + ("fused into the GEMV kernel (peer stores over NVLink; each launch waits for its predecessor's tiles after its own weight stream has started, a final wait closes the step)" if fused else "by NCCL"))
                        if world > 1 else "single GPU",
                        "l2": f"defeated by rotating over {R} distinct packed matrices per step "
                              f"({R * wbytes_full / 1e6:.0f} MB > 4 x 126 MB L2)",
-                       "timing": "CUDA events on the launch stream around a replayed CUDA graph, max over ranks"},
-            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": R * 4 * M * K * world,
-                    "d2h_bytes_per_step": R * 4 * M * (N if world > 1 else Nl) * world, "steps": e2e_steps,
-                    "note": "operator API per call: H2D activations from page-locked memory, kernel, D2H result, wait"},
+                       "settle_steps": settle,
+                       "timing": "CUDA events on the launch stream around the timed steps, max over ranks; "
+                                 "settle_steps untimed steps run just before, so the clock samples see load"},
+            "parity": parity,
+            "e2e": e2e,
             "gpu_launches": int(launches_value + launches_e2e),
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": runit, "frac": ach / peak,
-                         "traffic": traffic_for(args.workload) if world == 1 else None,
+                         "traffic": (traffic_for(name + ("#list" if use_list else "")) if world == 1 else None),
                          "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
                          else "fallback (no MEASURED_PEAKS.json)",
                          "peak_kind": ("copy bandwidth" if bound == "hbm" else
                                        ("sustained cuBLAS bf16 (timed region %.0f ms)" % ms if sustained
                                         else "burst cuBLAS bf16 (timed region %.0f ms)" % ms)),
                          "frac_of_nominal": ach / (8000.0 if bound == "hbm" else 2250.0),
-                         "algorithmic_per_launch": nbytes_l if bound == "hbm" else flops_l},
+                         "algorithmic_per_launch": (nbytes_l if bound == "hbm" else flops_l) * per_kernel,
+                         "launch_us": per_launch_s * per_kernel * 1e6},
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu:
-            per_call, threads, ckind, sample = cpu_run(kind, M, K, N, seconds=args.cpu_seconds)
-            cv, cu = metric_of(kind, M, K, N, per_call)
+        if world == 1 and with_cpu and not args.no_cpu:
+            per_call_cpu, threads, ckind, sample = cpu_run(kind, M, K, N, seconds=args.cpu_seconds)
+            cv, cu = metric_of(kind, M, K, N, per_call_cpu)
             line["cpu_baseline"] = {"value": cv, "unit": cu, "cores": threads, "kind": ckind, "sample": sample}
         else:
             line["cpu_baseline"] = None
+    # ---- give the memory back (secondary workloads follow in the same process)
+    if lst:
+        D.qmatmulListDestroy(lst)
+    if graph:
+        D.graphDestroy(graph)
+    for b in packs + outs + [a_dev] + ([] if (use_list or (gather and not fused)) else [c_dev]):
+        D.releaseBuffer(b)
+    return line
+
+
+SECONDARY = ["q4_prefill_4096x14336_m512", "q8_prefill_gemm_4096x11008_m512", "q4_gemv_4096x4096_m1"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-list", action="store_true", help="time one launch per product instead of the list form")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads of the default run")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference_arm(args, wl, args.workload)
+    if "step" in wl:
+        return run_step_workload(args, wl)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from smith_b200 import device as D
+    D.ctx()
+    stream = torch.cuda.ExternalStream(D.stream())
+    ctxinfo = (world, rank, local, stream)
+    warm = max(args.warmup, 3)
+    line = run_matrix_workload(args, args.workload, wl, args.steps, warm, ctxinfo)
+    # The default single-GPU run also times, in the same process, the shapes the other stated targets
+    # are quoted on (short runs: they are records, the headline is the line's own value).
+    if world == 1 and args.workload == DEFAULT and not args.no_secondary and line is not None:
+        sec = []
+        for nm in SECONDARY:
+            w2 = WORKLOADS[nm]
+            st2 = 20 if w2["M"] > 64 else 300
+            l2 = run_matrix_workload(args, nm, w2, st2, 5, ctxinfo, with_cpu=False, with_e2e=False, sampler_on=True)
+            sec.append({"workload": nm, "value": l2["value"], "unit": l2["unit"], "steps": st2,
+                        "us_per_product": l2["roofline"]["launch_us"] / (l2["config"]["products_per_step"]
+                                                                          if l2["config"]["launches_per_step"] == 1
+                                                                          and l2["config"]["products_per_step"] > 1
+                                                                          and l2["config"]["kernel"] == "gemv_list_dp4a" else 1),
+                        "form": "list" if l2["config"]["kernel"] == "gemv_list_dp4a" else "one launch per product",
+                        "kernel": l2["config"]["kernel"], "per_call": l2["config"]["per_call"],
+                        "roofline": {k: l2["roofline"][k] for k in ("bound", "achieved", "peak", "unit", "frac",
+                                                                     "frac_of_nominal", "peak_kind")},
+                        "frac_of_sustained_peak": (l2["roofline"]["achieved"] / measured_peaks()["tensor_sustained"]
+                                                   if l2["roofline"]["bound"] == "tensor" else None),
+                        "parity": l2["parity"], "clocks": l2["clocks"]})
+        line["secondary"] = sec
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -211,6 +211,29 @@ typedef struct SmithListItem {
 void* smith_qmatmul_list_create(void* ctx, uint32_t kind, uint64_t M, const SmithListItem* items, uint32_t count);
 int32_t smith_qmatmul_list_run(void* ctx, void* list);
 void smith_qmatmul_list_destroy(void* list);
+/* The same list with weights sharded along N over the GPUs of one box (one process per GPU): gathers[i]
+ * (world != 0) makes item i end in a fused all-gather.  The item's N columns are then columns
+ * [n0, n0 + N) of a row of n_total, and its threads store them, besides c, into EVERY rank's row buffer
+ * rows[r] (local, or another process's buffer opened with smith_ipc_import): one 8-byte store
+ * {value bits, launch tag} per element and rank, plain stores over NVLink, no fence -- a reader accepts a
+ * pair by its tag.  A row buffer holds 2 * M * n_total such pairs (zero-initialised once); launch number
+ * t (1, 2, ...; smith_qmatmul_list_next_tag) fills half t % 2, where pair m * n_total + col holds element
+ * (m, col) of the gathered row.  Before the launch ends, every rank waits -- bounded, ~0.2 s, reported by
+ * smith_kernel_status -- until its own row buffers are whole, unless SMITH_LIST_NO_CLOSING_WAIT is given;
+ * that wait also keeps the ranks within one launch of each other, which is what lets the halves
+ * alternate.  Every rank must create the same list (its own shards) and run it the same number of times. */
+typedef struct SmithListGather {
+  uint32_t world;            /* 0: item i is not gathered */
+  uint32_t reserved;
+  uint64_t n0, n_total;
+  void* rows[8];             /* rank r's row buffer (a buffer handle) */
+} SmithListGather;
+#define SMITH_LIST_NO_CLOSING_WAIT 1u
+void* smith_qmatmul_list_create_gather(void* ctx, uint32_t kind, uint64_t M, const SmithListItem* items,
+                                       const SmithListGather* gathers, uint32_t count, uint32_t rank, uint32_t flags);
+/* Tag the next launch of the list will use (the last finished launch used one less); 0 on error.
+ * Synchronises the device. */
+uint32_t smith_qmatmul_list_next_tag(void* list);
 /* 1 if an item of this shape can be part of a list. */
 int32_t smith_qmatmul_list_supports(uint32_t kind, uint64_t M, uint64_t N, uint64_t K);
 /* Device-side waits in these kernels (on a shared-memory barrier, a peer's

@@ -868,6 +868,11 @@ const uint8_t* list_operand(void* handle, uint64_t offset, uint64_t bytes, uint3
 }  // namespace
 
 void* smith_qmatmul_list_create(void* p, uint32_t kind, uint64_t M, const SmithListItem* items, uint32_t count) {
+  return smith_qmatmul_list_create_gather(p, kind, M, items, nullptr, count, 0, 0);
+}
+
+void* smith_qmatmul_list_create_gather(void* p, uint32_t kind, uint64_t M, const SmithListItem* items,
+                                       const SmithListGather* gathers, uint32_t count, uint32_t rank, uint32_t flags) {
   Context* c = as_ctx(p);
   if (!c) return nullptr;
   if (!items || count == 0) {
@@ -903,9 +908,23 @@ void* smith_qmatmul_list_create(void* p, uint32_t kind, uint64_t M, const SmithL
     if (it.residual && !(d.residual = reinterpret_cast<const float*>(
                              list_operand(it.residual, it.residual_offset, M * it.N * 4, i, "residual"))))
       return nullptr;
+    d.g_world = 0, d.g_n0 = 0, d.g_n_total = 0;
+    if (gathers && gathers[i].world) {
+      const SmithListGather& g = gathers[i];
+      if (g.world > 8) {
+        fail("smith_qmatmul_list_create_gather: item %u: world %u out of range", i, g.world);
+        return nullptr;
+      }
+      d.g_world = (int)g.world, d.g_n0 = (int64_t)g.n0, d.g_n_total = (int64_t)g.n_total;
+      for (uint32_t r = 0; r < g.world; r++) {
+        const uint8_t* row = list_operand(g.rows[r], 0, 2 * M * g.n_total * 8, i, "gather row buffer");
+        if (!row) return nullptr;
+        d.g_rows[r] = const_cast<uint8_t*>(row);
+      }
+    }
   }
   const char* why = "";
-  ListProgram* prog = qgemv_list_create((int)kind, (int64_t)M, descs.data(), (int)count, &why);
+  ListProgram* prog = qgemv_list_create((int)kind, (int64_t)M, descs.data(), (int)count, (int)rank, flags, &why);
   if (!prog) {
     fail("smith_qmatmul_list_create: %s", why);
     return nullptr;
@@ -937,6 +956,14 @@ void smith_qmatmul_list_destroy(void* list) {
   qgemv_list_destroy(h->prog);
   h->magic = 0;
   delete h;
+}
+
+uint32_t smith_qmatmul_list_next_tag(void* list) {
+  ListHandle* h = static_cast<ListHandle*>(list);
+  if (!h || h->magic != 0x534D4C53) return 0;
+  Context* c = as_ctx(h->ctx);
+  if (!c) return 0;
+  return qgemv_list_next_tag(h->prog);
 }
 
 int32_t smith_qmatmul_list_supports(uint32_t kind, uint64_t M, uint64_t N, uint64_t K) {
@@ -1017,6 +1044,9 @@ int32_t smith_allgather_wait(void* p, void* state_buf, void* y_buf, uint64_t M, 
   Context* c = as_ctx(p);
   Buffer *bs = as_buf(state_buf), *by = as_buf(y_buf);
   if (!c || !bs || !by) return 1;
+  if (M < 1 || M > 4 || (n_total % 8) != 0 || 2 * M * n_total > 0x7FFFFFFFull)
+    return fail("smith_allgather_wait: M = %llu, n_total = %llu: rows are read as 16-byte pairs of pairs, so n_total must be a "
+                "multiple of 8, M at most 4 and 2 * M * n_total below 2^31", (unsigned long long)M, (unsigned long long)n_total);
   if (!bs->dev || bs->bytes < 16 || !by->dev || by->bytes < 2 * M * n_total * 8)
     return fail("smith_allgather_wait: not the state and row buffers of a deferred all-gather of %llu x %llu",
                 (unsigned long long)M, (unsigned long long)n_total);
@@ -1033,6 +1063,10 @@ int32_t smith_qmatmul_allgather_ex(void* p, uint32_t kind, void* a, void* b, uin
   if (kind != 4 && kind != 8) return fail("kind must be 4 or 8, got %u", kind);
   if (world < 1 || world > 8 || rank >= world) return fail("smith_qmatmul_allgather: world %u / rank %u out of range", world, rank);
   if (!y_bufs || !state_bufs) return fail("smith_qmatmul_allgather: null buffer lists");
+  // The device code reads and writes the gathered rows with 16-byte accesses and 32-bit element counts.
+  if ((n_total % 8) != 0 || (n0 % 8) != 0 || 2 * M * n_total > 0x7FFFFFFFull)
+    return fail("smith_qmatmul_allgather: n_total = %llu and n0 = %llu must be multiples of 8 and 2 * M * n_total below 2^31",
+                (unsigned long long)n_total, (unsigned long long)n0);
   if (n0 + n_local > n_total) return fail("smith_qmatmul_allgather: slice [%llu, %llu) outside a row of %llu",
                                           (unsigned long long)n0, (unsigned long long)(n0 + n_local),
                                           (unsigned long long)n_total);
@@ -1077,7 +1111,7 @@ int32_t smith_qmatmul_allreduce(void* p, uint32_t kind, void* a, void* b, void* 
   if (!qgemv_supports((int)kind, M, N, k_local, groups_local))
     return fail("fused all-reduce is built into the GEMV kernel only (M <= 4, N %% 8 == 0, K %% 32 == 0); M=%llu N=%llu K=%llu",
                 (unsigned long long)M, (unsigned long long)N, (unsigned long long)k_local);
-  const int tiles = qgemv_tiles((int)kind, M, N, k_local);
+  if (2 * (uint64_t)world * M * N > 0x7FFFFFFFull) return fail("smith_qmatmul_allreduce: 2 * world * M * N must stay below 2^31");
   GemvGather g{};
   g.world = (int)world, g.rank = (int)rank, g.n0 = 0, g.n_total = (int64_t)N, g.target = 0, g.reduce = 1;
   for (uint32_t r = 0; r < world; r++) {
@@ -1088,16 +1122,14 @@ int32_t smith_qmatmul_allreduce(void* p, uint32_t kind, void* a, void* b, void* 
     g.y[r] = (float*)by->dev;
     g.state[r] = (unsigned*)bs->dev;
   }
-  (void)tiles;
   cudaError_t e = launch_qgemv_gather((int)kind, (const float*)ba->dev, (const uint8_t*)bb->dev, (float*)bo->dev, M, N,
                                       k_local, groups_local, &g, c->stream);
   return e == cudaSuccess ? 0 : fail("fused GEMV + all-reduce launch failed: %s", cudaGetErrorString(e));
 }
 
 uint64_t smith_qmatmul_allreduce_state_bytes(uint32_t kind, uint64_t M, uint64_t N, uint64_t k_local) {
-  const int tiles = qgemv_tiles((int)kind, M, N, k_local);
-  if (tiles < 0) return 0;
-  return 16;                                      // control words {step, ticket}
+  // 16 bytes (the control words {step, ticket}) for every shape the fused form takes, 0 for the others
+  return qgemv_supports((int)kind, (int64_t)M, (int64_t)N, (int64_t)k_local, (int64_t)(k_local / 32)) ? 16 : 0;
 }
 
 // ---------------------------------------------------------------- graphs

@@ -94,12 +94,23 @@ struct ListItemDesc {
   const float* residual;   // null, or f32 [M, N] added to the product (may be C)
   int64_t N, K;
   float eps;               // RMSNorm epsilon
+  // Fused all-gather of the output over peer memory (g_world == 0: none): this rank's N columns are
+  // columns [g_n0, g_n0 + N) of a row of g_n_total; g_rows[r] is rank r's row buffer of
+  // 2 * M * g_n_total {value, launch tag} pairs (zero-initialised once, local or peer-mapped).
+  int g_world;
+  int64_t g_n0, g_n_total;
+  void* g_rows[8];
 };
+// qgemv_list_create flags
+constexpr unsigned kListNoClosingWait = 1u;   // do not wait, before the launch ends, for the gathered rows to be whole
 struct ListProgram;
 bool qgemv_list_supports(int kind, int64_t M, int64_t N, int64_t K);
 // Plans the list for the current device and uploads it (allocates device memory).  nullptr with
 // *why set on failure.
-ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, int count, const char** why);
+ListProgram* qgemv_list_create(int kind, int64_t M, const ListItemDesc* items, int count, int rank, unsigned flags,
+                               const char** why);
+// Tag of the next launch of the list (tags start at 1; reads device memory, synchronises the device).
+unsigned qgemv_list_next_tag(const ListProgram* lp);
 cudaError_t qgemv_list_launch(const ListProgram* lp, cudaStream_t s);
 void qgemv_list_destroy(ListProgram* lp);
 size_t list_device_bytes(const ListProgram* lp);
@@ -111,6 +122,15 @@ cudaError_t launch_qgemm_tc_static(int kind, const float* A, const uint8_t* B, f
                                    int64_t K, int64_t groups, cudaStream_t s, const char** why);
 
 // util.cu
+// Number of SMs of the current device (cached per device; 148 if the query fails).
+int device_sm_count();
+// Per-device "this kernel's attributes are set" flags: function attributes such as the dynamic
+// shared-memory limit belong to a device, so a flag per process would leave the second device of a
+// process unconfigured.  Returns the slot for the current device (nullptr on error).
+struct PerDeviceFlag {
+  bool done[64] = {false};
+  bool* here();
+};
 // 1 if a bounded device-side wait gave up since the last call (then clears it), 0 if not, -1 on error.
 int kernel_take_status();
 // Device address of that status word on the current device (nullptr on error).

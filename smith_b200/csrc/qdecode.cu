@@ -396,7 +396,7 @@ constexpr int kMaxRows = 32;   // rows beyond this go to the tensor-core kernel
 
 Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
   const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
-  const int sms = 148;
+  const int sms = device_sm_count();
   Plan pl{};
   Params& p = pl.p;
   p.M = (int)M, p.N = (int)N, p.K = (int)K, p.G = (int)(K / 32);
@@ -454,12 +454,14 @@ cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t sm
 
 template <int KIND, int NT>
 cudaError_t launch_main(const Plan& pl, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceFlag configured;              // the attribute belongs to a device, not to the process
+  bool* set = configured.here();
+  if (!set) return cudaErrorInvalidDevice;
+  if (!*set) {
     cudaError_t e = cudaFuncSetAttribute(qdecode_kernel<KIND, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
-    configured = true;
+    *set = true;
   }
   const int threads = (pl.p.NS * pl.p.phases + 1) * 32;
   const cudaError_t e = launch_pdl(qdecode_kernel<KIND, NT>, dim3((unsigned)pl.tiles), dim3((unsigned)threads),

@@ -603,16 +603,17 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
   const int64_t mtiles = (M + pl.MT * kBM - 1) / (pl.MT * kBM);
   // Column tile: the multiple of 16 in [16, 256] that wastes the least of the
   // machine (partial last tile x partial last wave); wider wins ties.
+  const int64_t sms = device_sm_count();
   double best = -1.0;
   int bestBN = 128;
   for (int bn = 256; bn >= 16; bn -= 16) {
     const int64_t nt = (N + bn - 1) / bn;
     if (nt > 65535) continue;                                  // grid.y
     const int64_t ctas = nt * mtiles;
-    const int64_t waves = (ctas + 147) / 148;
+    const int64_t waves = (ctas + sms - 1) / sms;
     // useful fraction of the tiles x fill of the last wave x a mild preference for wide MMAs
     // (narrow tiles re-read the activations more often and amortise the dequantised tile less)
-    const double eff = ((double)N / (double)(nt * bn)) * ((double)ctas / (double)(waves * 148)) *
+    const double eff = ((double)N / (double)(nt * bn)) * ((double)ctas / (double)(waves * sms)) *
                        ((double)bn / (double)(bn + 48));
     if (eff > best + 1e-9) best = eff, bestBN = bn;
   }
@@ -664,12 +665,14 @@ Plan make_plan(int kind, int64_t M, int64_t N) {
 
 template <int KIND, int MT>
 cudaError_t launch_main(const CUtensorMap& map, const Params& p, const Plan& pl, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceFlag configured;              // the attribute belongs to a device, not to the process
+  bool* set = configured.here();
+  if (!set) return cudaErrorInvalidDevice;
+  if (!*set) {
     cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
-    configured = true;
+    *set = true;
   }
   // Programmatic dependent launch: CTAs start as SMs come free while the activation conversion is
   // still running; their weight pipeline fills meanwhile.

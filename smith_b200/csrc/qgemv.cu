@@ -505,7 +505,7 @@ struct Plan {
 
 Plan make_plan(int kind, int64_t M, const int64_t* Ns, int count, int64_t K) {
   const int BB = (kind == 4) ? kQ4Bytes : kQ8Bytes;
-  const int sms = 148;
+  const int sms = device_sm_count();
   Plan pl{};
   Params& p = pl.p;
   const int MR = (int)M;
@@ -603,12 +603,14 @@ void make_tensor_maps(Plan& pl, int kind, TensorMaps& tm) {
 
 template <int KIND, int MR, int RPP, bool COLL, bool WIDE>
 cudaError_t launch_one_mode(Plan& pl, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceFlag configured;              // the attribute belongs to a device, not to the process
+  bool* set = configured.here();
+  if (!set) return cudaErrorInvalidDevice;
+  if (!*set) {
     cudaError_t e =
         cudaFuncSetAttribute(qgemv_kernel<KIND, MR, RPP, COLL, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    configured = true;
+    *set = true;
   }
   const int threads = ((pl.p.nthreads + 31) / 32) * 32 + 32;
   cudaLaunchConfig_t cfg = {};

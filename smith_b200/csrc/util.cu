@@ -22,6 +22,27 @@ int* kernel_status_ptr() {
   return ptrs[dev];
 }
 
+int device_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!sms[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      return 148;
+    }
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+bool* PerDeviceFlag::here() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return &done[dev];
+}
+
 // Reads and clears the "a bounded device-side wait gave up" word of the current device.
 int kernel_take_status() {
   int v = 0, zero = 0;
@@ -67,14 +88,14 @@ __global__ void fill_bytes_kernel(uint4* __restrict__ out, size_t n16, uint32_t 
 
 cudaError_t launch_fill_normal(float* out, uint64_t count, uint64_t seed, float std, cudaStream_t s) {
   if (count == 0) return cudaSuccess;
-  fill_normal_kernel<<<148 * 8, 256, 0, s>>>(out, count, seed, std);
+  fill_normal_kernel<<<device_sm_count() * 8, 256, 0, s>>>(out, count, seed, std);
   count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_fill_bytes(void* out, size_t bytes, uint32_t value, cudaStream_t s) {
   if (bytes < 16) return cudaSuccess;
-  fill_bytes_kernel<<<148 * 4, 256, 0, s>>>(reinterpret_cast<uint4*>(out), bytes / 16, value);
+  fill_bytes_kernel<<<device_sm_count() * 4, 256, 0, s>>>(reinterpret_cast<uint4*>(out), bytes / 16, value);
   count_launch();
   return cudaGetLastError();
 }

@@ -43,6 +43,11 @@ class SmithListItem(C.Structure):
                 ("N", _u64), ("K", _u64), ("eps", C.c_float), ("reserved", _u32)]
 
 
+class SmithListGather(C.Structure):
+    """include/smith_cuda_bridge.h: the fused all-gather of one item of a list."""
+    _fields_ = [("world", _u32), ("reserved", _u32), ("n0", _u64), ("n_total", _u64), ("rows", _p * 8)]
+
+
 # name -> (restype, argtypes).  Part 1 is the table of src/device.js:10-50.
 SYMBOLS = {
     "smith_init": (_p, []),
@@ -92,6 +97,9 @@ SYMBOLS = {
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_qmatmul_list_create": (_p, [_p, _u32, _u64, C.POINTER(SmithListItem), _u32]),
+    "smith_qmatmul_list_create_gather": (_p, [_p, _u32, _u64, C.POINTER(SmithListItem), C.POINTER(SmithListGather), _u32, _u32,
+                                              _u32]),
+    "smith_qmatmul_list_next_tag": (_u32, [_p]),
     "smith_qmatmul_list_run": (_i32, [_p, _p]),
     "smith_qmatmul_list_destroy": (None, [_p]),
     "smith_qmatmul_list_supports": (_i32, [_u32, _u64, _u64, _u64]),
@@ -460,6 +468,34 @@ def qmatmulListCreate(kind, M, items):
     if not h:
         _raise("qmatmul_list_create")
     return h
+
+
+LIST_NO_CLOSING_WAIT = 1
+
+
+def listGather(world, n0, nTotal, rowBuffers):
+    """The fused all-gather of one list item: its columns are [n0, n0 + N) of a row of nTotal."""
+    g = SmithListGather()
+    g.world, g.n0, g.n_total = world, n0, nTotal
+    for r in range(world):
+        g.rows[r] = rowBuffers[r]
+    return g
+
+
+def qmatmulListCreateGather(kind, M, items, gathers, rank, flags=0):
+    """A list whose items may end in a fused all-gather over peer memory (see the header);
+    gathers[i] is None for an item that is not gathered."""
+    n = len(items)
+    arr = (SmithListItem * n)(*items)
+    garr = (SmithListGather * n)(*[g if g is not None else SmithListGather() for g in gathers])
+    h = lib.smith_qmatmul_list_create_gather(ctx(), kind, M, arr, garr, n, rank, flags)
+    if not h:
+        _raise("qmatmul_list_create_gather")
+    return h
+
+
+def qmatmulListNextTag(handle):
+    return int(lib.smith_qmatmul_list_next_tag(handle))
 
 
 def qmatmulListRun(handle):

@@ -188,6 +188,74 @@ class FusedGather:
         self.ys = self.states = []
 
 
+class ShardedList:
+    """R products y_i = a @ dequant(W_i), every W_i sharded along N over the ranks, as ONE persistent
+    launch per rank (smith_qmatmul_list_create_gather): each rank walks its R column shards with its
+    ring of weight stages never draining, and every item's epilogue stores its columns, as
+    {value, launch tag} pairs, straight into every rank's gathered row over peer memory.  No NCCL call
+    and no per-matrix hand-off between the GPUs: the ranks only meet at the end of a launch, when each
+    waits (bounded) until its own rows are whole.
+
+    Owns one device buffer with this rank's R row buffers (2 x M x N pairs each, the halves alternate
+    with the launch number), exported to the other ranks through IPC, and the R local slices."""
+
+    def __init__(self, kind, M, K, N, packed_shards, world, rank, a_buf, group=None, closing_wait=True):
+        from . import device as D
+        self.kind, self.M, self.K, self.N, self.world, self.rank = kind, M, K, N, world, rank
+        self.R = len(packed_shards)
+        self.n0, n1 = column_shard(N, world, rank)
+        self.Nl = n1 - self.n0
+        self.row_bytes = 2 * M * N * 8
+        self.rows = D.alloc(self.R * self.row_bytes, D.PRIVATE)
+        D.upload(self.rows, np.zeros(self.R * self.row_bytes // 4, np.uint32))
+        self.local = [D.alloc(M * self.Nl * 4, D.PRIVATE) for _ in range(self.R)]
+        self.all_rows = [None] * world
+        self.all_rows[rank] = self.rows
+        if world > 1:
+            import torch.distributed as dist
+            handles = [None] * world
+            dist.all_gather_object(handles, D.ipcExport(self.rows), group=group)
+            for r in range(world):
+                if r != rank:
+                    self.all_rows[r] = D.ipcImport(handles[r], self.R * self.row_bytes)
+        # one view per (rank, item) of the ranks' row buffers
+        self.views = [[D.wrapDeviceMemory(D.devicePtr(self.all_rows[r]) + i * self.row_bytes, self.row_bytes)
+                       for r in range(world)] for i in range(self.R)]
+        items = [D.listItem(a_buf, pk, c, self.Nl, K) for pk, c in zip(packed_shards, self.local)]
+        gathers = [D.listGather(world, self.n0, N, self.views[i]) for i in range(self.R)]
+        self.handle = D.qmatmulListCreateGather(kind, M, items, gathers, rank,
+                                                0 if closing_wait else D.LIST_NO_CLOSING_WAIT)
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=group)     # everyone has mapped everyone before the first store
+
+    def run(self):
+        """Asynchronous: all R products on this rank's shards, gathered into every rank's rows."""
+        from . import device as D
+        D.qmatmulListRun(self.handle)
+
+    def read(self, i):
+        """Gathered row [M, N] of product i as the last finished launch left it (synchronises)."""
+        from . import device as D
+        half = (D.qmatmulListNextTag(self.handle) - 1) & 1
+        n = self.M * self.N
+        pairs = D.download(self.rows, n * 8, np.uint32, offset=i * self.row_bytes + half * n * 8).reshape(n, 2)
+        return np.ascontiguousarray(pairs[:, 0]).view(np.float32).reshape(self.M, self.N), pairs[:, 1]
+
+    def close(self):
+        from . import device as D
+        D.qmatmulListDestroy(self.handle)
+        for vs in self.views:
+            for v in vs:
+                D.releaseBuffer(v)
+        for r in range(self.world):
+            if r != self.rank and self.all_rows[r]:
+                D.releaseBuffer(self.all_rows[r])
+        for b in self.local + [self.rows]:
+            D.releaseBuffer(b)
+        self.views, self.all_rows, self.local = [], [], []
+
+
 class FusedReduce:
     """Sum over ranks of K-sharded partial products, formed by the GEMV kernel itself (M <= 4): every
     rank's kernel pushes its partial sums as {value, step tag} pairs into its slot on every rank

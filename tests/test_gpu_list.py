@@ -231,6 +231,14 @@ def test_list_decode_layers_with_fused_glue(kind, M, dim, kv, ffn, layers):
             b.free()
 
 
+def test_list_chain_through_channels(monkeypatch):
+    """The same chain with SMITH_LIST_CHANNELS set: read-after-write hazards then travel as tagged
+    {value, launch tag} pairs instead of through the counters (the mechanism the multi-GPU rows use)."""
+    monkeypatch.setenv("SMITH_LIST_CHANNELS", "1")
+    test_list_chain_reads_what_earlier_items_wrote(2)
+    test_list_decode_layers_with_fused_glue("q4", 1, 1024, 256, 2816, 3)
+
+
 def test_rmsnorm_prologue_alone_matches_oracle_to_rounding():
     """An identity-like check of the fused RMSNorm: with a one-hot-column weight the product is
     (code * scale) * normalised x[k], so the normalised row can be read back through the matmul."""
@@ -270,4 +278,124 @@ def test_list_refusals():
     assert device.qmatmulListSupports(4, 1, 14336, 4096)
     assert not device.qmatmulListSupports(4, 1, 14336, 4100)
     for b in (pb, ab, cb):
+        b.free()
+
+
+# ------------------------------------------------------------------ fused all-gather (weights sharded along N)
+def _shard(packed, K, N, bb, n0, n1):
+    from smith_b200 import parallel as P
+    return P.slice_packed_columns(packed, K // 32, N, bb, n0, n1)
+
+
+def test_list_gather_world_of_one_alternates_halves():
+    """A list whose items end in the fused all-gather, with this GPU as the only rank: the rows hold
+    {value, tag} pairs, launch t fills half t % 2 with tag t."""
+    from smith_b200 import parallel as P
+    rng = np.random.default_rng(21)
+    M, K, N, R = 2, 1024, 2048, 5
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    ab = DevBuf.of(a)
+    packed = [O.quantize_q4((rng.standard_normal((K, N)) * 0.02).astype(np.float32)) for _ in range(R)]
+    pbs = [DevBuf.of(p) for p in packed]
+    sl = P.ShardedList(4, M, K, N, [b.handle for b in pbs], 1, 0, ab.handle)
+    for launch in (1, 2, 3):
+        sl.run()
+        device.synchronize()
+        assert device.kernelStatus() == 0
+        for i in range(R):
+            row, tags = sl.read(i)
+            assert np.all(tags == launch)
+            ref = O.matmul(a, packed[i], K, N, "q4", threads=O.host_threads())
+            ok, worst = within_tolerance(row, ref, a, packed[i], K, N, "q4", REL)
+            assert ok, worst
+            # the plain local slice holds the same values
+            local = device.download(sl.local[i], M * N * 4, np.uint32)
+            assert np.array_equal(local, row.view(np.uint32).reshape(-1))
+    sl.close()
+    for b in pbs + [ab]:
+        b.free()
+
+
+def test_list_gather_two_shards_emulated_on_one_gpu():
+    """Two ranks' lists, both on this GPU and sharing the two 'ranks' row buffers, launched one after
+    the other (never two launches that wait on each other on one GPU: the closing wait is off)."""
+    from smith_b200 import parallel as P
+    rng = np.random.default_rng(22)
+    M, K, N, R, world = 1, 2048, 4096, 3, 2
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    ab = DevBuf.of(a)
+    packed = [O.quantize_q4((rng.standard_normal((K, N)) * 0.02).astype(np.float32)) for _ in range(R)]
+    row_bytes = 2 * M * N * 8
+    rows = [DevBuf.of(np.zeros(R * row_bytes // 4, np.uint32)) for _ in range(world)]
+    lists, keep = [], []
+    for rank in range(world):
+        n0, n1 = P.column_shard(N, world, rank)
+        shards = [DevBuf.of(_shard(p, K, N, 24, n0, n1)) for p in packed]
+        outs = [DevBuf((n1 - n0) * M * 4) for _ in range(R)]
+        views = [[device.wrapDeviceMemory(device.devicePtr(rows[r].handle) + i * row_bytes, row_bytes) for r in range(world)]
+                 for i in range(R)]
+        items = [device.listItem(ab.handle, sh.handle, o.handle, n1 - n0, K) for sh, o in zip(shards, outs)]
+        gathers = [device.listGather(world, n0, N, views[i]) for i in range(R)]
+        lists.append(device.qmatmulListCreateGather(4, M, items, gathers, rank, device.LIST_NO_CLOSING_WAIT))
+        keep += shards + outs
+    for launch in (1, 2):
+        for lst in lists:                              # rank 0's launch, then rank 1's
+            device.qmatmulListRun(lst)
+            device.synchronize()
+        assert device.kernelStatus() == 0
+        half = launch & 1
+        for r in range(world):                         # both ranks' rows are whole and equal
+            for i in range(R):
+                pairs = device.download(rows[r].handle, M * N * 8, np.uint32, offset=i * row_bytes + half * M * N * 8).reshape(-1, 2)
+                assert np.all(pairs[:, 1] == launch)
+                row = np.ascontiguousarray(pairs[:, 0]).view(np.float32).reshape(M, N)
+                ref = O.matmul(a, packed[i], K, N, "q4", threads=O.host_threads())
+                ok, worst = within_tolerance(row, ref, a, packed[i], K, N, "q4", REL)
+                assert ok, worst
+    for lst in lists:
+        device.qmatmulListDestroy(lst)
+    for b in keep + rows + [ab]:
+        b.free()
+
+
+def test_bounded_wait_gives_up_when_a_peer_never_arrives():
+    """Failure detection without any fault: a two-rank gather list whose peer never runs.  The closing
+    wait of the launch runs out (~0.2 s), the kernel returns by itself, smith_kernel_status reports 1,
+    and the context stays usable: an ordinary product afterwards is correct and the status is clear."""
+    import time
+    from smith_b200 import parallel as P
+    rng = np.random.default_rng(23)
+    M, K, N, world = 1, 1024, 2048, 2
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    packed = O.quantize_q4(w)
+    ab = DevBuf.of(a)
+    n0, n1 = P.column_shard(N, world, 0)
+    shard, out = DevBuf.of(_shard(packed, K, N, 24, n0, n1)), DevBuf(M * (n1 - n0) * 4)
+    rows = [DevBuf.of(np.zeros(2 * M * N * 2, np.uint32)) for _ in range(world)]    # the peer's slice stays empty
+    lst = device.qmatmulListCreateGather(4, M, [device.listItem(ab.handle, shard.handle, out.handle, n1 - n0, K)],
+                                         [device.listGather(world, n0, N, [r.handle for r in rows])], 0)
+    t0 = time.perf_counter()
+    device.qmatmulListRun(lst)
+    device.synchronize()
+    waited = time.perf_counter() - t0
+    assert device.kernelStatus() == 1, "the closing wait should have given up"
+    assert waited < 5.0
+    assert device.kernelStatus() == 0                   # reading the status clears it
+    # this rank's own slice did arrive (launch 1, half 1) and the plain output is right
+    pairs = device.download(rows[0].handle, M * N * 8, np.uint32, offset=M * N * 8).reshape(-1, 2)
+    assert np.all(pairs[n0:n1, 1] == 1) and np.all(pairs[n1:, 1] == 0)
+    ref = O.matmul(a, packed, K, N, "q4")
+    got = out.get(np.float32).reshape(M, n1 - n0)
+    ok, worst = within_tolerance(got, ref[:, n0:n1], a, _shard(packed, K, N, 24, n0, n1), K, n1 - n0, "q4", REL)
+    assert ok, worst
+    # an ordinary product on the same context afterwards
+    pb, cb = DevBuf.of(packed), DevBuf(M * N * 4)
+    device.qmatmul(4, ab.handle, pb.handle, cb.handle, M, N, K, K // 32, device.PATH_AUTO)
+    device.synchronize()
+    assert device.kernelStatus() == 0
+    ok, worst = within_tolerance(cb.get(np.float32).reshape(M, N), ref, a, packed, K, N, "q4", REL)
+    assert ok, worst
+    device.qmatmulListDestroy(lst)
+    for b in [ab, shard, out, pb, cb] + rows:
         b.free()
