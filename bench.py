@@ -104,7 +104,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -205,7 +205,7 @@ def run_reference_arm(args, wl, name):
 
 
 # ----------------------------------------------------------------------------- decode-step workload
-def run_step_list(args, wl):
+def run_step_list(args, wl, ctxinfo, name=None, steps=None, with_cpu=True):
     """One GPU, M <= 4: the whole decode step's projections as ONE persistent launch with the
     reference's pointwise glue folded in (src/gguf_cache.js:121-171): per layer
         q, k, v = rmsnorm(x, ln1) W{q,k,v};   x2 = x + attn Wo;
@@ -221,36 +221,42 @@ def run_step_list(args, wl):
     kind, M, st = wl["kind"], wl["M"], wl["step"]
     dim, kv, ffn, vocab, layers = st["dim"], st["kv"], st["ffn"], st["vocab"], st["layers"]
     bb, eps = 24, 1e-5
-    torch.cuda.set_device(0)
-    D.ctx()
-    stream = torch.cuda.ExternalStream(D.stream())
-    steps = min(args.steps, 200)
+    stream = ctxinfo[3]
+    name = name or args.workload
+    steps = steps or min(args.steps, 200)
     warm = max(min(args.warmup, 10), 3)
-    wtmp = D.alloc(max(dim * ffn, dim * vocab) * 4, D.PRIVATE)
+    owned = []                                        # every buffer made here, released before returning
+
+    def alloc(n):
+        b = D.alloc(n, D.PRIVATE)
+        owned.append(b)
+        return b
+
+    wtmp = alloc(max(dim * ffn, dim * vocab) * 4)
     seed = [17]
     weight_bytes, alg_bytes = [0], [0]
 
     def make(k, n):
         D.fillNormal(wtmp, k * n, seed[0], wl["std"])
         seed[0] += 1
-        pk = D.alloc((k // 32) * n * bb, D.PRIVATE)
+        pk = alloc((k // 32) * n * bb)
         D.q4Pack(wtmp, pk, k, n)
         weight_bytes[0] += (k // 32) * n * bb
         alg_bytes[0] += (k // 32) * n * bb + 4 * M * k + 4 * M * n
         return pk
 
     def vec(n, sd, value):
-        b = D.alloc(n * 4, D.PRIVATE)
+        b = alloc(n * 4)
         D.fillNormal(b, n, sd, 0.05)
         v = D.download(b, n * 4, np.float32) + value
         D.upload(b, v.astype(np.float32))
         return b
 
-    xs = [D.alloc(M * dim * 4, D.PRIVATE) for _ in range(2)]
-    x2, attn = D.alloc(M * dim * 4, D.PRIVATE), D.alloc(M * dim * 4, D.PRIVATE)
-    q, k_, v_, h = (D.alloc(M * n * 4, D.PRIVATE) for n in (dim, kv, kv, ffn))
-    logits = D.alloc(M * vocab * 4, D.PRIVATE)
-    x0 = D.alloc(M * dim * 4, D.PRIVATE)
+    xs = [alloc(M * dim * 4) for _ in range(2)]
+    x2, attn = alloc(M * dim * 4), alloc(M * dim * 4)
+    q, k_, v_, h = (alloc(M * n * 4) for n in (dim, kv, kv, ffn))
+    logits = alloc(M * vocab * 4)
+    x0 = alloc(M * dim * 4)
     D.fillNormal(x0, M * dim, 7, 1.0)
     D.fillNormal(attn, M * dim, 8, 1.0)
     items = []
@@ -268,7 +274,6 @@ def run_step_list(args, wl):
     head = make(dim, vocab)
     items.append(D.listItem(x_last, head, logits, vocab, dim, gamma=lnf, eps=eps))
     D.synchronize()
-    D.releaseBuffer(wtmp)
     lst = D.qmatmulListCreate(kind, M, items)
 
     def sync():
@@ -297,10 +302,10 @@ def run_step_list(args, wl):
     for _ in range(warm):
         D.qmatmulListRun(lst)
     sync()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(ctxinfo[2])
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for _ in range(max(0, int(0.25 / 1.2e-3)) if layers <= 32 else 30):      # settle: clocks sampled under load
+    for _ in range(30 if layers <= 32 else 6):        # settle: some tens of ms, so the clock samples see load
         D.qmatmulListRun(lst)
     e0.record(stream)
     for _ in range(steps):
@@ -334,7 +339,7 @@ def run_step_list(args, wl):
         "metric": "Q4 decode step HBM GB/s (algorithmic bytes of all projections / time)",
         "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_NOTE["gemv"], "data": "synthetic",
-        "config": {"workload": args.workload, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv, "ffn": ffn,
+        "config": {"workload": name, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv, "ffn": ffn,
                    "vocab": vocab, "matmuls_per_step": 7 * layers + 1, "launches_per_step": 1, "items_per_launch": len(items),
                    "form": "list: every projection of the step in ONE persistent launch; RMSNorm folded into the "
                            "q/k/v, gate/up and lm_head items, SwiGLU into the gate/up item, the residual adds into the "
@@ -356,36 +361,32 @@ def run_step_list(args, wl):
                      "algorithmic_per_launch": alg_bytes[0], "launch_us": step_s * 1e6},
         "clocks": clocks,
     }
-    if not args.no_cpu:
+    if with_cpu and not args.no_cpu:
         per_call, threads, ckind, sample = cpu_run(kind, M, dim, ffn, seconds=args.cpu_seconds)
         gate_bytes = algorithmic(kind, M, dim, ffn)[0]
         line["cpu_baseline"] = {"value": gate_bytes / per_call / 1e9, "unit": "GB/s", "cores": threads, "kind": ckind,
                                 "sample": "the step's gate projection (%d x %d): " % (dim, ffn) + sample}
     else:
         line["cpu_baseline"] = None
-    print(json.dumps(line))
+    D.qmatmulListDestroy(lst)
+    for b in owned:
+        D.releaseBuffer(b)
+    return line
 
 
-def run_step_workload(args, wl):
-    """One decode step's projection list (no pointwise glue): per layer wq, wk, wv, wo, gate, up, down,
-    then lm_head: 225 matmuls over 5.63 GB of distinct packed weights (larger than L2 by itself),
-    issued as 129 launches (wq/wk/wv share one, gate/up share one).  N > 1: tensor parallel -- wq/wk/wv/gate/up column-sharded (outputs stay sharded), wo/down
-    sharded along K with the all-reduce fused into the GEMV kernel, lm_head column-sharded with the
-    all-gather fused into the GEMV kernel."""
+def run_step_workload(args, wl, ctxinfo, name=None, steps=None, with_cpu=True):
+    """One decode step's projection list, one launch per projection group: per layer wq, wk, wv, wo,
+    gate, up, down, then lm_head (wq/wk/wv share a launch, gate/up share one).  Several GPUs: tensor
+    parallel -- wq/wk/wv/gate/up column-sharded (outputs stay sharded), wo/down sharded along K with the
+    all-reduce fused into the GEMV kernel, lm_head column-sharded with the all-gather fused into the
+    GEMV kernel.  On one GPU with M <= 4 the step runs as a list instead (run_step_list)."""
     import numpy as np
     import torch
     import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    world, rank, local, stream = ctxinfo
+    name = name or args.workload
     if world == 1 and wl["M"] <= 4 and not args.no_list:
-        return run_step_list(args, wl)
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return run_step_list(args, wl, ctxinfo, name=name, steps=steps, with_cpu=with_cpu)
     import smith_b200 as smith
     from smith_b200 import device as D
     from smith_b200 import parallel as P
@@ -394,9 +395,7 @@ def run_step_workload(args, wl):
         raise SystemExit("the step workloads shard over GPUs with the GEMV kernel's fused collectives (M <= 4)")
     dim, kv, ffn, vocab, layers = st["dim"], st["kv"], st["ffn"], st["vocab"], st["layers"]
     bb = 24
-    D.ctx()
-    stream = torch.cuda.ExternalStream(D.stream())
-    steps = min(args.steps, 200)
+    steps = steps or min(args.steps, 200)
     warm = max(min(args.warmup, 10), 3)
 
     def shard_n(N):
@@ -482,6 +481,54 @@ def run_step_workload(args, wl):
     D.synchronize()
     if D.kernelStatus() != 0:
         raise SystemExit("a bounded device-side wait gave up during warm-up")
+    # ---- parity before timing (values, not only "no wait gave up")
+    from oracle import oracle as O
+    parity = None
+
+    def window(pk, kl, nl, c0, width=48):
+        c1 = min(nl, c0 + width)
+        return np.concatenate([D.download(pk, (c1 - c0) * bb, np.uint8, offset=(g * nl + c0) * bb)
+                               for g in range(kl // 32)]), c1 - c0
+
+    if world > 1:
+        # (1) K-sharded product with the fused all-reduce: every rank forms the oracle's partial product of
+        # its own shard on the CPU, the partials are summed over the ranks, and every rank compares the
+        # row its kernel produced with that sum.
+        nm, pks, kl, nls, _ = next(o for o in ops if o[4] == "reduce")
+        src = x_ffn if nm == "down" else x_dim
+        reducers[nm].enqueue(src, pks[0], y)
+        D.synchronize()
+        cols, wd = window(pks[0], kl, nls[0], 0)
+        a_loc = D.download(src, M * kl * 4, np.float32).reshape(M, kl)
+        part = torch.tensor(O.matmul(a_loc, cols, kl, wd, "q4", threads=O.host_threads()).astype(np.float64), device="cuda")
+        wsq = torch.tensor((O.dequant(cols, kl, wd, "q4").astype(np.float64) ** 2).sum(0), device="cuda")
+        asq = torch.tensor((a_loc.astype(np.float64) ** 2).sum(1), device="cuda")
+        for t in (part, wsq, asq):
+            dist.all_reduce(t)
+        got = D.download(y, M * nls[0] * 4, np.float32).reshape(M, nls[0])[:, :wd]
+        bound = 1e-3 * np.sqrt(asq.cpu().numpy())[:, None] * np.sqrt(wsq.cpu().numpy())[None, :]
+        worst_r = float((np.abs(got.astype(np.float64) - part.cpu().numpy()) / np.maximum(bound, 1e-300)).max())
+        # (2) the gathered logits: a window of this rank's own slice, read from the gathered row
+        one_pass()
+        D.synchronize()
+        row = gather.read()
+        nm, pks, kl, nls, _ = ops[-1]
+        n0g = P.column_shard(vocab, world, rank)[0]
+        c0 = (nls[0] // 2) // 8 * 8
+        cols, wd = window(pks[0], kl, nls[0], c0)
+        a_loc = D.download(x_dim, M * kl * 4, np.float32).reshape(M, kl)
+        want = O.matmul(a_loc, cols, kl, wd, "q4", threads=O.host_threads())
+        bnd = O.tolerance_bound(a_loc, O.dequant(cols, kl, wd, "q4"), 1e-3)
+        worst_g = float((np.abs(row[:, n0g + c0:n0g + c0 + wd].astype(np.float64) - want) / np.maximum(bnd, 1e-300)).max())
+        w = torch.tensor([worst_r, worst_g, 0.0 if np.all(np.isfinite(row)) else 2.0], device="cuda")
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+        worst_r, worst_g, bad = (float(v) for v in w.cpu())
+        parity = {"checked": True, "worst_err_over_bound": max(worst_r, worst_g, bad), "ok": bool(max(worst_r, worst_g, bad) <= 1.0),
+                  "all_reduce_worst": worst_r, "all_gather_worst": worst_g,
+                  "what": "max over ranks: 48 columns of a K-sharded product (fused all-reduce) against the sum of the ranks' "
+                          "oracle partials, and 48 logits of each rank's slice read from its gathered row; bound = 1e-3 * ||a|| * ||w_deq[:,n]||"}
+        if not parity["ok"]:
+            raise SystemExit(f"parity check failed before timing: {parity}")
     D.graphBegin()
     one_pass()
     graph = D.graphEnd()
@@ -512,7 +559,7 @@ def run_step_workload(args, wl):
         D.graphLaunch(graph)
         D.synchronize()
         if world > 1:
-            return gather.read((gather.calls - 1) & 1)
+            return gather.read()
         return D.download(y, n_logits * 4, np.float32)
 
     for _ in range(2):
@@ -546,7 +593,7 @@ def run_step_workload(args, wl):
             "value": alg_all / step_s / 1e9, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": DTYPE_NOTE["gemv" if M <= 4 else "decode"], "data": "synthetic",
-            "config": {"workload": args.workload, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv,
+            "config": {"workload": name, "kind": "q4", "M": M, "layers": layers, "dim": dim, "kv_dim": kv,
                        "ffn": ffn, "vocab": vocab, "matmuls_per_step": 7 * layers + 1, "launches_per_step": len(ops),
                        "packed_bytes_per_gpu": weight_bytes, "tokens_per_s": M / step_s,
                        "sharding": ("tensor parallel over %d GPUs: wq/wk/wv/gate/up column-sharded, wo/down K-sharded "
@@ -559,6 +606,7 @@ def run_step_workload(args, wl):
             "e2e": {"value": alg_all / (e2e_s / e2e_steps) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * M * dim * world,
                     "d2h_bytes_per_step": 4 * n_logits * world, "steps": e2e_steps,
                     "note": "per step: H2D of the input row from page-locked memory, graph launch, wait, D2H of the logits"},
+            "parity": parity,
             "gpu_launches": int((steps + e2e_steps) * len(ops)),
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s", "frac": ach / peaks["hbm"],
                          "traffic": None,
@@ -569,16 +617,15 @@ def run_step_workload(args, wl):
                          "note": "all %d launches of a step taken together" % len(ops)},
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and with_cpu and not args.no_cpu:
             per_call, threads, ckind, sample = cpu_run(kind, M, dim, ffn, seconds=args.cpu_seconds)
             gate_bytes = algorithmic(kind, M, dim, ffn)[0]
             line["cpu_baseline"] = {"value": gate_bytes / per_call / 1e9, "unit": "GB/s", "cores": threads, "kind": ckind,
                                     "sample": "the step's gate projection (%d x %d): " % (dim, ffn) + sample}
         else:
             line["cpu_baseline"] = None
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+        return line
+    return None
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -615,9 +662,12 @@ def parity_window(D, O, kind, M, K, Nl, a_dev, pack, read_out, c0=None, width=48
 
 
 def settle_steps(step_s, world, torch, dist):
-    """How many untimed steps make about a quarter of a second of load before the timed region, so
-    that the clock samples (one per 100 ms) are taken under load even when the timed region is short."""
-    n = int(min(20000, max(0, 0.25 / max(step_s, 1e-7))))
+    """How many untimed steps make about 60 ms of load just before the timed region, so that the
+    clock samples (one per 20 ms) see load even when the timed region itself is a few milliseconds.
+    (Longer would not measure the same thing: after some tenths of a second of streaming at full
+    rate the part runs into its power cap and the SM clock drops by a tenth; the HBM peak this is
+    compared with is a burst figure too.)"""
+    n = int(min(20000, max(0, 0.06 / max(step_s, 1e-7))))
     if world > 1:
         t = torch.tensor([n], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -657,16 +707,20 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
     D.releaseBuffer(wtmp)
     a_dev = D.alloc(M * K * 4, D.PRIVATE)
     D.fillNormal(a_dev, M * K, 7, 1.0)            # same seed on every rank: replicated activations
-    # N > 1: the GEMV kernel gathers its own output over peer memory (M <= 4); wider M uses NCCL
-    gather, fused = None, False
-    if world > 1:
+    # Several GPUs: the list kernel gathers its own outputs over peer memory (M <= 4, ShardedList);
+    # with --no-list every launch of the GEMV kernel does (FusedGather); wider M uses NCCL.
+    shards_ok = all(D.qmatmulListSupports(kind, M, b - a, K) for a, b in (P.column_shard(N, world, r) for r in range(world)))
+    use_list = M <= 4 and shards_ok and not args.no_list
+    gather, fused, slist = None, False, None
+    if world > 1 and use_list:
+        slist = P.ShardedList(kind, M, K, N, packs, world, rank, a_dev)
+    elif world > 1:
         fused = M <= 4 and all(D.qgemvTiles(kind, M, b - a, K) > 0
                                for a, b in (P.column_shard(N, world, r) for r in range(world)))
         gather = P.FusedGather(M, N, world, rank, deferred=True) if fused else P.OutputGather(M, N, world, rank)
-    use_list = world == 1 and M <= 4 and D.qmatmulListSupports(kind, M, Nl, K) and not args.no_list
-    outs = [D.alloc(M * Nl * 4, D.PRIVATE) for _ in range(R)] if use_list else []
-    c_dev = (outs[0] if use_list else D.alloc(M * Nl * 4, D.PRIVATE)) if (not gather or fused) else gather.local_buf
-    lst = D.qmatmulListCreate(kind, M, [D.listItem(a_dev, pk, c, Nl, K) for pk, c in zip(packs, outs)]) if use_list else None
+    outs = [D.alloc(M * Nl * 4, D.PRIVATE) for _ in range(R)] if (use_list and not slist) else []
+    c_dev = (outs[0] if outs else D.alloc(M * Nl * 4, D.PRIVATE)) if (not gather or fused) else gather.local_buf
+    lst = D.qmatmulListCreate(kind, M, [D.listItem(a_dev, pk, c, Nl, K) for pk, c in zip(packs, outs)]) if outs else None
 
     def launches_pass():
         for pk in packs:
@@ -679,15 +733,16 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
         if fused:
             gather.finish()                       # the last launch's row is whole when the pass ends
 
-    launches_pass()                               # sizes scratch before capture
-    D.synchronize()
-    if D.kernelStatus() != 0:
-        raise SystemExit("a bounded device-side wait gave up during warm-up")
     graph = None
-    if not gather or gather.capturable:
-        D.graphBegin()
-        launches_pass()
-        graph = D.graphEnd()
+    if not slist:
+        launches_pass()                           # sizes scratch before capture
+        D.synchronize()
+        if D.kernelStatus() != 0:
+            raise SystemExit("a bounded device-side wait gave up during warm-up")
+        if not gather or gather.capturable:
+            D.graphBegin()
+            launches_pass()
+            graph = D.graphEnd()
 
     def per_call_step():
         if graph:
@@ -696,7 +751,10 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
             launches_pass()
 
     def list_step():
-        D.qmatmulListRun(lst)
+        if slist:
+            slist.run()
+        else:
+            D.qmatmulListRun(lst)
 
     step = list_step if use_list else per_call_step
 
@@ -713,9 +771,15 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
         raise SystemExit("a bounded device-side wait gave up")
     parity = None
     if rank == 0:
-        if gather and fused:
+        if slist:
+            # the gathered row of the last product: this rank's window lies inside its own slice, and
+            # every pair of the row (all ranks' slices) must carry the launch's tag
+            row, tags = slist.read(R - 1)
+            worst = parity_window(D, O, kind, M, K, Nl, a_dev, packs[-1], lambda c0, c1: row[:, n0 + c0:n0 + c1])
+            whole = bool(np.all(np.isfinite(row)) and np.all(tags == tags[0]) and tags[0] > 0)
+        elif gather and fused:
             # the gathered row (all ranks' slices): this rank's window lies inside its own slice
-            row = gather.read((gather.calls - 1) & 1)
+            row = gather.read()
             worst = parity_window(D, O, kind, M, K, Nl, a_dev, packs[-1], lambda c0, c1: row[:, n0 + c0:n0 + c1])
             whole = bool(np.all(np.isfinite(row)))
         elif gather:
@@ -729,7 +793,7 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
             whole = bool(np.all(np.isfinite(full)))
         parity = {"checked": True, "worst_err_over_bound": worst, "ok": bool(worst <= 1.0 and whole),
                   "what": "48 columns of the last product of a step"
-                          + (" (read from the gathered row)" if gather else "") + " against the CPU oracle; "
+                          + (" (read from the gathered row)" if (gather or slist) else "") + " against the CPU oracle; "
                           "bound = 1e-3 * ||a_m|| * ||w_deq[:,n]||"}
         if not parity["ok"]:
             raise SystemExit(f"parity check failed before timing: {parity}")
@@ -766,7 +830,7 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
         launches_value = steps * R * ((1 + gather.kernels_per_call) if gather else 1)
     # the same products as one launch each (graph replay), for comparison with the list form
     per_call = None
-    if use_list:
+    if use_list and not slist:
         for _ in range(3):
             per_call_step()
         barrier()
@@ -850,7 +914,12 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
                                else "one launch per product, R launches replayed from one CUDA graph",
                        "kernel": ("gemv_list_dp4a" if use_list else path), "per_call": per_call,
                        "sharding": (f"N-sharded over {world} GPU(s), all-gather of outputs "
-                                    + ("fused into the GEMV kernel (peer stores over NVLink; each launch waits for its predecessor's tiles after its own weight stream has started, a final wait closes the step)" if fused else "by NCCL"))
+                                    + ("fused into the list kernel: every item's epilogue stores its columns as {value, launch tag} "
+                                       "pairs into every rank's row over peer memory (NVLink); the ranks meet once per launch, "
+                                       "when each waits until its own rows are whole" if slist else
+                                       ("fused into the GEMV kernel (peer stores over NVLink; each launch waits for its predecessor's "
+                                        "tiles after its own weight stream has started, a final wait closes the step)" if fused
+                                        else "by NCCL")))
                        if world > 1 else "single GPU",
                        "l2": f"defeated by rotating over {R} distinct packed matrices per step "
                              f"({R * wbytes_full / 1e6:.0f} MB > 4 x 126 MB L2)",
@@ -883,7 +952,9 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
         D.qmatmulListDestroy(lst)
     if graph:
         D.graphDestroy(graph)
-    for b in packs + outs + [a_dev] + ([] if (use_list or (gather and not fused)) else [c_dev]):
+    if slist:
+        slist.close()
+    for b in packs + outs + [a_dev] + ([] if (outs or (gather and not fused)) else [c_dev]):
         D.releaseBuffer(b)
     return line
 
@@ -906,8 +977,6 @@ def main():
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         return run_reference_arm(args, wl, args.workload)
-    if "step" in wl:
-        return run_step_workload(args, wl)
 
     import torch
     import torch.distributed as dist
@@ -926,31 +995,49 @@ def main():
     stream = torch.cuda.ExternalStream(D.stream())
     ctxinfo = (world, rank, local, stream)
     warm = max(args.warmup, 3)
-    line = run_matrix_workload(args, args.workload, wl, args.steps, warm, ctxinfo)
-    # The default single-GPU run also times, in the same process, the shapes the other stated targets
-    # are quoted on (short runs: they are records, the headline is the line's own value).
-    if world == 1 and args.workload == DEFAULT and not args.no_secondary and line is not None:
+    if "step" in wl:
+        line = run_step_workload(args, wl, ctxinfo)
+    else:
+        line = run_matrix_workload(args, args.workload, wl, args.steps, warm, ctxinfo)
+    if args.workload == DEFAULT and not args.no_secondary:
         sec = []
-        for nm in SECONDARY:
+        # The default single-GPU run also times, in the same process, the shapes the other stated targets
+        # are quoted on (short runs: they are records, the headline is the line's own value).
+        for nm in (SECONDARY if world == 1 else []):
             w2 = WORKLOADS[nm]
             st2 = 20 if w2["M"] > 64 else 300
             l2 = run_matrix_workload(args, nm, w2, st2, 5, ctxinfo, with_cpu=False, with_e2e=False, sampler_on=True)
+            is_list = l2["config"]["kernel"] == "gemv_list_dp4a"
             sec.append({"workload": nm, "value": l2["value"], "unit": l2["unit"], "steps": st2,
-                        "us_per_product": l2["roofline"]["launch_us"] / (l2["config"]["products_per_step"]
-                                                                          if l2["config"]["launches_per_step"] == 1
-                                                                          and l2["config"]["products_per_step"] > 1
-                                                                          and l2["config"]["kernel"] == "gemv_list_dp4a" else 1),
-                        "form": "list" if l2["config"]["kernel"] == "gemv_list_dp4a" else "one launch per product",
+                        "us_per_product": l2["roofline"]["launch_us"] / (l2["config"]["products_per_step"] if is_list else 1),
+                        "form": "list" if is_list else "one launch per product",
                         "kernel": l2["config"]["kernel"], "per_call": l2["config"]["per_call"],
                         "roofline": {k: l2["roofline"][k] for k in ("bound", "achieved", "peak", "unit", "frac",
                                                                      "frac_of_nominal", "peak_kind")},
                         "frac_of_sustained_peak": (l2["roofline"]["achieved"] / measured_peaks()["tensor_sustained"]
                                                    if l2["roofline"]["bound"] == "tensor" else None),
                         "parity": l2["parity"], "clocks": l2["clocks"]})
-        line["secondary"] = sec
+        # ... and, at every GPU count, the 70B-shaped decode step: the workload on which sharding pays
+        # (52 GB of packed weights; several GPUs: tensor parallel with the all-reduce after wo / down and
+        # the all-gather of the logits fused into the GEMV kernel).
+        nm = "q4_llama70b_step_m1"
+        try:
+            l3 = run_step_workload(args, WORKLOADS[nm], ctxinfo, name=nm, steps=10, with_cpu=False)
+            if rank == 0:
+                sec.append({"workload": nm, "value": l3["value"], "unit": l3["unit"], "steps": l3["steps"],
+                            "ms_per_step": l3["ms_per_step"], "n_gpus": world, "form": l3["config"].get("form", "one launch per projection group"),
+                            "sharding": l3["config"]["sharding"], "launches_per_step": l3["config"]["launches_per_step"],
+                            "roofline": {k: l3["roofline"][k] for k in ("bound", "achieved", "peak", "unit", "frac", "frac_of_nominal")},
+                            "e2e": l3["e2e"], "parity": l3.get("parity"), "clocks": l3["clocks"]})
+        except (SystemExit, Exception) as e:      # a record, not the headline: say what happened and go on
+            if rank == 0:
+                sec.append({"workload": nm, "error": str(e)[:300]})
+        if rank == 0:
+            line["secondary"] = sec
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -149,7 +149,8 @@ class FusedGather:
         return self._targets[key]
 
     def enqueue(self, kind, a_buf, packed_shard_buf, K, from_previous=False):
-        """Asynchronous fused matmul + all-gather; returns which half of the row buffer it fills.
+        """Asynchronous fused matmul + all-gather; returns which half of the row buffer it fills, counted
+        on the host (valid while no captured graph replays calls on this state: see ``last_half``).
         ``from_previous`` (deferred form, K == N): the activations are the row the previous call gathered."""
         from . import device as D
         n0, n1 = self.spans[self.rank]
@@ -168,9 +169,21 @@ class FusedGather:
         if self.deferred and self._last:
             D.allGatherWait(self.state, self.y, self.M, self.N)
 
-    def read(self, half):
-        """The gathered rows [M, N] of one half (after ``finish()`` in deferred mode, and a synchronize)."""
+    def last_half(self):
+        """Which half of the row buffer the last finished call filled.  Taken from the step number the
+        kernels keep in device memory: a host-side count of ``enqueue`` calls falls behind once calls
+        are replayed from a captured graph.  Synchronises."""
         from . import device as D
+        D.synchronize()
+        step = int(D.download(self.state, 4, np.uint32)[0])
+        return (step - 1) & 1
+
+    def read(self, half=None):
+        """The gathered rows [M, N] of one half (default: the half the last finished call filled), after
+        ``finish()`` in deferred mode and a synchronize."""
+        from . import device as D
+        if half is None:
+            half = self.last_half()
         n = self.M * self.N
         if self.deferred:                 # {value, tag} pairs
             pairs = D.download(self.y, n * 8, np.float32, offset=half * n * 8).reshape(n, 2)

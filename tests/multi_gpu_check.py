@@ -56,6 +56,48 @@ def main():
             print(f"world={world} kind={knd} M={M} K={K} N={N} fused={sm.fused}: worst err/bound {worst_all:.3f} "
                   f"failures(all ranks)={int(flag.item())}", flush=True)
         dist.barrier()
+    # ---- the list form: R column-sharded products per launch, every item's epilogue gathering its row
+    for kind, M, K, N, R in [(4, 1, 4096, 14336, 6), (8, 2, 1024, 2048, 4), (4, 4, 2048, 4096, 3)]:
+        knd, bb = ("q4", 24) if kind == 4 else ("q8", 34)
+        rng = np.random.default_rng(4321 + M + N)
+        a = rng.standard_normal((M, K)).astype(np.float32)
+        a_dev = D.alloc(M * K * 4, D.PRIVATE)
+        D.upload(a_dev, a)
+        packed, shards = [], []
+        n0, n1 = P.column_shard(N, world, rank)
+        for _ in range(R):
+            w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+            pk = O.quantize_q4(w) if kind == 4 else O.quantize_q8(w)
+            packed.append(pk)
+            sh = D.alloc((K // 32) * (n1 - n0) * bb, D.PRIVATE)
+            D.upload(sh, P.slice_packed_columns(pk, K // 32, N, bb, n0, n1))
+            shards.append(sh)
+        sl = P.ShardedList(kind, M, K, N, shards, world, rank, a_dev)
+        worst_all = 0.0
+        for launch in (1, 2, 3):                              # both halves of the row buffers, tags 1, 2, 3
+            sl.run()
+            D.synchronize()
+            assert D.kernelStatus() == 0, "a bounded device-side wait gave up"
+            dist.barrier()                                    # nobody starts the next launch while a row is read
+            for i in range(R):
+                row, tags = sl.read(i)
+                if not np.all(tags == launch):
+                    failures += 1
+                want = O.matmul(a, packed[i], K, N, knd, threads=O.max_threads())
+                ok, worst = within_tolerance(row, want, a, packed[i], K, N, knd, 1e-3)
+                worst_all = max(worst_all, worst)
+                if not ok:
+                    failures += 1
+            dist.barrier()
+        flag = torch.tensor([failures], device="cuda")
+        dist.all_reduce(flag)
+        if rank == 0:
+            print(f"world={world} list kind={knd} M={M} K={K} N={N} R={R}: worst err/bound {worst_all:.3f} "
+                  f"failures(all ranks)={int(flag.item())}", flush=True)
+        sl.close()
+        for b in shards + [a_dev]:
+            D.releaseBuffer(b)
+        dist.barrier()
     # ---- a real chain: each launch reads the row the launch before it gathered (no host round trip)
     K = N = 4096
     steps = 24
