@@ -65,6 +65,12 @@ WORKLOADS = {
     "q4_llama70b_step_m1": dict(kind=4, M=1, step=dict(layers=80, dim=8192, kv=1024, ffn=28672, vocab=128256), std=0.015,
                                 K=8192, N=28672),
 }
+# The packers by themselves (quantizeQ4 / quantizeQ8 on a weight of the decode GEMV's shape and of the lm_head's)
+WORKLOADS.update({
+    "pack_q4_4096x14336": dict(kind=4, pack=True, M=0, K=4096, N=14336, std=0.02),
+    "pack_q8_4096x14336": dict(kind=8, pack=True, M=0, K=4096, N=14336, std=0.02),
+    "pack_q4_4096x128256": dict(kind=4, pack=True, M=0, K=4096, N=128256, std=0.02),
+})
 DEFAULT = "q4_decode_gemv_4096x14336_m1"
 L2_BYTES = 126e6
 
@@ -178,6 +184,10 @@ def metric_name(M):
 def run_reference_arm(args, wl, name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if wl.get("pack"):
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's packer is JavaScript and no JS runtime is "
+                          "installed; its C restatement is timed as cpu_baseline of the packer workload itself"}))
         return
     times = []
     info = None
@@ -959,6 +969,113 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
     return line
 
 
+def run_pack_workload(args, name, wl, ctxinfo):
+    """quantizeQ4 / quantizeQ8 alone: f32 [K, N] on the device -> packed blocks.  A step packs one of three
+    distinct weight matrices (each larger than L2).  Algorithmic bytes: 4 K N read + groups N block-bytes
+    written.  The CPU arm is the packer's C restatement on ONE thread -- the reference's own execution model
+    (src/ops/quantize.js:14-68 runs on the single JS thread) -- on a column window, scaled."""
+    import numpy as np
+    import torch
+    import smith_b200 as smith
+    from oracle import oracle as O
+    from smith_b200 import device as D
+    world, rank, local, stream = ctxinfo
+    kind, K, N = wl["kind"], wl["K"], wl["N"]
+    bb = 24 if kind == 4 else 34
+    G = K // 32
+    nbytes = 4 * K * N + G * N * bb
+    pack = D.q4Pack if kind == 4 else D.q8Pack
+    R = 3
+    ws = [D.alloc(K * N * 4, D.PRIVATE) for _ in range(R)]
+    for i, w in enumerate(ws):
+        D.fillNormal(w, K * N, 50 + i, wl["std"])
+    out = D.alloc(G * N * bb, D.PRIVATE)
+    steps, warm = min(args.steps, 200), max(min(args.warmup, 10), 3)
+    pack(ws[0], out, K, N)
+    D.synchronize()
+    # parity before timing: 64 columns of the packed matrix, bit for bit against the CPU packer
+    c0 = (N // 2) // 8 * 8
+    w_cols = np.stack([D.download(ws[0], 64 * 4, np.float32, offset=(k * N + c0) * 4) for k in range(K)])
+    got = np.concatenate([D.download(out, 64 * bb, np.uint8, offset=(g * N + c0) * bb) for g in range(G)])
+    want = O.quantize_q4(w_cols) if kind == 4 else O.quantize_q8(w_cols)
+    parity = {"checked": True, "ok": bool(np.array_equal(got, want)), "what": "64 columns of packed blocks, bit-exact against the CPU packer"}
+    if not parity["ok"]:
+        raise SystemExit("packed bytes differ from the CPU packer")
+    for i in range(warm):
+        pack(ws[i % R], out, K, N)
+    D.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(30):
+        pack(ws[i % R], out, K, N)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        pack(ws[i % R], out, K, N)
+    e1.record(stream)
+    D.synchronize()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    # end to end through the operator: weights in page-locked host memory -> quantizeQ4 -> a read of the result's head
+    w_host = smith.tensorFrom(D.download(ws[0], K * N * 4, np.float32), [K, N])
+    quant = smith.quantizeQ4 if kind == 4 else smith.quantizeQ8
+    e2e_steps = 3
+
+    def e2e_pass():
+        q = quant(w_host)
+        head = D.download(q.buffer, 4096, np.uint8)
+        D.releaseBuffer(q.buffer)
+        return head
+
+    e2e_pass()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    clocks = sampler.stop()
+    step_s = ms * 1e-3 / steps
+    peaks = measured_peaks()
+    ach = nbytes / step_s / 1e9
+    line = {
+        "metric": "quantizeQ4/Q8 packer HBM GB/s (4 K N read + packed bytes written / time)", "value": ach, "unit": "GB/s",
+        "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64 arithmetic (the reference packs with JS numbers), u4/i8 codes, f32/f16 scales",
+        "data": "synthetic",
+        "config": {"workload": name, "kind": f"q{kind}", "K": K, "N": N, "launches_per_step": 1,
+                   "l2": "three distinct f32 matrices of %d MB in rotation" % (K * N * 4 // 1000000),
+                   "timing": "CUDA events on the launch stream"},
+        "parity": parity,
+        "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * K * N, "d2h_bytes_per_step": 4096,
+                "steps": e2e_steps, "ms_per_call": e2e_s * 1e3,
+                "note": "operator API: quantizeQ4/Q8 on a host tensor (H2D of the f32 weights from page-locked memory, the "
+                        "kernel, wait); the packed result stays on the device by design, its first 4 KB are read back"},
+        "gpu_launches": int(steps + warm + 31 + e2e_steps + 1),
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s", "frac": ach / peaks["hbm"],
+                     "traffic": None, "peak_source": peaks["source"], "peak_kind": "copy bandwidth",
+                     "frac_of_nominal": ach / 8000.0, "algorithmic_per_launch": nbytes, "launch_us": step_s * 1e6},
+        "clocks": clocks,
+    }
+    if not args.no_cpu:
+        cols = 256
+        rng = np.random.default_rng(0)
+        wc = (rng.standard_normal((K, cols)) * wl["std"]).astype(np.float32)
+        fn = O.quantize_q4 if kind == 4 else O.quantize_q8
+        fn(wc)
+        reps, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < min(args.cpu_seconds, 5.0):
+            fn(wc)
+            reps += 1
+        el = time.perf_counter() - t0
+        per_matrix = el / reps * (N / cols)
+        line["cpu_baseline"] = {"value": nbytes / per_matrix / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                                "sample": f"{reps} runs of {cols} of {N} columns on one thread (time scaled to all columns), {el:.1f} s of CPU work"}
+    else:
+        line["cpu_baseline"] = None
+    for b in ws + [out]:
+        D.releaseBuffer(b)
+    return line
+
+
 SECONDARY = ["q4_prefill_4096x14336_m512", "q8_prefill_gemm_4096x11008_m512", "q4_gemv_4096x4096_m1"]
 
 
@@ -995,7 +1112,11 @@ def main():
     stream = torch.cuda.ExternalStream(D.stream())
     ctxinfo = (world, rank, local, stream)
     warm = max(args.warmup, 3)
-    if "step" in wl:
+    if wl.get("pack"):
+        if world != 1:
+            raise SystemExit("the packer workloads run on one GPU")
+        line = run_pack_workload(args, args.workload, wl, ctxinfo)
+    elif "step" in wl:
         line = run_step_workload(args, wl, ctxinfo)
     else:
         line = run_matrix_workload(args, args.workload, wl, args.steps, warm, ctxinfo)

@@ -294,7 +294,16 @@ int submit(SmithEncoder* enc, cudaEvent_t e0, cudaEvent_t e1) {
     bool back = false;
     if (input_ptr(c, enc->bufs[0], 0, M * K * 4, &a)) return 1;
     if (input_ptr(c, enc->bufs[1], 1, G * N * bb, &b)) return 1;
-    if (output_ptr(c, enc->bufs[2], 2, M * N * 4, &cc, &back)) return 1;
+    Buffer* ob = enc->bufs[2];
+    if (M <= 4 && ob->mode == SMITH_SHARED && !ob->wrapped && !ob->resident && ob->host && ob->bytes >= M * N * 4) {
+      // A few rows of output: the kernel stores them straight into the page-locked host buffer (it is
+      // mapped into the device's address space), each element once, instead of into a staging buffer
+      // that a second copy would then carry over.  One operation less on the stream per call.
+      cc = ob->host;
+      back = false;
+    } else if (output_ptr(c, ob, 2, M * N * 4, &cc, &back)) {
+      return 1;
+    }
     if (e0) CU_TRY(cudaEventRecord(e0, c->stream));
     if (do_qmatmul(c, kind, (const float*)a, (const uint8_t*)b, (float*)cc, M, N, K, G, kAuto)) return 1;
     if (e1) CU_TRY(cudaEventRecord(e1, c->stream));
@@ -413,7 +422,7 @@ void* smith_alloc(void* p, uint64_t bytes, uint32_t mode) {
   const size_t n = bytes ? (size_t)bytes : 1;
   cudaError_t e;
   if (mode == SMITH_SHARED) {
-    e = cudaHostAlloc(&b->host, n, cudaHostAllocPortable);
+    e = cudaHostAlloc(&b->host, n, cudaHostAllocPortable | cudaHostAllocMapped);   // mapped: kernels may store results into it
   } else {
     e = cudaMalloc(&b->dev, n);
     b->owns_dev = true;

@@ -252,6 +252,8 @@ def bufferLength(buffer):
 
 
 def releaseBuffer(buffer):
+    for key in [k for k in _viewCache if k[0] == buffer]:
+        del _viewCache[key]
     lib.smith_release_buffer(buffer)
 
 
@@ -259,15 +261,23 @@ def bufferRetainCount(buffer):
     return int(lib.smith_buffer_retain_count(buffer))
 
 
+_viewCache = {}   # (buffer, bytes, dtype) -> view; pooled buffers come back many times
+
+
 def viewBuffer(buffer, byteLength, dtype=np.float32):
     """Zero-copy typed view of a SHARED buffer's host memory (src/device.js:136-140)."""
+    dt = np.dtype(dtype)
+    key = (buffer, int(byteLength), dt.str)
+    hit = _viewCache.get(key)
+    if hit is not None:
+        return hit
     raw = lib.smith_buffer_contents(buffer)
     if not raw:
         raise SmithError("smith: buffer has no host-visible contents (PRIVATE buffer?)")
-    dt = np.dtype(dtype)
     n = int(byteLength) // dt.itemsize
-    arr = np.ctypeslib.as_array(C.cast(raw, C.POINTER(C.c_uint8)), shape=(n * dt.itemsize,))
-    return arr.view(dt)
+    arr = np.frombuffer((C.c_uint8 * (n * dt.itemsize)).from_address(raw), dtype=dt, count=n)
+    _viewCache[key] = arr
+    return arr
 
 
 def devicePtr(buffer):
@@ -325,6 +335,19 @@ def setPipeline(enc, pipelinePtr):
 
 def dispatch(enc, gridX, gridY, gridZ, groupX, groupY, groupZ):
     lib.smith_dispatch(enc, gridX, gridY, gridZ, groupX, groupY, groupZ)
+
+
+def dispatchSync(pipelinePtr, buffers, indices, paramBytes, paramIndex, grid, group):
+    """native/gpu_bridge.h:104-108: bind, dispatch and wait in ONE call across the FFI (the reference's JS
+    table does not list it; a call costs about a microsecond here, and the encoder path makes nine)."""
+    n = len(buffers)
+    lib.smith_clear_error()
+    lib.smith_dispatch_sync(ctx(), pipelinePtr, (_p * n)(*buffers), (_u32 * n)(*indices), n,
+                            paramBytes.ctypes.data_as(C.c_void_p) if paramBytes is not None else None,
+                            paramBytes.nbytes if paramBytes is not None else 0, paramIndex,
+                            grid[0], grid[1], grid[2], group[0], group[1], group[2])
+    if lastError():
+        _raise("dispatch failed")
 
 
 def endSync(enc):

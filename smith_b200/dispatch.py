@@ -14,6 +14,16 @@ GROUP_1D = 256
 
 def run(kernel, buffers, grid, group=None, params=None):
     pso = device.pipeline(kernel)
+    if not isProfilingEnabled():
+        # Same sequence (src/dispatch.js:17-48) through the bridge's one-call form
+        # (native/gpu_bridge.h:104-108): one trip across the FFI instead of nine.
+        data = np.ascontiguousarray(params["data"]) if params is not None else None
+        gx, gy, gz = grid.get("x") or 1, grid.get("y") or 1, grid.get("z") or 1
+        g = group or {}
+        device.dispatchSync(pso, [b["buffer"] for b in buffers], [b["index"] for b in buffers], data,
+                            params["index"] if params is not None else 0, (gx, gy, gz),
+                            (g.get("x") or min(gx, GROUP_1D), g.get("y") or 1, g.get("z") or 1))
+        return
     enc = device.begin()
     device.setPipeline(enc, pso)
     for b in buffers:

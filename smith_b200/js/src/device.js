@@ -139,11 +139,33 @@ function endTimed(enc) {
 }
 const allocatedSize = () => Number(lib.smith_allocated_size(ctx))
 
+// src/device.js:195-213 in the reference.  The CUDA bridge has no run-time kernel compiler: the call
+// reaches the bridge, which reports that, and this throws with the bridge's message like the
+// reference does on a compile error.
+function compileSource(source) {
+  const src = Buffer.from(source + '\0', 'utf-8')
+  const errSlot = new BigUint64Array(1)
+  const library = lib.smith_compile_source(ctx, src, errSlot)
+  if (!library) {
+    const msg = errSlot[0] ? new CString(Number(errSlot[0])).toString() : (lastError() || 'unknown error')
+    throw new Error(`smith: shader compilation failed: ${msg}`)
+  }
+  return library
+}
+
+// src/device.js:217-256 in the reference: a pipeline by kernel name from a library handle.
+function createPipeline(library, fnName) {
+  const name = Buffer.from(fnName + '\0', 'utf-8')
+  const p = lib.smith_create_pipeline(ctx, library, name)
+  if (!p) throw new Error(`smith: kernel '${fnName}' not found`)
+  return p
+}
+
 export {
   SHARED, PRIVATE, ctx, lib, lastError,
   deviceName, maxThreadgroupMemory, maxThreadsPerThreadgroup,
   alloc, bufferContents, bufferLength, releaseBuffer, bufferRetainCount, viewBuffer, makeResident,
   shaderLib, pipeline,
   begin, setBuffer, setBytes, setThreadgroupMemory, setPipeline, dispatch, endSync, endAsync, wait,
-  endTimed, allocatedSize,
+  endTimed, allocatedSize, compileSource, createPipeline,
 }

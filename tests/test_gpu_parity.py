@@ -524,52 +524,74 @@ def test_fused_reduce_two_k_shards_with_a_preseeded_peer():
 
 
 # ------------------------------------------------------------------ full-size projection shapes, sampled columns
-# BASELINE configs 4 and 5: every Q4 linear projection of a Llama-3-8B-shaped and a 70B-shaped decode
-# step.  Weights are generated and packed on the device at full size; a window of columns is
+# Every Q4 linear projection of a Llama-3-8B-shaped and a 70B-shaped decode step.  Weights are generated and packed on the device at full size; a window of columns is
 # downloaded and checked against the oracle (packed bytes bit-exact, outputs within tolerance).
 LLAMA_8B = [("wq", 4096, 4096), ("wk", 4096, 1024), ("wo", 4096, 4096), ("gate", 4096, 14336), ("down", 14336, 4096),
             ("lm_head", 4096, 128256)]
 LLAMA_70B = [("wq", 8192, 8192), ("wk", 8192, 1024), ("gate", 8192, 28672), ("down", 28672, 8192)]
 
 
-def _check_projection(K, N, Ms, std, seed):
+def _check_projection(K, N, Ms, std, seed, kind="q4", windows=None):
+    """Full-size weights generated and packed on the device; windows of 48 columns are brought back
+    and checked: packed bytes bit-exact against the CPU packer on the same f32 columns, outputs within
+    tolerance of the oracle for every M."""
     G = K // 32
+    bb = 24 if kind == "q4" else 34
+    k4 = 4 if kind == "q4" else 8
     wb = DevBuf(K * N * 4)
     device.fillNormal(wb.handle, K * N, seed, std)
-    pb = DevBuf(G * N * 24)
-    device.q4Pack(wb.handle, pb.handle, K, N)
+    pb = DevBuf(G * N * bb)
+    (device.q4Pack if kind == "q4" else device.q8Pack)(wb.handle, pb.handle, K, N)
     device.synchronize()
-    c0 = (N // 2) // 8 * 8
-    c1 = min(N, c0 + 48)
-    # packed bytes of the window: bit-exact against the CPU packer on the same f32 columns
-    w_cols = np.empty((K, c1 - c0), np.float32)
+    starts = windows if windows is not None else [(N // 2) // 8 * 8]
     full_rows = wb.get(np.float32).reshape(K, N) if K * N <= (1 << 26) else None
-    if full_rows is not None:
-        w_cols[:] = full_rows[:, c0:c1]
-    else:                                               # too large to bring back whole: row by row
-        for k in range(K):
-            w_cols[k] = device.download(wb.handle, (c1 - c0) * 4, np.float32, offset=(k * N + c0) * 4)
+    cols = []
+    for c0 in starts:
+        c1 = min(N, c0 + 48)
+        w_cols = np.empty((K, c1 - c0), np.float32)
+        if full_rows is not None:
+            w_cols[:] = full_rows[:, c0:c1]
+        else:                                               # too large to bring back whole: row by row
+            for k in range(K):
+                w_cols[k] = device.download(wb.handle, (c1 - c0) * 4, np.float32, offset=(k * N + c0) * 4)
+        packed_cols = np.empty((G, (c1 - c0) * bb), np.uint8)
+        for g in range(G):
+            packed_cols[g] = device.download(pb.handle, (c1 - c0) * bb, np.uint8, offset=(g * N + c0) * bb)
+        packed_cols = packed_cols.reshape(-1)
+        want = O.quantize_q4(w_cols) if kind == "q4" else O.quantize_q8(w_cols)
+        assert np.array_equal(packed_cols, want), f"packed bytes of columns [{c0}, {c1}) differ from the oracle"
+        cols.append((c0, c1, packed_cols))
     wb.free()
-    packed_cols = np.empty((G, (c1 - c0) * 24), np.uint8)
-    for g in range(G):
-        packed_cols[g] = device.download(pb.handle, (c1 - c0) * 24, np.uint8, offset=(g * N + c0) * 24)
-    packed_cols = packed_cols.reshape(-1)
-    assert np.array_equal(packed_cols, O.quantize_q4(w_cols))
     rng = np.random.default_rng(seed)
     for M in Ms:
         a = rng.standard_normal((M, K)).astype(np.float32)
         ab, cb = DevBuf.of(a), DevBuf(M * N * 4)
-        device.qmatmul(4, ab.handle, pb.handle, cb.handle, M, N, K, G, device.PATH_AUTO)
+        device.qmatmul(k4, ab.handle, pb.handle, cb.handle, M, N, K, G, device.PATH_AUTO)
         device.synchronize()
         assert device.kernelStatus() == 0
-        got = cb.get(np.float32).reshape(M, N)[:, c0:c1]
-        want = O.matmul(a, packed_cols, K, c1 - c0, "q4", threads=O.max_threads())
-        ok, worst = within_tolerance(got, want, a, packed_cols, K, c1 - c0, "q4", REL)
-        assert ok, f"K={K} N={N} M={M}: worst err/bound = {worst}"
-        assert np.all(np.isfinite(cb.get(np.float32)))
+        out = cb.get(np.float32).reshape(M, N)
+        assert np.all(np.isfinite(out))
+        for c0, c1, packed_cols in cols:
+            want = O.matmul(a, packed_cols, K, c1 - c0, kind, threads=O.host_threads())
+            ok, worst = within_tolerance(out[:, c0:c1], want, a, packed_cols, K, c1 - c0, kind, REL)
+            assert ok, f"K={K} N={N} M={M} columns [{c0}, {c1}): worst err/bound = {worst}"
         ab.free()
         cb.free()
     pb.free()
+
+
+# The two stated benchmark configurations at their full shapes.
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_q8_prefill_gemm_512x4096x11008_full_shape(seed):
+    """Q8 prefill GEMM: activations [512, 4096] ~N(0,1), weight [4096, 11008] ~N(0,0.02) packed by
+    quantizeQ8, seeds 0..3; three windows of columns (first, middle, last) against the oracle."""
+    _check_projection(4096, 11008, (512,), 0.02, seed, kind="q8", windows=[0, 5496, 11008 - 48])
+
+
+def test_q4_decode_and_skinny_sweep_4096x14336_full_shape():
+    """Q4 weight [4096, 14336] ~N(0,0.02); activations [M, 4096] for M in {1, 4, 16, 64, 256}: every
+    dispatch path (GEMV, decode, tensor) at the shape the decode target is quoted on."""
+    _check_projection(4096, 14336, (1, 4, 16, 64, 256), 0.02, 0, kind="q4", windows=[0, 7168, 14336 - 48])
 
 
 @pytest.mark.parametrize("name,K,N", LLAMA_8B)
