@@ -829,7 +829,7 @@ def run_matrix_workload(args, name, wl, steps, warm, ctxinfo, with_cpu=True, wit
     sampler = ClockSampler(local)
     if rank == 0 and sampler_on:
         sampler.start()
-    settle = settle_steps(est, world, torch, dist)
+    settle = 0 if args.no_settle else settle_steps(est, world, torch, dist)
     for _ in range(settle):
         step()
     barrier()
@@ -1090,6 +1090,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-list", action="store_true", help="time one launch per product instead of the list form")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads of the default run")
+    ap.add_argument("--no-settle", action="store_true", help="no untimed load before the timed region (for profiler captures)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

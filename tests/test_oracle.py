@@ -151,3 +151,37 @@ def test_q8_rule_properties():
     # scale is amax/127 truncated to half precision: error per element below one code step
     step = np.repeat(amax / 127, 32, axis=0).reshape(64, 8)
     assert np.all(np.abs(deq - w) <= step * 1.01 + 1e-12)
+
+
+# ---- the pointwise glue of the decode step (folded into the list kernel)
+@pytest.mark.skipif(not (O.have_ref() and O.have_ref_glue()), reason="oracle/_ref not built (no reference checkout on this machine)")
+@pytest.mark.parametrize("rows,cols", [(1, 64), (3, 100), (2, 256), (1, 4096), (2, 14336), (1, 7)])
+def test_rmsnorm_restatement_equals_the_compiled_shader(rows, cols):
+    """oracle_rmsnorm against shaders/rmsnorm.metal compiled as C++ and run as a threadgroup (an OpenMP
+    team): same partial sums, same halving tree, same bits."""
+    rng = np.random.default_rng(rows * 1000 + cols)
+    x = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+    g = (1.0 + 0.3 * rng.standard_normal(cols)).astype(np.float32)
+    for eps in (1e-5, 1e-6):
+        a, b = O.rmsnorm(x, g, eps), O.ref_rmsnorm(x, g, eps)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.skipif(not (O.have_ref() and O.have_ref_glue()), reason="oracle/_ref not built (no reference checkout on this machine)")
+def test_swiglu_restatement_equals_the_compiled_shader():
+    rng = np.random.default_rng(5)
+    gate = (rng.standard_normal(5000) * 4).astype(np.float32)
+    up = rng.standard_normal(5000).astype(np.float32)
+    gate[:4] = [0.0, -0.0, 88.0, -88.0]
+    assert np.array_equal(O.swiglu(gate, up).view(np.uint32), O.ref_swiglu(gate, up).view(np.uint32))
+
+
+def test_rmsnorm_and_swiglu_known_answers():
+    """Hand-checkable cases: a row of equal values normalises to gamma (up to eps); silu(0) = 0."""
+    x = np.full((1, 64), 2.0, np.float32)
+    g = np.arange(64, dtype=np.float32)
+    out = O.rmsnorm(x, g, 0.0)
+    assert np.allclose(out, g, rtol=1e-6)
+    assert O.swiglu(np.zeros(3, np.float32), np.ones(3, np.float32)).tolist() == [0.0, 0.0, 0.0]
+    big = O.swiglu(np.array([20.0], np.float32), np.array([2.0], np.float32))
+    assert abs(float(big[0]) - 40.0) < 1e-5
