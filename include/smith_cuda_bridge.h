@@ -155,6 +155,19 @@ int32_t smith_download(void* buffer, uint64_t offset, void* host, uint64_t bytes
 int32_t smith_q4_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
 int32_t smith_q8_pack(void* ctx, void* w, void* out, uint64_t K, uint64_t N);
 
+/* GGUF blocks straight into the matmul layouts, on the device.  The reference de-quantises a GGUF
+ * tensor to f32 on the host (src/gguf.js:187-231, 343-400), transposes it from [out_dim, in_dim] to
+ * [in_dim, out_dim] (src/gguf_loader.js:236-252) and multiplies in f32.  src holds the tensor's blocks
+ * as they lie in the file (block of row r, group b at (r * in_dim/32 + b) * block bytes); dst receives
+ * the packed matrix matmul_q8 / matmul_q4 read, with K = in_dim and N = out_dim:
+ *   ggml type 8 (Q8_0, 34-byte blocks): the same 34 bytes, re-tiled to (b * N + r) * 34;
+ *   ggml type 2 (Q4_0, 18-byte blocks): the nibble bytes as they are, the f16 scale widened to f32,
+ *     zero = 8 -> 24-byte Q4 blocks; scale * (nibble - 8) is the same f32 value either way.
+ * Other types are refused (their arithmetic is not the two shaders').  Asynchronous. */
+#define SMITH_GGML_Q4_0 2u
+#define SMITH_GGML_Q8_0 8u
+int32_t smith_gguf_repack(void* ctx, uint32_t ggml_type, void* src, void* dst, uint64_t out_dim, uint64_t in_dim);
+
 /* Direct, asynchronous C[M,N] = A[M,K] * dequant(B) on device-side buffers.
  * kind: 4 or 8.  path: 0 = choose by shape, 1 = any-shape CUDA-core kernel,
  * 2 = decode kernel (M <= 32, integer mma.sync), 3 = tensor-core (tcgen05) kernel,

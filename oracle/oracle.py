@@ -78,6 +78,8 @@ def lib():
         _lib.oracle_max_threads.restype = C.c_int
         _lib.oracle_rmsnorm.restype = None
         _lib.oracle_rmsnorm.argtypes = [p, p, p, i64, i64, C.c_float]
+        _lib.oracle_gguf_dequant.restype = C.c_int
+        _lib.oracle_gguf_dequant.argtypes = [C.c_int, p, i64, p]
         _lib.oracle_swiglu.restype = None
         _lib.oracle_swiglu.argtypes = [p, p, p, i64]
     return _lib
@@ -213,6 +215,17 @@ def swiglu(gate, up):
 
 def ref_swiglu(gate, up):
     return _swiglu(ref().ref_swiglu, gate, up)
+
+
+def gguf_dequant(ggml_type, blocks):
+    """src/gguf.js:187-197 / 221-231 restated: raw Q4_0 (type 2) or Q8_0 (type 8) blocks -> f32, 32 per block."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    per = 18 if ggml_type == 2 else 34
+    n = blocks.size // per
+    out = np.zeros(n * 32, dtype=np.float32)
+    if lib().oracle_gguf_dequant(int(ggml_type), _ptr(blocks), n, _ptr(out)) != 0:
+        raise ValueError("gguf_dequant: only Q4_0 (2) and Q8_0 (8)")
+    return out
 
 
 def have_ref_glue():

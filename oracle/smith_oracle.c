@@ -14,6 +14,7 @@
  *   oracle_matmul_q8     shaders/matmul_q8.metal:20-57
  *   oracle_rmsnorm       shaders/rmsnorm.metal:15-49, src/ops/rmsnorm.js:19-38
  *   oracle_swiglu        shaders/swiglu.metal:12-22
+ *   oracle_gguf_dequant  src/gguf.js:187-197 (Q4_0), 221-231 (Q8_0)
  *   oracle_quantize_q8   NO reference counterpart ("parity unpinned"): the
  *                        reference has no producer for the layout that
  *                        matmul_q8 consumes.  The rule frozen here is written
@@ -306,6 +307,30 @@ void oracle_swiglu(const float *gate, const float *up, float *out, int64_t n) {
     float silu = g / (1.0f + expf(-g));
     out[i] = silu * up[i];
   }
+}
+
+/* ---- GGUF block decoders: src/gguf.js:187-197 (Q4_0) and 221-231 (Q8_0) ------------- */
+/* blocks: `nblocks` consecutive blocks as they lie in the file; out: 32 f32 per block.
+ * Q4_0 (type 2): 18 bytes, value = scale * (nibble - 8), element i in byte i >> 1, low nibble if i is
+ * even (the reference's reading).  Q8_0 (type 8): 34 bytes, value = scale * int8.  The scale goes
+ * through the reference's fromFloat16; the product is rounded to f32 by the Float32Array store. */
+int oracle_gguf_dequant(int ggml_type, const uint8_t *blocks, int64_t nblocks, float *out) {
+  if (ggml_type != 2 && ggml_type != 8) return 1;
+  const int bytes = ggml_type == 2 ? 18 : 34;
+  for (int64_t b = 0; b < nblocks; b++) {
+    const uint8_t *blk = blocks + b * bytes;
+    const double scale = oracle_from_float16((uint16_t)(blk[0] | (blk[1] << 8)));
+    for (int i = 0; i < 32; i++) {
+      if (ggml_type == 2) {
+        const uint8_t byte = blk[2 + (i >> 1)];
+        const int nib = (i & 1) ? (byte >> 4) : (byte & 0x0F);
+        out[b * 32 + i] = (float)(scale * (double)(nib - 8));
+      } else {
+        out[b * 32 + i] = (float)(scale * (double)(int8_t)blk[2 + i]);
+      }
+    }
+  }
+  return 0;
 }
 
 int oracle_max_threads(void) {

@@ -5,13 +5,15 @@ the four quantization operators, profiling and device info.  Everything runs
 through libsmith_cuda.so; importing this package without the built library
 raises ImportError.
 """
-from . import device, dispatch, dtype, lifecycle, pool, profile, tensor
+from . import checkpoint, device, dispatch, dtype, gguf, lifecycle, pool, profile, tensor
+from .checkpoint import loadQuantized, saveQuantized
+from .gguf import quantizedFromGGUF
 from .device import PRIVATE, SHARED, SmithError
 from .lifecycle import dispose, isDisposed, retain, using, withNoAlloc
 from .ops.quantize import (GROUP_BYTES, GROUP_SIZE, Q8_BLOCK_BYTES, Q8_BLOCK_SIZE, matmulQ4, matmulQ8,
                            quantizeQ4, quantizeQ8)
 from .pool import poolDrain, poolFlush, poolStats
-from .profile import benchmark, disableProfiling, enableProfiling, report, resetProfile
+from .profile import benchmark, disableProfiling, enableProfiling, report, resetProfile, setPeaks
 from .profile import profile as profileFn
 from .tensor import create, full, ones, rand, randn, toArray, toNumpy, zeros
 from .tensor import tensor as tensorFrom

@@ -784,6 +784,21 @@ int32_t smith_q8_pack(void* p, void* w, void* out, uint64_t K, uint64_t N) {
   return e == cudaSuccess ? 0 : fail("pack_q8 launch failed: %s", cudaGetErrorString(e));
 }
 
+int32_t smith_gguf_repack(void* p, uint32_t ggml_type, void* src, void* dst, uint64_t out_dim, uint64_t in_dim) {
+  Context* c = as_ctx(p);
+  Buffer *bs = as_buf(src), *bd = as_buf(dst);
+  if (!c || !bs || !bd) return 1;
+  if (ggml_type != 2 && ggml_type != 8)
+    return fail("smith_gguf_repack: ggml type %u is not one the quantized kernels read directly (Q4_0 = 2, Q8_0 = 8)", ggml_type);
+  if (in_dim == 0 || (in_dim % 32) != 0) return fail("smith_gguf_repack: in_dim = %llu is not a multiple of 32", (unsigned long long)in_dim);
+  if (!bs->dev || !bd->dev) return fail("smith_gguf_repack needs buffers with a device side");
+  const uint64_t G = in_dim / 32, sb = (ggml_type == 8) ? 34 : 18, db = (ggml_type == 8) ? kQ8Bytes : kQ4Bytes;
+  if (bs->bytes < out_dim * G * sb || bd->bytes < out_dim * G * db) return fail("smith_gguf_repack: buffer too small");
+  cudaError_t e = launch_gguf_repack((int)ggml_type, (const uint8_t*)bs->dev, (uint8_t*)bd->dev, (int64_t)out_dim, (int64_t)in_dim,
+                                     c->stream);
+  return e == cudaSuccess ? 0 : fail("gguf repack launch failed: %s", cudaGetErrorString(e));
+}
+
 int32_t smith_qmatmul(void* p, uint32_t kind, void* a, void* b, void* cbuf, uint64_t M, uint64_t N, uint64_t K,
                       uint64_t groups, uint32_t path) {
   Context* c = as_ctx(p);

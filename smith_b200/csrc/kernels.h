@@ -30,6 +30,11 @@ inline void count_launch(int n = 1) {
 cudaError_t launch_pack_q4(const float* w, uint8_t* out, int64_t K, int64_t N, cudaStream_t s);
 cudaError_t launch_pack_q8(const float* w, uint8_t* out, int64_t K, int64_t N, cudaStream_t s);
 
+// gguf_repack.cu : GGUF Q8_0 (ggml type 8) / Q4_0 (type 2) blocks of a [out_dim, in_dim] tensor -> the
+// [in_dim/32][out_dim][block] layouts the matmul kernels read (K = in_dim, N = out_dim).
+cudaError_t launch_gguf_repack(int ggml_type, const uint8_t* src, uint8_t* dst, int64_t out_dim, int64_t in_dim,
+                               cudaStream_t s);
+
 // qmatmul_generic.cu : any shape, CUDA cores, sequential-k f32 accumulation.
 cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                                    int64_t N, int64_t K, int64_t groups, cudaStream_t s);

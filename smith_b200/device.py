@@ -94,6 +94,7 @@ SYMBOLS = {
     "smith_download": (_i32, [_p, _u64, _p, _u64]),
     "smith_q4_pack": (_i32, [_p, _p, _p, _u64, _u64]),
     "smith_q8_pack": (_i32, [_p, _p, _p, _u64, _u64]),
+    "smith_gguf_repack": (_i32, [_p, _u32, _p, _p, _u64, _u64]),
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_qmatmul_list_create": (_p, [_p, _u32, _u64, C.POINTER(SmithListItem), _u32]),
@@ -421,6 +422,13 @@ def q4Pack(wBuffer, outBuffer, K, N):
 
 def q8Pack(wBuffer, outBuffer, K, N):
     _check(lib.smith_q8_pack(ctx(), wBuffer, outBuffer, K, N), "q8_pack")
+
+
+GGML_Q4_0, GGML_Q8_0 = 2, 8
+
+
+def ggufRepack(ggmlType, srcBuffer, dstBuffer, outDim, inDim):
+    _check(lib.smith_gguf_repack(ctx(), ggmlType, srcBuffer, dstBuffer, outDim, inDim), "gguf_repack")
 
 
 def qmatmul(kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path=PATH_AUTO):

@@ -7,7 +7,7 @@ bytes, dispatch, then either a timed submit (profiling on) or a blocking one.
 import numpy as np
 
 from . import device
-from .profile import isProfilingEnabled, recordKernel
+from .profile import algorithmicCost, isProfilingEnabled, recordKernel
 
 GROUP_1D = 256
 
@@ -41,6 +41,6 @@ def run(kernel, buffers, grid, group=None, params=None):
     device.dispatch(enc, gx, gy, gz, grpX, grpY, grpZ)
     if isProfilingEnabled():
         timing = device.endTimed(enc)
-        recordKernel(kernel, timing["gpuMs"])
+        recordKernel(kernel, timing["gpuMs"], algorithmicCost(kernel, params["data"] if params is not None else None))
     else:
         device.endSync(enc)

@@ -602,3 +602,71 @@ def test_llama_8b_shaped_projections(name, K, N):
 @pytest.mark.parametrize("name,K,N", LLAMA_70B)
 def test_llama_70b_shaped_projections(name, K, N):
     _check_projection(K, N, (1, 32, 256), 0.015, 70 + len(name))
+
+
+def test_packed_weights_save_and_load_round_trip(tmp_path):
+    """saveQuantized / loadQuantized: the packed bytes come back bit for bit and multiply the same."""
+    rng = np.random.default_rng(77)
+    K, N = 512, 264
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    a = rng.standard_normal((2, K)).astype(np.float32)
+    wt, at = smith.tensorFrom(w, [K, N]), smith.tensorFrom(a, [2, K])
+    q4, q8 = smith.quantizeQ4(wt), smith.quantizeQ8(wt)
+    path = str(tmp_path / "packed")
+    smith.saveQuantized({"layer0.wq": ("q4", q4), "layer0.wk": ("q8", q8)}, path)
+    back = smith.loadQuantized(path)
+    assert list(back) == ["layer0.wq", "layer0.wk"] and back["layer0.wq"][0] == "q4" and back["layer0.wk"][0] == "q8"
+    for name, rec in (("layer0.wq", q4), ("layer0.wk", q8)):
+        got = back[name][1]
+        assert (got.K, got.N, got.groups, got.totalBytes) == (rec.K, rec.N, rec.groups, rec.totalBytes)
+        assert np.array_equal(device.download(got.buffer, got.totalBytes), device.download(rec.buffer, rec.totalBytes))
+    y0 = smith.toNumpy(smith.matmulQ4(at, q4))
+    y1 = smith.toNumpy(smith.matmulQ4(at, back["layer0.wq"][1]))
+    assert np.array_equal(y0.view(np.uint32), y1.view(np.uint32))
+    import json
+    manifest = json.load(open(path + ".json"))
+    manifest["totalBytes"] += 1
+    json.dump(manifest, open(path + ".json", "w"))
+    with pytest.raises(ValueError):
+        smith.loadQuantized(path)
+
+
+def test_profile_report_carries_bandwidth_and_roofline():
+    rng = np.random.default_rng(78)
+    K, N = 4096, 1792
+    wt = smith.tensorFrom((rng.standard_normal((K, N)) * 0.02).astype(np.float32), [K, N])
+    at = smith.tensorFrom(rng.standard_normal((1, K)).astype(np.float32), [1, K])
+    wq = smith.quantizeQ4(wt)
+    prof = smith.profileFn(lambda: [smith.dispose(smith.matmulQ4(at, wq)) for _ in range(5)])
+    mm = next(k for k in prof["kernels"] if k["kernel"] == "matmul_q4")
+    assert mm["calls"] == 5 and mm["gbs"] > 10 and 0 < mm["pctRoofline"] <= 110 and mm["bound"] == "hbm"
+
+
+@pytest.mark.parametrize("ggml_type,M", [(8, 1), (8, 64), (2, 1), (2, 3), (2, 96)])
+def test_gguf_blocks_run_on_the_quantized_path(ggml_type, M):
+    """Q8_0 / Q4_0 blocks as they lie in a GGUF file, re-tiled on the device (smith_gguf_repack), then
+    matmulQ8 / matmulQ4: the result is held to the matmul tolerance against the reference's own route
+    (de-quantise every block to f32, src/gguf.js:187-231; transpose, src/gguf_loader.js:236-252;
+    sequential f32 product), and the re-tiled bytes de-quantise to exactly those f32 weights."""
+    rng = np.random.default_rng(ggml_type * 10 + M)
+    out_dim, in_dim = 1032, 2048                       # N (not a multiple of 256), K
+    G = in_dim // 32
+    per = 34 if ggml_type == 8 else 18
+    blocks = rng.integers(0, 256, (out_dim, G, per), dtype=np.uint8)
+    blocks[:, :, 0] = rng.integers(0, 256, (out_dim, G))
+    blocks[:, :, 1] = rng.integers(0x1C, 0x24, (out_dim, G))      # f16 scales around 2^-8 .. 2^-6
+    w_file = O.gguf_dequant(ggml_type, blocks).reshape(out_dim, in_dim)
+    kind, rec = smith.quantizedFromGGUF(blocks, ggml_type, [out_dim, in_dim])
+    knd = "q8" if ggml_type == 8 else "q4"
+    assert kind == knd and (rec.K, rec.N, rec.groups) == (in_dim, out_dim, G)
+    packed = device.download(rec.buffer, rec.totalBytes)
+    assert np.array_equal(O.dequant(packed, in_dim, out_dim, knd).view(np.uint32), w_file.T.copy().view(np.uint32))
+    a = rng.standard_normal((M, in_dim)).astype(np.float32)
+    at = smith.tensorFrom(a, [M, in_dim])
+    got = smith.toNumpy((smith.matmulQ8 if ggml_type == 8 else smith.matmulQ4)(at, rec))
+    want = O.matmul(a, packed, in_dim, out_dim, knd, threads=O.host_threads())
+    ok, worst = within_tolerance(got, want, a, packed, in_dim, out_dim, knd, REL)
+    assert ok, worst
+    with pytest.raises(ValueError):
+        smith.quantizedFromGGUF(blocks, 3, [out_dim, in_dim])     # Q4_1: not the shaders' arithmetic
+    device.releaseBuffer(rec.buffer)

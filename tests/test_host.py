@@ -142,3 +142,34 @@ def test_profile_stats_shape():
     s = computeStats(sorted([1.0, 2.0, 3.0, 4.0]))
     assert s == {"mean": 2.5, "median": 2.5, "min": 1.0, "max": 4.0, "p95": 4.0, "stddev": 1.118}
     assert computeStats([])["mean"] == 0
+
+
+def test_profile_algorithmic_cost_and_roofline_fields():
+    """The additions to src/profile.js's report: bytes / flops per dispatch and the roofline fraction."""
+    from smith_b200 import profile as P
+    assert P.algorithmicCost("matmul_q4", [1, 14336, 4096, 128]) == (128 * 14336 * 24 + 4 * 4096 + 4 * 14336, 2 * 4096 * 14336)
+    assert P.algorithmicCost("matmul_q8", [512, 11008, 4096, 128]) == (128 * 11008 * 34 + 4 * 512 * 4096 + 4 * 512 * 11008,
+                                                                        2 * 512 * 4096 * 11008)
+    assert P.algorithmicCost("quantize_q4", [100, 40]) == (4 * 100 * 40 + 4 * 40 * 24, 0)
+    assert P.algorithmicCost("relu_forward", [3]) is None and P.algorithmicCost("matmul_q4", None) is None
+    saved = dict(P._kernelStats), P._totalDispatches, P._totalGpuMs
+    try:
+        P._kernelStats.clear()
+        P._totalDispatches, P._totalGpuMs = 0, 0.0
+        orig = P.device.allocatedSize
+        P.device.allocatedSize = lambda: 0            # no device on this machine
+        P.setPeaks(8000.0, 2250.0, "nominal")
+        P.recordKernel("matmul_q4", 0.01, P.algorithmicCost("matmul_q4", [1, 14336, 4096, 128]))   # 10 us
+        P.recordKernel("matmul_q4", 0.01, P.algorithmicCost("matmul_q4", [1, 14336, 4096, 128]))
+        P.recordKernel("other", 1.0)
+        rep = P.report()
+        mm = next(k for k in rep["kernels"] if k["kernel"] == "matmul_q4")
+        assert abs(mm["gbs"] - 44113920 / 1e-5 / 1e9) < 1 and mm["bound"] == "hbm"
+        assert abs(mm["pctRoofline"] - 100 * mm["gbs"] / 8000.0) < 0.01
+        assert "gbs" not in next(k for k in rep["kernels"] if k["kernel"] == "other")
+        assert rep["peaks"]["hbmGBs"] == 8000.0
+    finally:
+        P.device.allocatedSize = orig
+        P._kernelStats.clear()
+        P._kernelStats.update(saved[0])
+        P._totalDispatches, P._totalGpuMs = saved[1], saved[2]

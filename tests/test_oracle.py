@@ -185,3 +185,37 @@ def test_rmsnorm_and_swiglu_known_answers():
     assert O.swiglu(np.zeros(3, np.float32), np.ones(3, np.float32)).tolist() == [0.0, 0.0, 0.0]
     big = O.swiglu(np.array([20.0], np.float32), np.array([2.0], np.float32))
     assert abs(float(big[0]) - 40.0) < 1e-5
+
+
+# ---- GGUF block decoders (src/gguf.js:187-197, 221-231), the known answers of tests/gguf.test.js:208-243
+def test_gguf_q4_0_block_known_answers():
+    block = np.zeros(18, np.uint8)
+    block[0], block[1] = 0x00, 0x38                 # scale 0.5 as f16
+    block[2:] = 0x88                                # every nibble 8 -> 0.5 * (8 - 8) = 0
+    assert np.all(O.gguf_dequant(2, block) == 0.0)
+    block[2:] = 0xFF                                # every nibble 15 -> 0.5 * (15 - 8) = 3.5
+    assert np.all(O.gguf_dequant(2, block) == 3.5)
+    block[2] = 0x21                                 # element 0 = low nibble 1, element 1 = high nibble 2
+    v = O.gguf_dequant(2, block)
+    assert v[0] == 0.5 * (1 - 8) and v[1] == 0.5 * (2 - 8)
+
+
+def test_gguf_q8_0_block_known_answers():
+    block = np.zeros(34, np.uint8)
+    block[0], block[1] = 0x00, 0x3C                 # scale 1.0 as f16
+    block[2::2], block[3::2] = 1, 255               # +1, -1 alternating
+    v = O.gguf_dequant(8, block)
+    assert v[0] == 1.0 and v[1] == -1.0 and v[2] == 1.0
+
+
+def test_gguf_q8_0_blocks_are_the_matmul_q8_blocks():
+    """A Q8_0 tensor [outDim, inDim] re-tiled block by block is the packed [inDim/32][outDim][34] matrix:
+    de-quantising either way gives the transposed weights bit for bit."""
+    rng = np.random.default_rng(8)
+    out_dim, in_dim = 24, 96
+    G = in_dim // 32
+    blocks = rng.integers(0, 256, (out_dim, G, 34), dtype=np.uint8)
+    blocks[:, :, 1] = rng.integers(0x20, 0x3C, (out_dim, G))      # finite f16 scales
+    w_file = O.gguf_dequant(8, blocks).reshape(out_dim, in_dim)   # the reference's f32 weights, [outDim, inDim]
+    packed = np.ascontiguousarray(blocks.transpose(1, 0, 2)).reshape(-1)
+    assert np.array_equal(O.dequant(packed, in_dim, out_dim, "q8").view(np.uint32), w_file.T.copy().view(np.uint32))
