@@ -171,12 +171,14 @@ int32_t smith_gguf_repack(void* ctx, uint32_t ggml_type, void* src, void* dst, u
 /* Direct, asynchronous C[M,N] = A[M,K] * dequant(B) on device-side buffers.
  * kind: 4 or 8.  path: 0 = choose by shape, 1 = any-shape CUDA-core kernel,
  * 2 = decode kernel (M <= 32, integer mma.sync), 3 = tensor-core (tcgen05) kernel,
- * 4 = GEMV kernel (M <= 4, dp4a).  A forced path that does not take the shape fails. */
+ * 4 = GEMV kernel (M <= 4, dp4a), 5 = skinny kernel (M <= 64, f16 mma.sync with the weights
+ * de-quantised in registers).  A forced path that does not take the shape fails. */
 #define SMITH_PATH_AUTO 0
 #define SMITH_PATH_GENERIC 1
 #define SMITH_PATH_DECODE 2
 #define SMITH_PATH_TENSOR 3
 #define SMITH_PATH_GEMV 4
+#define SMITH_PATH_SKINNY 5
 int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint64_t M, uint64_t N,
                       uint64_t K, uint64_t groups, uint32_t path);
 /* No counterpart in the reference, whose callers issue one matmul per weight matrix

@@ -246,6 +246,13 @@ int do_qmatmul(Context* c, int kind, const float* A, const uint8_t* B, float* C,
                     (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
       e = launch_qgemv(kind, A, B, C, M, N, K, groups, c->stream);
       break;
+    case kSkinny:
+      if (!qskinny_supports(kind, M, N, K, groups))
+        return fail("skinny kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,
+                    (unsigned long long)N, (unsigned long long)K, (unsigned long long)groups);
+      if (ensure_workspace(c, qskinny_workspace_bytes(kind, M, N, K))) return 1;
+      e = launch_qskinny(kind, A, B, C, M, N, K, groups, c->ws, c->stream);
+      break;
     case kTensor: {
       if (!qgemm_tc_supports(kind, M, N, K, groups))
         return fail("tensor-core kernel does not take M=%llu N=%llu K=%llu groups=%llu", (unsigned long long)M,

@@ -12,7 +12,7 @@ constexpr int kQ4Bytes = 24;  // 16 nibble bytes + f32 scale + f32 zero (src/ops
 constexpr int kQ8Group = 32;  // elements per Q8 block (src/ops/quantize.js:94)
 constexpr int kQ8Bytes = 34;  // f16 scale + 32 int8 (src/ops/quantize.js:95)
 
-enum Path : int { kAuto = 0, kGeneric = 1, kDecode = 2, kTensor = 3, kGemv = 4 };
+enum Path : int { kAuto = 0, kGeneric = 1, kDecode = 2, kTensor = 3, kGemv = 4, kSkinny = 5 };
 
 // Scratch memory a matmul launch may use (owned by the caller of the launch).
 struct Workspace {
@@ -43,6 +43,13 @@ cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, f
 bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 size_t qdecode_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
+                           int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
+
+// qskinny.cu : M <= 64, activations as f16 slabs in scratch, weights de-quantised in registers into
+// the B fragments of f16 mma.sync, f32 accumulators through all of K.
+bool qskinny_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
+size_t qskinny_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
+cudaError_t launch_qskinny(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                            int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
 
 // qgemm_tc.cu : M > 16, dequantise to bf16 tiles in shared memory, tcgen05 MMA, TMEM accumulators.

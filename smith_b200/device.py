@@ -136,7 +136,7 @@ _libc = C.CDLL(None)
 _libc.free.argtypes = [C.c_void_p]
 _libc.free.restype = None
 
-PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR, PATH_GEMV = 0, 1, 2, 3, 4
+PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_TENSOR, PATH_GEMV, PATH_SKINNY = 0, 1, 2, 3, 4, 5
 
 
 class SmithError(RuntimeError):

@@ -103,7 +103,8 @@ def test_matmul_auto_path_within_tolerance(kind, M, K, N):
     assert ok, f"worst err/bound = {worst}"
 
 
-@pytest.mark.parametrize("path", [device.PATH_GENERIC, device.PATH_DECODE, device.PATH_TENSOR, device.PATH_GEMV])
+@pytest.mark.parametrize("path", [device.PATH_GENERIC, device.PATH_DECODE, device.PATH_TENSOR, device.PATH_GEMV,
+                                  device.PATH_SKINNY])
 @pytest.mark.parametrize("kind", ["q4", "q8"])
 def test_matmul_each_path_where_supported(kind, path):
     shapes = {device.PATH_GENERIC: [(1, 64, 32), (9, 1000, 77)],
@@ -114,6 +115,9 @@ def test_matmul_each_path_where_supported(kind, path):
                                  # tensor-map boxes (narrow tiles, >= 192 group-rows) with ragged edges:
                                  # partial last stage, partial last tile, Q8's 8-column quantum
                                  (3, 6176, 1000), (1, 8192, 8200), (4, 6208, 2056)],
+              # 1, 2 and 4 row tiles; ragged last column tile; one group; K-phases that do not divide the groups
+              device.PATH_SKINNY: [(5, 256, 64), (16, 512, 1000), (17, 1024, 1192), (33, 2048, 4096), (64, 4096, 2048),
+                                   (7, 32, 8), (1, 4096, 1024), (48, 4128, 136), (64, 14336, 512)],
               device.PATH_TENSOR: [(64, 1024, 256), (512, 4096, 512), (17, 256, 128), (200, 2048, 384), (300, 1056, 72),
                                    # two k-blocks per hand-off with a zero tail, narrow column tiles, ragged N
                                    (33, 1024, 48), (100, 4160, 1024), (130, 1056, 1000)]}[path]
