@@ -181,6 +181,25 @@ int32_t smith_gguf_repack(void* ctx, uint32_t ggml_type, void* src, void* dst, u
 #define SMITH_PATH_SKINNY 5
 int32_t smith_qmatmul(void* ctx, uint32_t kind, void* a, void* b, void* c, uint64_t M, uint64_t N,
                       uint64_t K, uint64_t groups, uint32_t path);
+/* The dense (unquantised) matmul as a direct, asynchronous call on device-side buffers:
+ * c[batch,M,N] = a[batch,M,K] @ b[batch,K,N], row-major, dtype 0 = f32, 1 = f16 storage (f32 sums).
+ * It stands for the reference's matmul family (src/ops/matmul.js:13-107; shaders/matmul.metal:31-260),
+ * which the encoder path reaches under the names matmul_f32, matmul_f16, matmul_simple[_f16] and
+ * matmul_batched[_f16] with {M,N,K} or {M,N,K,batch} as uint32 at index 3.
+ * path: 0 = the reference's own rule (src/ops/matmul.js:10,28): tensor cores when M, N and K are all
+ *           at least 64, the any-shape kernel otherwise;
+ *       1 = any-shape CUDA-core kernel: every output the sequential f32 sum of the shaders, bit for bit;
+ *       2 = tensor cores (tcgen05), f32 storage split into three bf16 planes and six partial products
+ *           (error of the order of f32 rounding), f16 storage as it is;
+ *       3 = tensor cores, f32 storage rounded to bf16 once (one product; about 2^-8 relative). */
+#define SMITH_DTYPE_F32 0u
+#define SMITH_DTYPE_F16 1u
+#define SMITH_DENSE_AUTO 0u
+#define SMITH_DENSE_GENERIC 1u
+#define SMITH_DENSE_TENSOR 2u
+#define SMITH_DENSE_TENSOR_FAST 3u
+int32_t smith_matmul(void* ctx, uint32_t dtype, void* a, void* b, void* c, uint64_t M, uint64_t N, uint64_t K,
+                     uint64_t batch, uint32_t path);
 /* No counterpart in the reference, whose callers issue one matmul per weight matrix
  * (src/gguf_cache.js:121-171: wq, wk, wv on the same input; gate and up on the same input).
  * c_bufs[i] [M, n_list[i]] = a [M, K] x dequant(b_bufs[i]) for 1 to 4 packed matrices of the same K

@@ -82,6 +82,10 @@ def lib():
         _lib.oracle_gguf_dequant.argtypes = [C.c_int, p, i64, p]
         _lib.oracle_swiglu.restype = None
         _lib.oracle_swiglu.argtypes = [p, p, p, i64]
+        for name in ("oracle_dense_f32", "oracle_dense_f16"):
+            f = getattr(_lib, name)
+            f.restype = None
+            f.argtypes = [p, p, p, i64, i64, i64, i64]
     return _lib
 
 
@@ -105,6 +109,9 @@ def ref():
             _ref.ref_rmsnorm.argtypes = [p, p, p, i64, i64, C.c_float]
             _ref.ref_swiglu.restype = None
             _ref.ref_swiglu.argtypes = [p, p, p, i64]
+        if hasattr(_ref, "ref_dense"):
+            _ref.ref_dense.restype = C.c_int
+            _ref.ref_dense.argtypes = [C.c_int, C.c_int, p, p, p, i64, i64, i64, i64]
     return _ref
 
 
@@ -215,6 +222,47 @@ def swiglu(gate, up):
 
 def ref_swiglu(gate, up):
     return _swiglu(ref().ref_swiglu, gate, up)
+
+
+def _dense_operands(a, b):
+    f16 = a.dtype == np.float16
+    dt = np.float16 if f16 else np.float32
+    a = np.ascontiguousarray(a, dtype=dt)
+    b = np.ascontiguousarray(b, dtype=dt)
+    if a.ndim == 2:
+        a, b = a[None], b[None]
+    batch, M, K = a.shape
+    assert b.shape[0] == batch and b.shape[1] == K
+    return f16, a, b, batch, M, b.shape[2], K
+
+
+def dense_matmul(a, b):
+    """shaders/matmul.metal restated: c[b,M,N] = a[b,M,K] @ b[b,K,N], sequential f32 sums; f16 arrays
+    give the half-storage variants.  2-D operands give a 2-D result."""
+    two_d = np.asarray(a).ndim == 2
+    f16, a3, b3, batch, M, N, K = _dense_operands(np.asarray(a), np.asarray(b))
+    out = np.zeros((batch, M, N), np.float16 if f16 else np.float32)
+    (lib().oracle_dense_f16 if f16 else lib().oracle_dense_f32)(_ptr(a3), _ptr(b3), _ptr(out), M, N, K, batch)
+    return out[0] if two_d else out
+
+
+def have_ref_dense():
+    return have_ref() and hasattr(ref(), "ref_dense")
+
+
+def ref_dense_matmul(a, b, which):
+    """The same product from the reference's compiled shader source; which = "simple", "tiled" or
+    "batched" names the shader function (matmul_simple, matmul_f32, matmul_batched and their _f16 forms)."""
+    two_d = np.asarray(a).ndim == 2
+    f16, a3, b3, batch, M, N, K = _dense_operands(np.asarray(a), np.asarray(b))
+    out = np.zeros((batch, M, N), np.float16 if f16 else np.float32)
+    code = {"simple": 0, "tiled": 1, "batched": 2}[which]
+    if code != 2:
+        assert batch == 1
+    rc = ref().ref_dense(code, int(f16), _ptr(a3), _ptr(b3), _ptr(out), M, N, K, batch)
+    if rc != 0:
+        raise RuntimeError("a team of 64 threads could not be formed for the tiled shader")
+    return out[0] if two_d else out
 
 
 def gguf_dequant(ggml_type, blocks):

@@ -13,6 +13,7 @@
  *   oracle_matmul_q4     shaders/matmul_q4.metal:24-28,34-65
  *   oracle_matmul_q8     shaders/matmul_q8.metal:20-57
  *   oracle_rmsnorm       shaders/rmsnorm.metal:15-49, src/ops/rmsnorm.js:19-38
+ *   oracle_dense_f32/f16 shaders/matmul.metal:31-165 (f32), 172-260 (f16): the dense matmul family
  *   oracle_swiglu        shaders/swiglu.metal:12-22
  *   oracle_gguf_dequant  src/gguf.js:187-197 (Q4_0), 221-231 (Q8_0)
  *   oracle_quantize_q8   NO reference counterpart ("parity unpinned"): the
@@ -307,6 +308,50 @@ void oracle_swiglu(const float *gate, const float *up, float *out, int64_t n) {
     float silu = g / (1.0f + expf(-g));
     out[i] = silu * up[i];
   }
+}
+
+/* ---- dense matmul: shaders/matmul.metal ------------------------------------------------------
+ * matmul_simple (:116-132) and matmul_batched (:145-165): sum = 0; for k: sum += A[row,k] * B[k,col],
+ * every product and sum rounded to f32.  The tiled matmul_f32 (:31-112) keeps one accumulator per
+ * output and walks its k-tiles in order, so it forms the same sum (its zero padding of the last
+ * k-tile adds +0 terms, which can only turn a -0 result into +0).  C[b,M,N] = A[b,M,K] @ B[b,K,N]. */
+void oracle_dense_f32(const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K, int64_t batch) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t bi = 0; bi < batch; bi++)
+    for (int64_t m = 0; m < M; m++) {
+      const float *ar = a + (bi * M + m) * K;
+      const float *bm = b + bi * K * N;
+      float *cr = c + (bi * M + m) * N;
+      for (int64_t n = 0; n < N; n++) {
+        float sum = 0.0f;
+        for (int64_t k = 0; k < K; k++) sum += ar[k] * bm[k * N + n];
+        cr[n] = sum;
+      }
+    }
+}
+
+/* The f16 variants (:172-260): halves widened to f32, f32 products and sums, the sum rounded to
+ * half once (round to nearest even).  Operands and result are IEEE binary16 bit patterns. */
+void oracle_dense_f16(const uint16_t *a, const uint16_t *b, uint16_t *c, int64_t M, int64_t N, int64_t K,
+                      int64_t batch) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t bi = 0; bi < batch; bi++)
+    for (int64_t m = 0; m < M; m++) {
+      const uint16_t *ar = a + (bi * M + m) * K;
+      const uint16_t *bm = b + bi * K * N;
+      uint16_t *cr = c + (bi * M + m) * N;
+      for (int64_t n = 0; n < N; n++) {
+        float sum = 0.0f;
+        for (int64_t k = 0; k < K; k++) {
+          _Float16 x, y;
+          memcpy(&x, ar + k, 2);
+          memcpy(&y, bm + k * N + n, 2);
+          sum += (float)x * (float)y;
+        }
+        _Float16 h = (_Float16)sum;
+        memcpy(cr + n, &h, 2);
+      }
+    }
 }
 
 /* ---- GGUF block decoders: src/gguf.js:187-197 (Q4_0) and 221-231 (Q8_0) ------------- */

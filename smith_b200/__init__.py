@@ -10,6 +10,7 @@ from .checkpoint import loadQuantized, saveQuantized
 from .gguf import quantizedFromGGUF
 from .device import PRIVATE, SHARED, SmithError
 from .lifecycle import dispose, isDisposed, retain, using, withNoAlloc
+from .ops.matmul import matmul, matmul2d, matmulBatched
 from .ops.quantize import (GROUP_BYTES, GROUP_SIZE, Q8_BLOCK_BYTES, Q8_BLOCK_SIZE, matmulQ4, matmulQ8,
                            quantizeQ4, quantizeQ8)
 from .pool import poolDrain, poolFlush, poolStats

@@ -49,8 +49,15 @@ int fail(const char* fmt, ...) {
     if (e_ != cudaSuccess) return fail("%s: %s", #expr, cudaGetErrorString(e_)); \
   } while (0)
 
-enum KernelId { kMatmulQ4 = 0, kMatmulQ8 = 1, kQuantQ4 = 2, kQuantQ8 = 3, kNumKernels };
-const char* const kKernelNames[kNumKernels] = {"matmul_q4", "matmul_q8", "quantize_q4", "quantize_q8"};
+enum KernelId {
+  kMatmulQ4 = 0, kMatmulQ8 = 1, kQuantQ4 = 2, kQuantQ8 = 3,
+  // the dense matmul family (shaders/matmul.metal): tiled, simple and batched, f32 and f16 storage
+  kMatmulF32, kMatmulF16, kMatmulSimple, kMatmulSimpleF16, kMatmulBatched, kMatmulBatchedF16,
+  kNumKernels
+};
+const char* const kKernelNames[kNumKernels] = {"matmul_q4", "matmul_q8", "quantize_q4", "quantize_q8",
+                                               "matmul_f32", "matmul_f16", "matmul_simple", "matmul_simple_f16",
+                                               "matmul_batched", "matmul_batched_f16"};
 
 struct Context {
   uint32_t magic = kCtxMagic;
@@ -268,6 +275,37 @@ int do_qmatmul(Context* c, int kind, const float* A, const uint8_t* B, float* C,
   return 0;
 }
 
+// The dense matmul, C[b,M,N] = A[b,M,K] @ B[b,K,N].  path 0 follows the reference's own rule
+// (src/ops/matmul.js:10,28): the tiled kernel's successor -- the tensor-core kernel -- when M, N and K
+// are all at least 64, the any-shape kernel otherwise.
+int do_dense(Context* c, int dtype, const void* A, const void* B, void* C, uint64_t M, uint64_t N, uint64_t K,
+             uint64_t batch, uint32_t path) {
+  if (dtype != kDenseF32 && dtype != kDenseF16) return fail("dtype must be 0 (f32) or 1 (f16), got %d", dtype);
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  const size_t es = dtype == kDenseF16 ? 2 : 4;
+  int p = (int)path;
+  if (p == kDenseAuto)
+    p = (M >= 64 && N >= 64 && K >= 64 && dense_tc_supports(dtype, (int64_t)M, (int64_t)N, (int64_t)K)) ? kDenseTcExact
+                                                                                                       : kDenseGeneric;
+  cudaError_t e = cudaSuccess;
+  if (p == kDenseGeneric) {
+    e = launch_dense_generic(dtype, A, B, C, (int64_t)M, (int64_t)N, (int64_t)K, (int64_t)batch, c->stream);
+  } else if (p == kDenseTcExact || p == kDenseTcFast) {
+    if (K == 0 || !dense_tc_supports(dtype, (int64_t)M, (int64_t)N, (int64_t)K))
+      return fail("tensor-core matmul does not take M=%llu N=%llu K=%llu dtype=%d", (unsigned long long)M,
+                  (unsigned long long)N, (unsigned long long)K, dtype);
+    if (ensure_workspace(c, dense_tc_workspace_bytes(dtype, p, (int64_t)M, (int64_t)N, (int64_t)K))) return 1;
+    for (uint64_t b = 0; b < batch && e == cudaSuccess; b++)
+      e = launch_dense_tc(dtype, p, static_cast<const uint8_t*>(A) + b * M * K * es,
+                          static_cast<const uint8_t*>(B) + b * K * N * es, static_cast<uint8_t*>(C) + b * M * N * es,
+                          (int64_t)M, (int64_t)N, (int64_t)K, c->ws, c->stream);
+  } else {
+    return fail("unknown dense path %u", path);
+  }
+  if (e != cudaSuccess) return fail("dense matmul launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 }  // namespace
 
 struct SmithEncoder {
@@ -316,6 +354,33 @@ int submit(SmithEncoder* enc, cudaEvent_t e0, cudaEvent_t e1) {
     if (e1) CU_TRY(cudaEventRecord(e1, c->stream));
     if (back && M * N)
       CU_TRY(cudaMemcpyAsync(enc->bufs[2]->host, cc, M * N * 4, cudaMemcpyDeviceToHost, c->stream));
+    return 0;
+  }
+  if (id >= kMatmulF32 && id <= kMatmulBatchedF16) {
+    const char* name = kKernelNames[id];
+    const bool batched = (id == kMatmulBatched || id == kMatmulBatchedF16);
+    const int dtype = (id == kMatmulF16 || id == kMatmulSimpleF16 || id == kMatmulBatchedF16) ? kDenseF16 : kDenseF32;
+    const size_t es = dtype == kDenseF16 ? 2 : 4, need = batched ? 16 : 12;
+    if (!enc->bufs[0] || !enc->bufs[1] || !enc->bufs[2]) return fail("%s needs buffers 0, 1 and 2", name);
+    if (enc->bytes[3].size() < need)
+      return fail("%s needs %zu bytes %s at index 3", name, need, batched ? "{M,N,K,batch}" : "{M,N,K}");
+    uint32_t prm[4] = {0, 0, 0, 1};
+    memcpy(prm, enc->bytes[3].data(), need);
+    const uint64_t M = prm[0], N = prm[1], K = prm[2], batch = prm[3];
+    const void *a = nullptr, *b = nullptr;
+    void* cc = nullptr;
+    bool back = false;
+    if (input_ptr(c, enc->bufs[0], 0, batch * M * K * es, &a)) return 1;
+    if (input_ptr(c, enc->bufs[1], 1, batch * K * N * es, &b)) return 1;
+    if (output_ptr(c, enc->bufs[2], 2, batch * M * N * es, &cc, &back)) return 1;
+    // the tiled kernels' successor is the tensor-core kernel; the simple and batched kernels keep
+    // their one-thread-per-output order of operations (bit-identical sums)
+    const uint32_t path = (id == kMatmulF32 || id == kMatmulF16) ? kDenseAuto : kDenseGeneric;
+    if (e0) CU_TRY(cudaEventRecord(e0, c->stream));
+    if (do_dense(c, dtype, a, b, cc, M, N, K, batch, path)) return 1;
+    if (e1) CU_TRY(cudaEventRecord(e1, c->stream));
+    if (back && batch * M * N)
+      CU_TRY(cudaMemcpyAsync(enc->bufs[2]->host, cc, batch * M * N * es, cudaMemcpyDeviceToHost, c->stream));
     return 0;
   }
   if (id == kQuantQ4 || id == kQuantQ8) {
@@ -820,6 +885,23 @@ int32_t smith_qmatmul(void* p, uint32_t kind, void* a, void* b, void* cbuf, uint
   if (bc->bytes < M * N * 4) return fail("smith_qmatmul: C holds %llu bytes, needs %llu", (unsigned long long)bc->bytes,
                                          (unsigned long long)(M * N * 4));
   return do_qmatmul(c, (int)kind, (const float*)ba->dev, (const uint8_t*)bb->dev, (float*)bc->dev, M, N, K, groups, path);
+}
+
+int32_t smith_matmul(void* p, uint32_t dtype, void* a, void* b, void* cbuf, uint64_t M, uint64_t N, uint64_t K,
+                     uint64_t batch, uint32_t path) {
+  Context* c = as_ctx(p);
+  Buffer *ba = as_buf(a), *bb = as_buf(b), *bc = as_buf(cbuf);
+  if (!c || !ba || !bb || !bc) return 1;
+  if (!ba->dev || !bb->dev || !bc->dev) return fail("smith_matmul needs buffers with a device side");
+  if (dtype != kDenseF32 && dtype != kDenseF16) return fail("dtype must be 0 (f32) or 1 (f16), got %u", dtype);
+  const uint64_t es = dtype == kDenseF16 ? 2 : 4;
+  if (ba->bytes < batch * M * K * es) return fail("smith_matmul: A holds %llu bytes, needs %llu",
+                                                  (unsigned long long)ba->bytes, (unsigned long long)(batch * M * K * es));
+  if (bb->bytes < batch * K * N * es) return fail("smith_matmul: B holds %llu bytes, needs %llu",
+                                                  (unsigned long long)bb->bytes, (unsigned long long)(batch * K * N * es));
+  if (bc->bytes < batch * M * N * es) return fail("smith_matmul: C holds %llu bytes, needs %llu",
+                                                  (unsigned long long)bc->bytes, (unsigned long long)(batch * M * N * es));
+  return do_dense(c, (int)dtype, ba->dev, bb->dev, bc->dev, M, N, K, batch, path);
 }
 
 int32_t smith_qmatmul_multi(void* p, uint32_t kind, void* a, uint32_t count, void* const* b_bufs, void* const* c_bufs,

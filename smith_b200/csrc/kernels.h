@@ -58,6 +58,16 @@ size_t qgemm_tc_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
 cudaError_t launch_qgemm_tc(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
                             int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
 
+// dense_generic.cu / dense_tc.cu : the unquantised matmul, f32 or f16 storage.
+enum DenseType : int { kDenseF32 = 0, kDenseF16 = 1 };
+enum DensePath : int { kDenseAuto = 0, kDenseGeneric = 1, kDenseTcExact = 2, kDenseTcFast = 3 };
+cudaError_t launch_dense_generic(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                 int64_t batch, cudaStream_t s);
+bool dense_tc_supports(int dtype, int64_t M, int64_t N, int64_t K);
+size_t dense_tc_workspace_bytes(int dtype, int mode, int64_t M, int64_t N, int64_t K);
+cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                            Workspace ws, cudaStream_t s);
+
 // qgemv.cu : M <= 4, activations as int8 digit pairs, dp4a against the packed codes.
 bool qgemv_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 cudaError_t launch_qgemv(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N,

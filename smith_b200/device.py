@@ -96,6 +96,7 @@ SYMBOLS = {
     "smith_q8_pack": (_i32, [_p, _p, _p, _u64, _u64]),
     "smith_gguf_repack": (_i32, [_p, _u32, _p, _p, _u64, _u64]),
     "smith_qmatmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
+    "smith_matmul": (_i32, [_p, _u32, _p, _p, _p, _u64, _u64, _u64, _u64, _u32]),
     "smith_qmatmul_path": (_i32, [_u32, _u64, _u64, _u64]),
     "smith_qmatmul_list_create": (_p, [_p, _u32, _u64, C.POINTER(SmithListItem), _u32]),
     "smith_qmatmul_list_create_gather": (_p, [_p, _u32, _u64, C.POINTER(SmithListItem), C.POINTER(SmithListGather), _u32, _u32,
@@ -433,6 +434,15 @@ def ggufRepack(ggmlType, srcBuffer, dstBuffer, outDim, inDim):
 
 def qmatmul(kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path=PATH_AUTO):
     _check(lib.smith_qmatmul(ctx(), kind, aBuffer, bBuffer, cBuffer, M, N, K, groups, path), "qmatmul")
+
+
+DTYPE_F32, DTYPE_F16 = 0, 1
+DENSE_AUTO, DENSE_GENERIC, DENSE_TENSOR, DENSE_TENSOR_FAST = 0, 1, 2, 3
+
+
+def matmul(dtype, aBuffer, bBuffer, cBuffer, M, N, K, batch=1, path=DENSE_AUTO):
+    """smith_matmul: the dense matmul c[batch,M,N] = a[batch,M,K] @ b[batch,K,N] on device-side buffers."""
+    _check(lib.smith_matmul(ctx(), dtype, aBuffer, bBuffer, cBuffer, M, N, K, batch, path), "matmul")
 
 
 def qmatmulStatic(kind, aPtr, bPtr, cPtr, M, N, K, groups, streamPtr=None):

@@ -36,8 +36,9 @@ def setPeaks(hbmGBs=None, tensorTFlops=None, source="caller"):
 
 
 def algorithmicCost(kernelName, params):
-    """(bytes, flops) of one dispatch of a quantized-path kernel from its parameter block, else None.
-    matmul_q4 / matmul_q8: params = [M, N, K, groups]; quantize_q4 / quantize_q8: params = [K, N]."""
+    """(bytes, flops) of one dispatch of a kernel from its parameter block, else None.
+    matmul_q4 / matmul_q8: params = [M, N, K, groups]; quantize_q4 / quantize_q8: params = [K, N];
+    matmul_f32 / matmul_f16 / matmul_simple[_f16] / matmul_batched[_f16]: params = [M, N, K(, batch)]."""
     if params is None:
         return None
     p = [int(v) for v in params]
@@ -49,6 +50,12 @@ def algorithmicCost(kernelName, params):
         K, N = p[:2]
         bb = 24 if kernelName == "quantize_q4" else 34
         return 4 * K * N + ((K + 31) // 32) * N * bb, 0
+    if kernelName.startswith("matmul_") and len(p) >= 3:
+        # the dense family: [M, N, K] or [M, N, K, batch]; f16 storage in the names that end in _f16
+        M, N, K = p[:3]
+        batch = p[3] if len(p) >= 4 and "batched" in kernelName else 1
+        es = 2 if kernelName.endswith("_f16") else 4
+        return batch * es * (M * K + K * N + M * N), batch * 2 * M * K * N
     return None
 
 

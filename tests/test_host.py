@@ -173,3 +173,31 @@ def test_profile_algorithmic_cost_and_roofline_fields():
         P._kernelStats.clear()
         P._kernelStats.update(saved[0])
         P._totalDispatches, P._totalGpuMs = saved[1], saved[2]
+
+
+def test_dense_matmul_operator_messages_and_parameter_blocks():
+    # src/ops/matmul.js:21-23, 91-93 -- raised before anything touches the device; src/dispatch.js:57-63, 92-94
+    from smith_b200.ops import matmul as MM
+
+    class _T(_FakeTensor):
+        def __init__(self, shape):
+            super().__init__(shape)
+            self.strides = smith.tensor.computeStrides(shape)
+
+    with pytest.raises(ValueError) as e:
+        MM.matmul(_T([2, 3]), _T([4, 2]))
+    assert str(e.value) == "matmul: inner dims don't match: 3 vs 4"
+    with pytest.raises(ValueError) as e:
+        MM.matmul(_T([3]), _T([3, 2]))
+    assert str(e.value) == "matmul requires at least 2D tensors, got 1D and 2D"
+    with pytest.raises(ValueError) as e:
+        MM._broadcastShapes([2, 3], [4, 3])
+    assert str(e.value) == "Cannot broadcast shapes [2,3] and [4,3]"
+    assert MM._broadcastShapes([5, 1], [4]) == [5, 4]
+    assert MM.matmulParams(3, 4, 5).tolist() == [3, 4, 5] and MM.matmulParams(3, 4, 5).dtype == np.uint32
+    assert MM.batchMatmulParams(3, 4, 5, 6).tolist() == [3, 4, 5, 6]
+    assert MM.k("matmul_simple", "f16") == "matmul_simple_f16" and MM.k("matmul_batched", "f32") == "matmul_batched"
+    assert MM.TILE_THRESHOLD == 64
+    from smith_b200 import profile as P
+    assert P.algorithmicCost("matmul_f32", [64, 128, 256]) == (4 * (64 * 256 + 256 * 128 + 64 * 128), 2 * 64 * 128 * 256)
+    assert P.algorithmicCost("matmul_batched_f16", [8, 16, 32, 5]) == (5 * 2 * (8 * 32 + 32 * 16 + 8 * 16), 5 * 2 * 8 * 16 * 32)

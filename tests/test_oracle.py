@@ -219,3 +219,49 @@ def test_gguf_q8_0_blocks_are_the_matmul_q8_blocks():
     w_file = O.gguf_dequant(8, blocks).reshape(out_dim, in_dim)   # the reference's f32 weights, [outDim, inDim]
     packed = np.ascontiguousarray(blocks.transpose(1, 0, 2)).reshape(-1)
     assert np.array_equal(O.dequant(packed, in_dim, out_dim, "q8").view(np.uint32), w_file.T.copy().view(np.uint32))
+
+
+# ---------------------------------------------------------------- dense matmul (shaders/matmul.metal)
+DENSE_SHAPES = [(1, 1, 1), (2, 3, 2), (16, 16, 16), (33, 70, 65), (64, 64, 64), (70, 100, 96)]
+
+
+@pytest.mark.skipif(not (O.have_ref() and O.have_ref_dense()), reason="oracle/_ref not built (no reference checkout on this machine)")
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_dense_restatement_equals_the_compiled_shaders(dtype):
+    """oracle_dense_f32 / oracle_dense_f16 against matmul_simple, the tiled matmul_f32 (run as teams of
+    64 threads with real barriers) and matmul_batched of shaders/matmul.metal compiled as C++: bit for bit."""
+    rng = np.random.default_rng(17)
+    bits = np.uint16 if dtype == np.float16 else np.uint32
+    for M, K, N in DENSE_SHAPES:
+        a, b = rng.standard_normal((M, K)).astype(dtype), rng.standard_normal((K, N)).astype(dtype)
+        want = O.dense_matmul(a, b)
+        assert np.array_equal(want.view(bits), O.ref_dense_matmul(a, b, "simple").view(bits)), (M, K, N)
+        # the tiled kernel pads its last k-tile with zeros: +0 terms, which only a -0 sum could notice
+        assert np.array_equal(want, O.ref_dense_matmul(a, b, "tiled")), (M, K, N)
+    a, b = rng.standard_normal((3, 9, 17)).astype(dtype), rng.standard_normal((3, 17, 5)).astype(dtype)
+    assert np.array_equal(O.dense_matmul(a, b).view(bits), O.ref_dense_matmul(a, b, "batched").view(bits))
+
+
+def test_dense_known_answers_of_the_reference_tests():
+    # tests/matmul.test.js:15-48 and tests/f16.test.js:88-98
+    for dtype in (np.float32, np.float16):
+        c = O.dense_matmul(np.array([[1, 2], [3, 4]], dtype), np.array([[5, 6], [7, 8]], dtype))
+        assert c.dtype == dtype and c.tolist() == [[19, 22], [43, 50]]
+        c = O.dense_matmul(np.array([[1, 2, 3], [4, 5, 6]], dtype), np.array([[7, 8], [9, 10], [11, 12]], dtype))
+        assert c.tolist() == [[58, 64], [139, 154]]
+    a = np.random.default_rng(2).standard_normal((16, 16)).astype(np.float32)
+    assert np.array_equal(O.dense_matmul(a, np.eye(16, dtype=np.float32)), a)          # :74-86
+
+
+def test_dense_restatement_is_a_sequential_f32_sum():
+    rng = np.random.default_rng(4)
+    a, b = rng.standard_normal((5, 300)).astype(np.float32), rng.standard_normal((300, 7)).astype(np.float32)
+    want = np.zeros((5, 7), np.float32)
+    for k in range(300):
+        want = (want + (a[:, k:k + 1] * b[k:k + 1, :]).astype(np.float32)).astype(np.float32)
+    assert np.array_equal(O.dense_matmul(a, b), want)
+    ah, bh = a.astype(np.float16), b.astype(np.float16)
+    want = np.zeros((5, 7), np.float32)
+    for k in range(300):
+        want = (want + (ah[:, k:k + 1].astype(np.float32) * bh[k:k + 1, :].astype(np.float32))).astype(np.float32)
+    assert np.array_equal(O.dense_matmul(ah, bh), want.astype(np.float16))
