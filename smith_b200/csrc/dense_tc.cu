@@ -10,8 +10,11 @@
 // significand bits, so the three planes hold x exactly (bf16 has f32's exponent range, so no scaling
 // is needed).  The product a * b is then accumulated as the six partial products
 //     ah*bh + ah*bm + am*bh + ah*bl + al*bh + am*bm
-// into one f32 accumulator; the three left out (am*bl, al*bm, al*bl) are below 2^-23 of |a*b|, the
-// size of one f32 rounding.  Six MMAs at the bf16 rate are the cost of three at the tf32 rate, with
+// in tensor memory; the three left out (am*bl, al*bm, al*bl) are below 2^-23 of |a*b|, the size of
+// one f32 rounding.  The tensor core truncates each f32 accumulation, so ah*bh has an accumulator of
+// its own and the five small products share a second one (added in the epilogue): the error is then
+// that of the K/16 truncated accumulations of the leading product, about 1e-7 * ||a_m|| * ||b_n||
+// at K = 2048 and growing in proportion to K.  Six MMAs at the bf16 rate are the cost of three at the tf32 rate, with
 // 6 instead of 8 bytes per element staged through shared memory.  A `fast` mode keeps only ah*bh
 // (one plane each, 2^-9 relative per factor) for callers that accept bf16 inputs.
 //
@@ -220,11 +223,17 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
         if (!ok) break;
         tc_fence_after();
         for (int t = 0; t < p.MT; t++) {
-          const uint32_t d_tmem = tmem_base + (uint32_t)(t * p.BN);
+          // With three planes the leading product ah*bh has an accumulator of its own and the five
+          // small ones share a second: the tensor core truncates every f32 accumulation, so small
+          // terms added to the large sum would each cost an ulp of the LARGE sum.
+          const uint32_t d_main = tmem_base + (uint32_t)(t * p.BN);
+          const uint32_t d_corr = tmem_base + (uint32_t)((p.MT + t) * p.BN);
           for (int q = 0; q < p.npairs; q++) {
-            const uint32_t a_lo = lo0 + soff + (uint32_t)((int)((p.pair_a >> (4 * q)) & 15u) * p.MT + t) * a_tile_step;
-            const uint32_t b_lo = lo0 + soff + b_off + ((p.pair_b >> (4 * q)) & 15u) * b_tile_step;
-            umma_f16_kblock(d_tmem, a_lo, b_lo, desc_hi, p.idesc, (kb > 0 || q > 0) ? 1u : 0u);
+            const uint32_t pa = (p.pair_a >> (4 * q)) & 15u, pb = (p.pair_b >> (4 * q)) & 15u;
+            const uint32_t a_lo = lo0 + soff + (uint32_t)((int)pa * p.MT + t) * a_tile_step;
+            const uint32_t b_lo = lo0 + soff + b_off + pb * b_tile_step;
+            const bool lead = (pa | pb) == 0u;
+            umma_f16_kblock(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, (kb > 0 || (!lead && q > 0)) ? 1u : 0u);
           }
         }
         umma_commit(smem_u32(&empty[s]));
@@ -253,6 +262,13 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
           tmem_ld_wait();
+          if (p.npairs > 1) {
+            uint32_t r2[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((p.MT + t) * p.BN + c), r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<float4*>(stage + lane * kPitch + i) =
@@ -335,7 +351,8 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   if (stages > kMaxStages) stages = kMaxStages;
   pl.stages = stages;
   int cols = 32;                                 // the epilogue reads whole 32-column chunks
-  while (cols < (pl.MT - 1) * pl.BN + (pl.BN + 31) / 32 * 32) cols <<= 1;
+  const int accs = pl.MT * (exact ? 2 : 1);      // three planes: a second accumulator for the small products
+  while (cols < (accs - 1) * pl.BN + (pl.BN + 31) / 32 * 32) cols <<= 1;
   pl.tmem_cols = cols;
   pl.smem = 1024 + (size_t)stages * pl.stage_bytes;
   pl.Kp = (K + 7) / 8 * 8;
@@ -394,7 +411,7 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
   if (!dense_tc_supports(dtype, M, N, K)) return cudaErrorInvalidValue;
   const Plan pl = make_plan(dtype, mode, M, N, K);
   if (pl.stages < 2 || pl.smem > 227 * 1024) return cudaErrorInvalidValue;
-  if (!ws.ptr || ws.bytes < dense_tc_workspace_bytes(dtype, mode, M, N, K) || (reinterpret_cast<uintptr_t>(ws.ptr) & 1023))
+  if (!ws.ptr || ws.bytes < dense_tc_workspace_bytes(dtype, mode, M, N, K) || (reinterpret_cast<uintptr_t>(ws.ptr) & 255))
     return cudaErrorInvalidValue;
   const bool f16 = dtype == kDenseF16;
   if (f16 && (reinterpret_cast<uintptr_t>(A) & 15)) return cudaErrorMisalignedAddress;
@@ -437,7 +454,7 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
   Params p{};
   p.C = C, p.M = (int)M, p.N = (int)N, p.K = (int)K, p.out_f16 = f16 ? 1 : 0;
   p.MT = pl.MT, p.BN = pl.BN, p.planes = pl.planes, p.npairs = pl.npairs;
-  // smallest partial products first within a k-block
+  // the five small products (smallest first), then the leading one
   static const int pa[kMaxPairs] = {1, 2, 0, 1, 0, 0}, pb[kMaxPairs] = {1, 0, 2, 0, 1, 0};
   p.pair_a = p.pair_b = 0;
   if (pl.npairs == 6)

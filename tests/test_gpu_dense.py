@@ -137,6 +137,7 @@ def test_non_finite_inputs_propagate():
     a[3, 7] = np.inf
     a[100, 0] = np.nan
     b[5, 9] = 3.0e38                                        # rounds to infinity in bf16: must stay finite
+    a[:, 5] *= 1e-4
     got = dense_on_device(a, b, device.DENSE_TENSOR)
     want = O.dense_matmul(a, b)
     assert np.all(np.isnan(got[100]))
