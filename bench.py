@@ -71,6 +71,12 @@ WORKLOADS.update({
     "pack_q8_4096x14336": dict(kind=8, pack=True, M=0, K=4096, N=14336, std=0.02),
     "pack_q4_4096x128256": dict(kind=4, pack=True, M=0, K=4096, N=128256, std=0.02),
 })
+# The unquantised sibling (src/ops/matmul.js): one dense product per step
+WORKLOADS.update({
+    "dense_f32_4096x4096x4096": dict(dense="f32", M=4096, K=4096, N=4096, kind=0, std=1.0),
+    "dense_f16_4096x4096x4096": dict(dense="f16", M=4096, K=4096, N=4096, kind=0, std=1.0),
+    "dense_f32_512x4096x11008": dict(dense="f32", M=512, K=4096, N=11008, kind=0, std=1.0),
+})
 DEFAULT = "q4_decode_gemv_4096x14336_m1"
 L2_BYTES = 126e6
 
@@ -188,6 +194,31 @@ def run_reference_arm(args, wl, name):
     if wl.get("pack"):
         print(json.dumps({"impl": "reference", "unavailable": "the reference's packer is JavaScript and no JS runtime is "
                           "installed; its C restatement is timed as cpu_baseline of the packer workload itself"}))
+        return
+    if wl.get("dense"):
+        import numpy as np
+        from oracle import oracle as O
+        f16 = wl["dense"] == "f16"
+        M, K, N, rows = wl["M"], wl["K"], wl["N"], 8
+        rng = np.random.default_rng(5)
+        a = rng.standard_normal((rows, K)).astype(np.float16 if f16 else np.float32)
+        b = rng.standard_normal((K, N)).astype(a.dtype)
+        times = []
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            O.dense_matmul(a, b)
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        per = sum(times) / len(times)
+        value = 2.0 * rows * N * K / per / 1e12
+        sample = f"{rows} of {M} rows per step (the sequential-sum restatement of shaders/matmul.metal, all host threads)"
+        print(json.dumps({
+            "impl": "reference", "metric": "dense matmul TFLOP/s (2 M N K / time)", "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "M": M, "K": K, "N": N, "note": "the reference's Metal path is unavailable on this box"},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": O.max_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
         return
     times = []
     info = None
@@ -1076,6 +1107,129 @@ def run_pack_workload(args, name, wl, ctxinfo):
     return line
 
 
+def run_dense_workload(args, name, wl, ctxinfo, steps=None, with_cpu=True, with_e2e=True):
+    """The dense matmul c = a @ b through smith_matmul on device-resident operands; a step is one product
+    (f32 storage: two split launches + the tcgen05 kernel; f16 storage: one transposition + the kernel).
+    b alternates between two matrices, so a step's operands (>= 128 MB) do not fit L2.  Algorithmic flops
+    2 M N K; the f32 path executes six bf16 products per f32 product, so its ceiling is a sixth of the
+    bf16 peak and the line says so."""
+    import numpy as np
+    import torch
+    import smith_b200 as smith
+    from oracle import oracle as O
+    from smith_b200 import device as D
+    world, rank, local, stream = ctxinfo
+    f16 = wl["dense"] == "f16"
+    M, K, N = wl["M"], wl["K"], wl["N"]
+    dt, es, npdt = (D.DTYPE_F16, 2, np.float16) if f16 else (D.DTYPE_F32, 4, np.float32)
+    rng = np.random.default_rng(5)
+    a_h = rng.standard_normal((M, K)).astype(npdt)
+    b_h = [rng.standard_normal((K, N)).astype(npdt) for _ in range(2)]
+    a = D.alloc(M * K * es, D.PRIVATE)
+    bs = [D.alloc(K * N * es, D.PRIVATE) for _ in range(2)]
+    c = D.alloc(M * N * es, D.PRIVATE)
+    D.upload(a, a_h)
+    for buf, h in zip(bs, b_h):
+        D.upload(buf, h)
+    steps = min(args.steps, 50) if steps is None else steps
+    warm = max(min(args.warmup, 5), 3)
+    D.matmul(dt, a, bs[0], c, M, N, K)
+    D.synchronize()
+    if D.kernelStatus() != 0:
+        raise SystemExit("a bounded device-side wait gave up")
+    # parity before timing: 16 rows of the product against the CPU restatement
+    r0, nr = (M // 2) // 8 * 8, 16
+    got = D.download(c, nr * N * es, npdt, offset=r0 * N * es).reshape(nr, N).astype(np.float64)
+    if f16:
+        want = a_h[r0:r0 + nr].astype(np.float64) @ b_h[0].astype(np.float64)
+        bound = 2.0 ** -10 * np.abs(want) + 4e-6 * np.linalg.norm(a_h[r0:r0 + nr].astype(np.float64), axis=1)[:, None] * \
+            np.linalg.norm(b_h[0].astype(np.float64), axis=0)[None, :]
+        what = "16 rows against the exact product: 2^-10 |c| (one rounding to half) + 4e-6 ||a_m|| ||b_n||"
+    else:
+        want = O.dense_matmul(a_h[r0:r0 + nr], b_h[0]).astype(np.float64)
+        bound = 4e-6 * np.linalg.norm(a_h[r0:r0 + nr].astype(np.float64), axis=1)[:, None] * \
+            np.linalg.norm(b_h[0].astype(np.float64), axis=0)[None, :]
+        what = "16 rows against the sequential f32 sums of the shaders: 4e-6 ||a_m|| ||b_n||"
+    worst = float((np.abs(got - want) / bound).max())
+    parity = {"checked": True, "ok": bool(worst <= 1.0), "worst_err_over_bound": worst, "what": what}
+    if not parity["ok"]:
+        raise SystemExit(f"dense product outside its tolerance: worst err/bound = {worst}")
+    for i in range(warm):
+        D.matmul(dt, a, bs[i % 2], c, M, N, K)
+    D.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    n0 = D.launchCount()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        D.matmul(dt, a, bs[i % 2], c, M, N, K)
+    e1.record(stream)
+    D.synchronize()
+    torch.cuda.synchronize()
+    launches = D.launchCount() - n0
+    step_s = e0.elapsed_time(e1) * 1e-3 / steps
+    e2e = None
+    if with_e2e:
+        ta, tb = smith.tensorFrom(a_h.ravel(), [M, K], "f32") if not f16 else None, None
+        if f16:                                   # f16 tensors are filled through their views (tensorFrom converts element by element)
+            ta, tb = smith.create([M, K], "f16"), smith.create([K, N], "f16")
+            ta.data[:] = a_h.view(np.uint16).ravel()
+            tb.data[:] = b_h[0].view(np.uint16).ravel()
+        else:
+            tb = smith.tensorFrom(b_h[0].ravel(), [K, N], "f32")
+        out = smith.matmul(ta, tb)
+        smith.tensor.release(out)
+        n_e2e = 3
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            out = smith.matmul(ta, tb)
+            head = float(out.data[0])
+            smith.tensor.release(out)
+        e2e_s = (time.perf_counter() - t0) / n_e2e
+        e2e = {"value": 2.0 * M * N * K / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": (M * K + K * N) * es,
+               "d2h_bytes_per_step": M * N * es, "steps": n_e2e, "ms_per_call": e2e_s * 1e3,
+               "note": "operator API: matmul(a, b) on host tensors (H2D of both operands from page-locked memory, "
+                       "the launches, D2H of the whole product, wait)"}
+        for t in (ta, tb):
+            smith.tensor.release(t)
+    clocks = sampler.stop()
+    peaks = measured_peaks()
+    ach = 2.0 * M * N * K / step_s / 1e12
+    products = 1 if f16 else 6
+    line = {
+        "metric": "dense matmul TFLOP/s (2 M N K / time)", "value": ach, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+        "warmup": warm, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 storage, f32 sums" if f16 else "f32 storage as three bf16 planes, six partial products, f32 sums",
+        "data": "synthetic",
+        "config": {"workload": name, "M": M, "K": K, "N": N, "launches_per_step": launches // steps,
+                   "kernel": "dense_tc_kernel (tcgen05)", "l2": "b alternates between two matrices; operands of a step exceed L2",
+                   "timing": "CUDA events on the launch stream, split / transposition launches included"},
+        "parity": parity, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
+                     "traffic": None, "peak_source": peaks["source"], "peak_kind": "cuBLAS bf16 burst",
+                     "frac_of_nominal": ach / 2250.0, "algorithmic_per_launch": 2 * M * N * K, "launch_us": step_s * 1e6,
+                     "bf16_products_per_product": products, "mma_tflops_executed": ach * products,
+                     "frac_mma_executed": ach * products / peaks["tensor"]},
+        "clocks": clocks,
+    }
+    if with_cpu and not args.no_cpu:
+        rows = 8
+        O.dense_matmul(a_h[:rows], b_h[0])
+        reps, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < min(args.cpu_seconds, 5.0):
+            O.dense_matmul(a_h[:rows], b_h[0])
+            reps += 1
+        el = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 2.0 * rows * N * K * reps / el / 1e12, "unit": "TFLOP/s", "cores": O.max_threads(),
+                                "kind": "port", "sample": f"{reps} runs of {rows} of {M} rows, {el:.1f} s of CPU work"}
+    else:
+        line["cpu_baseline"] = None
+    for x in [a, c] + bs:
+        D.releaseBuffer(x)
+    return line
+
+
 SECONDARY = ["q4_prefill_4096x14336_m512", "q8_prefill_gemm_4096x11008_m512", "q4_gemv_4096x4096_m1"]
 
 
@@ -1117,6 +1271,10 @@ def main():
         if world != 1:
             raise SystemExit("the packer workloads run on one GPU")
         line = run_pack_workload(args, args.workload, wl, ctxinfo)
+    elif wl.get("dense"):
+        if world != 1:
+            raise SystemExit("the dense workloads run on one GPU")
+        line = run_dense_workload(args, args.workload, wl, ctxinfo)
     elif "step" in wl:
         line = run_step_workload(args, wl, ctxinfo)
     else:
@@ -1139,6 +1297,14 @@ def main():
                         "frac_of_sustained_peak": (l2["roofline"]["achieved"] / measured_peaks()["tensor_sustained"]
                                                    if l2["roofline"]["bound"] == "tensor" else None),
                         "parity": l2["parity"], "clocks": l2["clocks"]})
+        for nm in (["dense_f32_4096x4096x4096", "dense_f16_4096x4096x4096"] if world == 1 else []):
+            try:
+                l4 = run_dense_workload(args, nm, WORKLOADS[nm], ctxinfo, steps=10, with_cpu=False, with_e2e=False)
+                sec.append({"workload": nm, "value": l4["value"], "unit": l4["unit"], "steps": l4["steps"],
+                            "ms_per_step": l4["ms_per_step"], "kernel": l4["config"]["kernel"], "roofline": l4["roofline"],
+                            "parity": l4["parity"], "clocks": l4["clocks"]})
+            except (SystemExit, Exception) as e:
+                sec.append({"workload": nm, "error": str(e)[:300]})
         # ... and, at every GPU count, the 70B-shaped decode step: the workload on which sharding pays
         # (52 GB of packed weights; several GPUs: tensor parallel with the all-reduce after wo / down and
         # the all-gather of the logits fused into the GEMV kernel).

@@ -78,7 +78,11 @@ void* smith_compile_source(void* ctx, const char* source, char** error_out);
  * f32 [M,K], 1=packed B, 2=C f32 [M,N]; bytes at 3 = uint32 {M,N,K,groups}, as
  * src/ops/quantize.js:80-87 binds them) and the new "quantize_q4",
  * "quantize_q8" (buffers 0=W f32 [K,N], 1=packed out; bytes at 2 = uint32
- * {K,N}).  NULL for anything else. */
+ * {K,N}); the dense family "matmul_f32", "matmul_f16", "matmul_simple",
+ * "matmul_simple_f16" (buffers 0=A [M,K], 1=B [K,N], 2=C [M,N]; bytes at 3 =
+ * uint32 {M,N,K}) and "matmul_batched", "matmul_batched_f16" (leading batch
+ * dimension on all three; bytes at 3 = uint32 {M,N,K,batch}), as
+ * src/ops/matmul.js:26-52,70-79 binds them.  NULL for anything else. */
 void* smith_create_pipeline(void* ctx, void* library, const char* fn_name);
 
 typedef struct SmithEncoder SmithEncoder;
