@@ -22,9 +22,8 @@
 //  1. split kernels: A -> planes [P][Mp][Kp] (row-major as A is), B -> planes [P][Np][Kp]
 //     TRANSPOSED, so that both operands are K-major for the MMA and rows start on 16 bytes.  For f16
 //     storage A is read in place and only B is transposed.
-//  2. dense_tc_kernel: one CTA computes MT x 128 rows by BN columns through a ring of stages
-//     {A planes' tiles, B planes' tiles}: 64 k per stage in rows of 128 bytes (128-byte swizzle), or,
-//     for the three-plane 256 x 128 tile, 32 k per stage in rows of 64 bytes (64-byte swizzle).
+//  2. dense_tc_kernel: one CTA computes MT x 128 rows by BN columns, 64 k at a time, through a ring
+//     of stages {A planes' tiles, B planes' tiles}.
 //       warp 0  producer: one thread issues the stage's tensor-map loads (128-byte swizzle)
 //       warp 1  allocates tensor memory; one thread issues, per stage and row tile, the 4 MMAs
 //               (128 x BN x 16) of each plane pair, then tcgen05.commit frees the stage
@@ -35,7 +34,6 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <stdlib.h>
 
 #include "kernels.h"
 #include "pipeline.cuh"
@@ -45,7 +43,8 @@
 namespace smith {
 namespace {
 
-constexpr int kBM = 128;
+constexpr int kBM = 128, kBK = 64;
+constexpr int kATile = kBM * kBK * 2;       // 16 KB: one plane's 128 x 64 tile
 constexpr int kMaxStages = 8;
 constexpr int kMaxPairs = 6;
 constexpr int kThreads = 6 * 32;
@@ -55,8 +54,6 @@ struct Params {
   int M, N, K;
   int out_f16;
   int MT, BN;
-  int bk;                  // k per stage: 64 (rows of 128 bytes, 128-byte swizzle) or 32 (rows of 64 bytes, 64-byte swizzle)
-  int a_tile;              // bytes of one plane's 128-row tile: 128 * bk * 2
   int planes;              // 1 or 3 per operand
   int npairs;
   uint32_t pair_a, pair_b;  // plane index of pair q in bits [4q, 4q+4)
@@ -165,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
   const int row0 = blockIdx.x * (p.MT * kBM);
   const int col0 = blockIdx.y * p.BN;
   const int tn = min(p.BN, p.N - col0);
-  const int nkb = (p.K + p.bk - 1) / p.bk;
+  const int nkb = (p.K + kBK - 1) / kBK;
 
   if (tid == 0) {
     for (int s = 0; s < kMaxStages; s++) {
@@ -193,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
       asm volatile("griddepcontrol.wait;" ::: "memory");   // the planes are written by the launches before
       int s = 0;
       uint32_t par = 0;
-      const uint32_t tx_bytes = (uint32_t)(p.planes * p.MT * p.a_tile + p.planes * p.b_tile);
+      const uint32_t tx_bytes = (uint32_t)(p.planes * p.MT * kATile + p.planes * p.b_tile);
       for (int kb = 0; kb < nkb; kb++) {
         if (kb >= p.stages) {
           if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status)) break;
@@ -203,10 +200,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
         mbar_expect_tx(bar, tx_bytes);
         uint32_t dst = smem_u32(tiles) + (uint32_t)s * (uint32_t)p.stage_bytes;
         for (int pl = 0; pl < p.planes; pl++)
-          for (int t = 0; t < p.MT; t++, dst += p.a_tile)
-            tma_load_2d(dst, &tmap_a, kb * p.bk, pl * p.a_plane_rows + row0 + t * kBM, bar);
+          for (int t = 0; t < p.MT; t++, dst += kATile)
+            tma_load_2d(dst, &tmap_a, kb * kBK, pl * p.a_plane_rows + row0 + t * kBM, bar);
         for (int pl = 0; pl < p.planes; pl++, dst += p.b_tile)
-          tma_load_2d(dst, &tmap_b, kb * p.bk, pl * p.b_plane_rows + col0, bar);
+          tma_load_2d(dst, &tmap_b, kb * kBK, pl * p.b_plane_rows + col0, bar);
         if (++s == p.stages) s = 0, par ^= 1u;
       }
     }
@@ -215,11 +212,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
     if (lane == 0) {
       int s = 0;
       uint32_t par = 0;
-      const uint64_t desc0 = (p.bk == 64) ? smem_desc_sw128(smem_u32(tiles)) : smem_desc_sw64(smem_u32(tiles));
-      const int ksteps = p.bk / 16;             // MMAs per tile pair: each covers 16 k = 32 bytes of a row
+      const uint64_t desc0 = smem_desc_sw128(smem_u32(tiles));
       const uint32_t lo0 = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
       const uint32_t slot_step = (uint32_t)p.stage_bytes >> 4;
-      const uint32_t a_tile_step = (uint32_t)p.a_tile >> 4, b_off = (uint32_t)p.a_bytes >> 4;
+      const uint32_t a_tile_step = (uint32_t)kATile >> 4, b_off = (uint32_t)p.a_bytes >> 4;
       const uint32_t b_tile_step = (uint32_t)p.b_tile >> 4;
       uint32_t soff = 0;
       for (int kb = 0; kb < nkb; kb++) {
@@ -237,13 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
             const uint32_t a_lo = lo0 + soff + (uint32_t)((int)pa * p.MT + t) * a_tile_step;
             const uint32_t b_lo = lo0 + soff + b_off + pb * b_tile_step;
             const bool lead = (pa | pb) == 0u;
-            const uint32_t first = (kb > 0 || (!lead && q > 0)) ? 1u : 0u;
-            if (ksteps == 4) {
-              umma_f16_kblock(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, first);
-            } else {
-              umma_f16_one(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, first);
-              umma_f16_one(lead ? d_main : d_corr, a_lo + 2, b_lo + 2, desc_hi, p.idesc, 1u);
-            }
+            umma_f16_kblock(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, (kb > 0 || (!lead && q > 0)) ? 1u : 0u);
           }
         }
         umma_commit(smem_u32(&empty[s]));
@@ -333,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
 
 // ---------------------------------------------------------------- host side
 struct Plan {
-  int MT, BN, bk, a_tile, planes, npairs, stages, tmem_cols;
+  int MT, BN, planes, npairs, stages, tmem_cols;
   int a_bytes, b_tile, stage_bytes;
   int64_t Mp, Np, Kp;
   size_t smem;
@@ -345,25 +335,16 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   const bool exact = (dtype == kDenseF32 && mode != kDenseTcFast);
   pl.planes = exact ? 3 : 1;
   pl.npairs = exact ? 6 : 1;
-  pl.bk = 64;
   if (exact) {
-    // 128 x 128 x 64 stages (six 16 KB tiles, two stages) need 61 bytes per clock from L2 at the full
-    // MMA rate and get 40; 256 x 128 x 32 stages (nine 8 KB tiles, three stages) need 46.  The wider
-    // tile halves the number of tiles, so it is taken where the waves it leaves cost less.
-    pl.MT = 1, pl.BN = 128;
-    const int sms = device_sm_count();
-    const int64_t ct = (N + 127) / 128, t1 = (M + 127) / 128 * ct, t2 = (M + 255) / 256 * ct;
-    const double cost1 = (double)((t1 + sms - 1) / sms) / 0.62, cost2 = (double)((t2 + sms - 1) / sms) * 2.0 / 0.87;
-    if (M > 128 && cost2 < cost1 && !getenv("SMITH_DENSE_NARROW")) pl.MT = 2, pl.bk = 32;
+    pl.MT = 1, pl.BN = 128;                      // 6 tiles of 16 KB per stage
   } else {
     pl.MT = (M > 128) ? 2 : 1;
     pl.BN = 256;
   }
-  pl.a_tile = kBM * pl.bk * 2;
   const int n16 = (int)((N + 15) / 16 * 16);
   if (n16 < pl.BN) pl.BN = n16;
-  pl.a_bytes = pl.planes * pl.MT * pl.a_tile;
-  pl.b_tile = pl.BN * pl.bk * 2;
+  pl.a_bytes = pl.planes * pl.MT * kATile;
+  pl.b_tile = pl.BN * kBK * 2;
   pl.b_tile = (pl.b_tile + 1023) / 1024 * 1024;  // every tile starts on 1024 bytes (the swizzle pattern's period)
   pl.stage_bytes = pl.a_bytes + pl.planes * pl.b_tile;
   int stages = (226 * 1024 - 1024) / pl.stage_bytes;
@@ -395,17 +376,15 @@ cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t sm
   return e;
 }
 
-bool encode_2d(CUtensorMap* map, bool f16, const void* base, int64_t inner, int64_t rows, int64_t pitch_elems, int box_rows,
-               int bk) {
+bool encode_2d(CUtensorMap* map, bool f16, const void* base, int64_t inner, int64_t rows, int64_t pitch_elems, int box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_rows};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   return enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
-             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -466,15 +445,15 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
 
   CUtensorMap map_a, map_b;
   if (f16) {
-    if (!encode_2d(&map_a, true, A, K, M, K, kBM, pl.bk)) return cudaErrorInvalidValue;
+    if (!encode_2d(&map_a, true, A, K, M, K, kBM)) return cudaErrorInvalidValue;
   } else {
-    if (!encode_2d(&map_a, false, a_planes, K, (int64_t)pl.planes * pl.Mp, pl.Kp, kBM, pl.bk)) return cudaErrorInvalidValue;
+    if (!encode_2d(&map_a, false, a_planes, K, (int64_t)pl.planes * pl.Mp, pl.Kp, kBM)) return cudaErrorInvalidValue;
   }
-  if (!encode_2d(&map_b, f16, b_planes, K, (int64_t)pl.planes * pl.Np, pl.Kp, pl.BN, pl.bk)) return cudaErrorInvalidValue;
+  if (!encode_2d(&map_b, f16, b_planes, K, (int64_t)pl.planes * pl.Np, pl.Kp, pl.BN)) return cudaErrorInvalidValue;
 
   Params p{};
   p.C = C, p.M = (int)M, p.N = (int)N, p.K = (int)K, p.out_f16 = f16 ? 1 : 0;
-  p.MT = pl.MT, p.BN = pl.BN, p.bk = pl.bk, p.a_tile = pl.a_tile, p.planes = pl.planes, p.npairs = pl.npairs;
+  p.MT = pl.MT, p.BN = pl.BN, p.planes = pl.planes, p.npairs = pl.npairs;
   // the five small products (smallest first), then the leading one
   static const int pa[kMaxPairs] = {1, 2, 0, 1, 0, 0}, pb[kMaxPairs] = {1, 0, 2, 0, 1, 0};
   p.pair_a = p.pair_b = 0;

@@ -65,20 +65,6 @@ __device__ __forceinline__ void umma_f16_kblock(uint32_t d_tmem, uint32_t a_lo, 
       "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)
       : "memory");
 }
-// One tcgen05.mma (128 x N x 16, 16-bit inputs, f32 accumulate) from explicit descriptor words.
-__device__ __forceinline__ void umma_f16_one(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 da, db;\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "mov.b64 da, {%1, %3};\n"
-      "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
-      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // mbarrier arrive once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -102,15 +88,6 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 //   [0,14)  start address >> 4        [16,30) leading byte offset >> 4 (unused here)
 //   [32,46) stride byte offset >> 4   [46,48) descriptor version = 1
 //   [49,52) base offset = 0 (tiles are 1024-byte aligned)   [61,64) layout: 2 = 128-byte swizzle
-// The same for rows of 64 bytes with 64-byte swizzle: groups of 8 rows 512 bytes apart, layout 4.
-__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)(512u >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)4 << 61;
-  return d;
-}
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
