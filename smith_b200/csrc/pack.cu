@@ -17,12 +17,15 @@
 // (src/dtype.js:60-79); code = dq > 0 ? clamp(round_half_up(v/dq), -127, 127) : 0.
 // Block bytes: [f16 scale, little endian][32 x int8].
 //
-// Speed: 32 f64 divisions per block would make the packers divide-bound (measured 1.84 TB/s of
-// read + write traffic, 0.28 of the HBM copy peak).  A code only depends on which side of a
-// half-integer the quotient falls, so each element first takes v * (1 / scale), which is within a few
-// ulps of the correctly rounded quotient, and only when the result lies closer to a half-integer than
-// that error can reach (about once in 10^13 elements for ordinary data) is the reference's own
-// expression, division included, evaluated.  The codes are the same bit for bit either way.
+// Speed: evaluated per element in f64 the packers were bound by instruction issue (an ncu capture
+// counted 48 instructions per weight: 0.28 to 0.37 of the HBM copy peak).  A code only depends on which
+// side of a half-integer the f64 value falls, so a full block is first SCREENED in f32, branch-free:
+// fma(v, 1/scale, zero) in f32 is within 2.5e-7 * (|v/scale| + |zero| + 16) of the f64 value, and
+// unless some element of the block lies closer than that to a half-integer (a block in a few hundred
+// for ordinary data) the nearest integers ARE the reference's codes.  Only the remaining blocks, tail
+// groups and blocks with an extraordinary scale go through the reference's own expressions, division
+// included (q4_block_exact / q8_block_exact).  Scale and zero point are always computed in f64.  The
+// bytes are the same either way.
 //
 // Layout of both outputs: block (g, col) at byte (g*N + col) * block_bytes, so
 // for one g the N blocks are contiguous.  One thread packs one block; a CTA
@@ -79,6 +82,42 @@ __device__ __forceinline__ double js_from_float16(uint32_t h) {
   return sign ? -v : v;
 }
 
+constexpr float kMagic = 12582912.f;   // 1.5 * 2^23: x + kMagic rounds x to the nearest integer (|x| < 2^22),
+                                       // which then sits in the low mantissa bits
+
+// One block by the reference's own expressions, evaluated element by element in f64 (division
+// included), reading the values again from global memory.  The slow lane: tail groups, blocks whose
+// scale is far from ordinary, and blocks with an element the f32 screen could not call.
+__device__ __noinline__ void q4_block_exact(const float* __restrict__ src, int64_t N, int valid, uint32_t* words,
+                                            uint32_t* sbits, uint32_t* zbits) {
+  // quantize.js:26-31 -- in-order compares so NaN and signed zeros behave as in JS.
+  float mn = __int_as_float(0x7F800000), mx = __int_as_float(0xFF800000);
+#pragma unroll 1
+  for (int k = 0; k < valid; k++) {
+    const float x = src[(int64_t)k * N];
+    if (x < mn) mn = x;
+    if (x > mx) mx = x;
+  }
+  const double range = __dsub_rn((double)mx, (double)mn);
+  const bool pos = range > 0.0;
+  const double scale = pos ? __ddiv_rn(range, 15.0) : 1.0;
+  const double zero = pos ? __ddiv_rn(-(double)mn, scale) : 8.0;
+  words[0] = words[1] = words[2] = words[3] = 0u;
+#pragma unroll 1
+  for (int k = 0; k < kQ4Group; k++) {
+    const double x = (k < valid) ? (double)src[(int64_t)k * N] : 0.0;
+    const double t = __dadd_rn(__ddiv_rn(x, scale), zero);  // quantize.js:45
+    // Math.max(0, t) then Math.min(15, t); a NaN ends as code 0 like the typed-array store.
+    double m = (t > 0.0) ? t : 0.0;
+    m = (m < 15.0) ? m : 15.0;
+    const double f = floor(m);
+    const uint32_t q = (uint32_t)((__dsub_rn(m, f) >= 0.5) ? f + 1.0 : f);   // Math.round: ties toward +infinity
+    words[k >> 3] |= q << ((k & 7) * 4);  // element k: byte k>>1, low nibble if k even
+  }
+  *sbits = __float_as_uint(__double2float_rn(scale));
+  *zbits = __float_as_uint(__double2float_rn(zero));
+}
+
 __global__ void __launch_bounds__(kPackThreads)
 pack_q4_kernel(const float* __restrict__ w, uint8_t* __restrict__ out, int64_t K, int64_t N) {
   __shared__ __align__(16) uint2 stage[kPackThreads * 3];
@@ -89,51 +128,60 @@ pack_q4_kernel(const float* __restrict__ w, uint8_t* __restrict__ out, int64_t K
   const int valid = (int)((K - k0 < kQ4Group) ? (K - k0) : kQ4Group);
 
   if (col < N) {
-    float v[kQ4Group];
     const float* src = w + k0 * N + col;
+    uint32_t words[4], sbits = 0, zbits = 0;
+    bool done = false;
+    if (valid == kQ4Group) {
+      float v[kQ4Group];
 #pragma unroll
-    for (int k = 0; k < kQ4Group; k++) v[k] = (k < valid) ? src[(int64_t)k * N] : 0.0f;
-
-    // quantize.js:26-31 -- in-order compares so NaN and signed zeros behave as in JS.
-    float mn = __int_as_float(0x7F800000), mx = __int_as_float(0xFF800000);
+      for (int k = 0; k < kQ4Group; k++) v[k] = src[(int64_t)k * N];
+      // min / max.  fminf / fmaxf skip NaNs as the reference's compares do; where they differ is the
+      // SIGN of a zero minimum (the reference keeps the first zero it meets), restored below.
+      float mn = __int_as_float(0x7F800000), mx = __int_as_float(0xFF800000);
 #pragma unroll
-    for (int k = 0; k < kQ4Group; k++) {
-      if (k < valid) {
-        if (v[k] < mn) mn = v[k];
-        if (v[k] > mx) mx = v[k];
+      for (int k = 0; k < kQ4Group; k++) mn = fminf(mn, v[k]), mx = fmaxf(mx, v[k]);
+      if (mn == 0.f) {
+#pragma unroll
+        for (int k = kQ4Group - 1; k >= 0; k--)
+          if (v[k] == 0.f) mn = v[k];
+      }
+      const double range = __dsub_rn((double)mx, (double)mn);
+      const bool pos = range > 0.0;
+      const double scale = pos ? __ddiv_rn(range, 15.0) : 1.0;
+      const double zero = pos ? __ddiv_rn(-(double)mn, scale) : 8.0;
+      // f32 screen (see the file comment).  rcp32 is within 2 * 2^-24 of 1/scale, zero32 within 2^-24 of
+      // zero, the fused multiply-add rounds once: t32 is within 2^-24 * (2|a| + |zero| + |t|) of the f64
+      // value, inside bound = 2.5e-7 * (|a| + |zero| + 16).
+      if (pos && scale > 1e-30 && scale < 1e30) {
+        const float rcp32 = __frcp_rn(__double2float_rn(scale));
+        const float zero32 = __double2float_rn(zero);
+        const float slope = 2.5e-7f * fabsf(rcp32);                       // bound = slope * |v| + bound0
+        const float thr0 = 0.5f - 2.5e-7f * (fabsf(zero32) + 16.f);       // may go negative: then nothing passes
+        bool ok = true;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < kQ4Group; k++) {
+          const float t32 = fmaf(v[k], rcp32, zero32);
+          const float m32 = fminf(fmaxf(t32, 0.f), 15.f);                 // a NaN becomes 0, as in the reference
+          const float r = (m32 + kMagic) - kMagic;                        // nearest integer
+          ok = ok && (fabsf(m32 - r) < fmaf(-slope, fabsf(v[k]), thr0));  // false for NaN and near a half-integer
+          // four codes per accumulator, weights 1, 16, 256, 4096: exact in f32 (sum < 2^16)
+          const float wgt = (float)(1 << (4 * (k & 3)));
+          acc[k >> 2] = (k & 3) ? fmaf(r, wgt, acc[k >> 2]) : r;
+        }
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint32_t lo = __float_as_uint(acc[2 * i] + kMagic), hi = __float_as_uint(acc[2 * i + 1] + kMagic);
+            words[i] = __byte_perm(lo, hi, 0x5410);                       // low 16 bits of each
+          }
+          sbits = __float_as_uint(__double2float_rn(scale));
+          zbits = __float_as_uint(__double2float_rn(zero));
+          done = true;
+        }
       }
     }
-    const double range = __dsub_rn((double)mx, (double)mn);
-    const bool pos = range > 0.0;
-    const double scale = pos ? __ddiv_rn(range, 15.0) : 1.0;
-    const double zero = pos ? __ddiv_rn(-(double)mn, scale) : 8.0;
-
-    const double rcp = __ddiv_rn(1.0, scale);
-    uint32_t words[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-    for (int k = 0; k < kQ4Group; k++) {
-      // Fast: a = v * (1/scale) differs from RN(v / scale) by at most 3 * 2^-53 * |a|, and the sum with
-      // `zero` adds one more rounding of a number below 16 + |a| + |zero|.
-      const double a = __dmul_rn((double)v[k], rcp);
-      double t = __dadd_rn(a, zero);
-      double m = (t > 0.0) ? t : 0.0;
-      m = (m < 15.0) ? m : 15.0;
-      double f = floor(m);
-      double fr = __dsub_rn(m, f);
-      if (!(fabs(__dsub_rn(fr, 0.5)) > 2e-15 * (fabs(a) + fabs(zero) + 16.0))) {
-        // too close to a rounding boundary to call (or not a number): the reference's expression itself
-        t = __dadd_rn(__ddiv_rn((double)v[k], scale), zero);  // quantize.js:45
-        // Math.max(0, t) then Math.min(15, t); a NaN ends as code 0 like the typed-array store.
-        m = (t > 0.0) ? t : 0.0;
-        m = (m < 15.0) ? m : 15.0;
-        f = floor(m);
-        fr = __dsub_rn(m, f);
-      }
-      const uint32_t q = (uint32_t)((fr >= 0.5) ? f + 1.0 : f);     // Math.round: ties toward +infinity
-      words[k >> 3] |= q << ((k & 7) * 4);  // element k: byte k>>1, low nibble if k even
-    }
-    const uint32_t sbits = __float_as_uint(__double2float_rn(scale));
-    const uint32_t zbits = __float_as_uint(__double2float_rn(zero));
+    if (!done) q4_block_exact(src, N, valid, words, &sbits, &zbits);
     uint2* mine = stage + threadIdx.x * 3;
     mine[0] = make_uint2(words[0], words[1]);
     mine[1] = make_uint2(words[2], words[3]);
@@ -143,6 +191,38 @@ pack_q4_kernel(const float* __restrict__ w, uint8_t* __restrict__ out, int64_t K
   const int64_t ncols = (N - col0 < kPackThreads) ? (N - col0) : kPackThreads;
   uint2* dst = reinterpret_cast<uint2*>(out + (g * N + col0) * kQ4Bytes);  // 24*i is 8-byte aligned
   for (int i = threadIdx.x; i < ncols * 3; i += kPackThreads) dst[i] = stage[i];
+}
+
+// One Q8 block by the rule's own expressions in f64 (see q4_block_exact).
+__device__ __noinline__ void q8_block_exact(const float* __restrict__ src, int64_t N, int valid, uint16_t* mine) {
+  float amax = 0.0f;
+#pragma unroll 1
+  for (int k = 0; k < valid; k++) {
+    const float a = fabsf(src[(int64_t)k * N]);
+    if (a > amax) amax = a;  // NaN never wins
+  }
+  const double d = __ddiv_rn((double)amax, 127.0);
+  const uint32_t h = js_to_float16(d);
+  const double dq = js_from_float16(h);
+  mine[0] = (uint16_t)h;
+#pragma unroll 1
+  for (int k = 0; k < kQ8Group; k += 2) {
+    int q[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      int c = 0;
+      if (k + i < valid && dq > 0.0) {
+        double t = js_round(__ddiv_rn((double)src[(int64_t)(k + i) * N], dq));
+        if (t == t) {
+          t = (t > 127.0) ? 127.0 : t;
+          t = (t < -127.0) ? -127.0 : t;
+          c = (int)t;
+        }
+      }
+      q[i] = c & 0xFF;
+    }
+    mine[1 + (k >> 1)] = (uint16_t)(q[0] | (q[1] << 8));
+  }
 }
 
 __global__ void __launch_bounds__(kPackThreads)
@@ -155,47 +235,49 @@ pack_q8_kernel(const float* __restrict__ w, uint8_t* __restrict__ out, int64_t K
   const int valid = (int)((K - k0 < kQ8Group) ? (K - k0) : kQ8Group);
 
   if (col < N) {
-    float v[kQ8Group];
     const float* src = w + k0 * N + col;
-#pragma unroll
-    for (int k = 0; k < kQ8Group; k++) v[k] = (k < valid) ? src[(int64_t)k * N] : 0.0f;
-    float amax = 0.0f;
-#pragma unroll
-    for (int k = 0; k < kQ8Group; k++) {
-      float a = fabsf(v[k]);
-      if (k < valid && a > amax) amax = a;  // NaN never wins
-    }
-    const double d = __ddiv_rn((double)amax, 127.0);
-    const uint32_t h = js_to_float16(d);
-    const double dq = js_from_float16(h);
-    const double rcp = (dq > 0.0) ? __ddiv_rn(1.0, dq) : 0.0;
     uint16_t* mine = stage + threadIdx.x * 17;
-    mine[0] = (uint16_t)h;
+    bool done = false;
+    if (valid == kQ8Group) {
+      float v[kQ8Group];
 #pragma unroll
-    for (int k = 0; k < kQ8Group; k += 2) {
-      int q[2];
+      for (int k = 0; k < kQ8Group; k++) v[k] = src[(int64_t)k * N];
+      float amax = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 2; i++) {
-        int c = 0;
-        if (k + i < valid && dq > 0.0) {
-          // fast quotient first; the exact one only next to a rounding boundary (see the file comment)
-          const double a = __dmul_rn((double)v[k + i], rcp);
-          double f = floor(a);
-          double t;
-          if (fabs(__dsub_rn(__dsub_rn(a, f), 0.5)) > 2e-15 * (fabs(a) + 1.0))
-            t = (__dsub_rn(a, f) >= 0.5) ? f + 1.0 : f;
-          else
-            t = js_round(__ddiv_rn((double)v[k + i], dq));
-          if (t == t) {
-            t = (t > 127.0) ? 127.0 : t;
-            t = (t < -127.0) ? -127.0 : t;
-            c = (int)t;
-          }
+      for (int k = 0; k < kQ8Group; k++) amax = fmaxf(amax, fabsf(v[k]));   // NaN never wins
+      const double d = __ddiv_rn((double)amax, 127.0);
+      const uint32_t h = js_to_float16(d);
+      const double dq = js_from_float16(h);
+      if (dq > 1e-30 && dq < 1e30) {
+        // dq is a half, so exact in f32; rcp32 within 2^-24 of 1/dq; a32 = v * rcp32 within
+        // 2 * 2^-24 * |a| of v / dq, inside bound = 2.5e-7 * (|a| + 1).  |v| <= amax keeps |a| below 128.
+        const float rcp32 = __frcp_rn(__double2float_rn(dq));
+        bool ok = true;
+        uint32_t ub[kQ8Group];
+#pragma unroll
+        for (int k = 0; k < kQ8Group; k++) {
+          const float a32 = v[k] * rcp32;
+          const float c32 = fminf(fmaxf(a32, -127.f), 127.f);             // clamping before or after rounding is the same
+          const float u = c32 + kMagic;
+          const float r = u - kMagic;
+          ok = ok && (fabsf(a32) < 200.f) && (fabsf(c32 - r) < fmaf(-2.5e-7f, fabsf(a32), 0.5f - 2.5e-7f));
+          ub[k] = __float_as_uint(u);                                     // low byte = the code in two's complement
         }
-        q[i] = c & 0xFF;
+        if (ok) {
+          mine[0] = (uint16_t)h;
+#pragma unroll
+          for (int k = 0; k < kQ8Group; k += 2) mine[1 + (k >> 1)] = (uint16_t)__byte_perm(ub[k], ub[k + 1], 0x0040);
+          done = true;
+        }
+      } else if (!(dq > 0.0) && amax == amax) {
+        // the scale underflowed to zero: every code is 0
+        mine[0] = (uint16_t)h;
+#pragma unroll
+        for (int k = 0; k < kQ8Group; k += 2) mine[1 + (k >> 1)] = 0;
+        done = true;
       }
-      mine[1 + (k >> 1)] = (uint16_t)(q[0] | (q[1] << 8));
     }
+    if (!done) q8_block_exact(src, N, valid, mine);
   }
   __syncthreads();
   const int64_t ncols = (N - col0 < kPackThreads) ? (N - col0) : kPackThreads;

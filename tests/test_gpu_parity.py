@@ -43,6 +43,35 @@ def test_packers_bit_exact_random(kind, K, N):
         assert np.array_equal(pack_on_device(w, kind), want)
 
 
+@pytest.mark.parametrize("kind", ["q4", "q8"])
+def test_packers_bit_exact_where_the_f32_screen_is_weak_or_off(kind):
+    """The packers screen every element in f32 and evaluate the f64 expression only next to a rounding
+    boundary.  Data chosen to strain that: a large common offset (the f32 sum cancels, every element
+    must take the f64 path), scales far outside the ordinary range (screen switched off), groups that
+    are constant, denormal or infinite, and quotients that land on multiples of 1/8 and of 2^-20."""
+    K, N = 96, 1536
+    rng = np.random.default_rng(77)
+    cases = [
+        (1000.0 + rng.random((K, N)) * 1e-3).astype(np.float32),
+        (-3.0e6 + rng.standard_normal((K, N))).astype(np.float32),
+        (rng.standard_normal((K, N)) * 1e-36).astype(np.float32),
+        (rng.standard_normal((K, N)) * 1e-41).astype(np.float32),            # denormals
+        (rng.standard_normal((K, N)) * 1e36).astype(np.float32),
+        np.full((K, N), 0.25, np.float32),
+        (rng.integers(-120, 121, (K, N)) / 8.0).astype(np.float32),
+        (rng.integers(0, 16, (K, N)) + rng.integers(-3, 4, (K, N)) * 2.0 ** -20 + 0.5).astype(np.float32),
+    ]
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    w[5, ::7] = np.inf
+    w[40, ::11] = -np.inf
+    w[70, ::13] = np.nan
+    cases.append(w)
+    for i, w in enumerate(cases):
+        with np.errstate(all="ignore"):
+            want = O.quantize_q4(w) if kind == "q4" else O.quantize_q8(w)
+        assert np.array_equal(pack_on_device(w, kind), want), f"case {i}"
+
+
 def test_packer_rounding_boundaries():
     # values engineered to sit on and next to .5 code boundaries after v/scale + zero
     K, N = 32, 4096
