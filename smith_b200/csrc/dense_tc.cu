@@ -34,6 +34,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 
 #include "kernels.h"
 #include "pipeline.cuh"
@@ -146,6 +147,10 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const IN* __restri
 }
 
 // ---------------------------------------------------------------- main kernel
+// PAIR: two CTAs of a cluster work as one MMA unit (cta_group::2) on 2 x MT x 128 rows by BN columns;
+// each stages its own rows of A and its own half of the BN columns of B, so a stage carries half the B
+// bytes per MMA: what binds the single-CTA form is the bytes per clock an SM receives from L2.
+template <bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                const __grid_constant__ CUtensorMap tmap_b,
                                                                const Params p) {
@@ -163,10 +168,11 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
   const int col0 = blockIdx.y * p.BN;
   const int tn = min(p.BN, p.N - col0);
   const int nkb = (p.K + kBK - 1) / kBK;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0: the CTA that issues the pair's MMAs
 
   if (tid == 0) {
     for (int s = 0; s < kMaxStages; s++) {
-      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&full[s]), PAIR ? 2 : 1);      // pair: one arrival per CTA's producer, on the leader's barrier
       mbar_init(smem_u32(&empty[s]), 1);
     }
     mbar_init(smem_u32(acc_ready), 1);
@@ -174,13 +180,21 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_base_slot), (uint32_t)p.tmem_cols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_base_slot), (uint32_t)p.tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_base_slot), (uint32_t)p.tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();                        // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t own_tmem = *tmem_base_slot;           // what this CTA's allocation returned (freed at the end)
+  // the accumulators' address is the leader's: its thread issues the MMAs for both CTAs
+  const uint32_t tmem_base = PAIR ? ld_cluster_u32(mapa_u32(smem_u32(tmem_base_slot), 0)) : own_tmem;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   bool ok = true;
@@ -195,21 +209,32 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
         if (kb >= p.stages) {
           if (!mbar_wait(smem_u32(&empty[s]), par ^ 1u, abort_flag, p.status)) break;
         }
-        const uint32_t bar = smem_u32(&full[s]);
         // a box beyond K or beyond the last row is filled with zeros and still counts its bytes
-        mbar_expect_tx(bar, tx_bytes);
         uint32_t dst = smem_u32(tiles) + (uint32_t)s * (uint32_t)p.stage_bytes;
-        for (int pl = 0; pl < p.planes; pl++)
-          for (int t = 0; t < p.MT; t++, dst += kATile)
-            tma_load_2d(dst, &tmap_a, kb * kBK, pl * p.a_plane_rows + row0 + t * kBM, bar);
-        for (int pl = 0; pl < p.planes; pl++, dst += p.b_tile)
-          tma_load_2d(dst, &tmap_b, kb * kBK, pl * p.b_plane_rows + col0, bar);
+        if (PAIR) {
+          // both CTAs' bytes are counted on the LEADER's barrier, the one its MMA thread waits on
+          const uint32_t bar = mapa_u32(smem_u32(&full[s]), 0);
+          mbar_expect_tx_cluster(bar, tx_bytes);
+          for (int pl = 0; pl < p.planes; pl++)
+            for (int t = 0; t < p.MT; t++, dst += kATile)
+              tma_load_2d_pair(dst, &tmap_a, kb * kBK, pl * p.a_plane_rows + row0 + t * kBM, bar);
+          for (int pl = 0; pl < p.planes; pl++, dst += p.b_tile)     // this CTA's half of the BN columns
+            tma_load_2d_pair(dst, &tmap_b, kb * kBK, pl * p.b_plane_rows + col0 + (int)rank * (p.BN / 2), bar);
+        } else {
+          const uint32_t bar = smem_u32(&full[s]);
+          mbar_expect_tx(bar, tx_bytes);
+          for (int pl = 0; pl < p.planes; pl++)
+            for (int t = 0; t < p.MT; t++, dst += kATile)
+              tma_load_2d(dst, &tmap_a, kb * kBK, pl * p.a_plane_rows + row0 + t * kBM, bar);
+          for (int pl = 0; pl < p.planes; pl++, dst += p.b_tile)
+            tma_load_2d(dst, &tmap_b, kb * kBK, pl * p.b_plane_rows + col0, bar);
+        }
         if (++s == p.stages) s = 0, par ^= 1u;
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (pair: the leader's only)
+    if (lane == 0 && rank == 0) {
       int s = 0;
       uint32_t par = 0;
       const uint64_t desc0 = smem_desc_sw128(smem_u32(tiles));
@@ -233,14 +258,28 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
             const uint32_t a_lo = lo0 + soff + (uint32_t)((int)pa * p.MT + t) * a_tile_step;
             const uint32_t b_lo = lo0 + soff + b_off + pb * b_tile_step;
             const bool lead = (pa | pb) == 0u;
-            umma_f16_kblock(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, (kb > 0 || (!lead && q > 0)) ? 1u : 0u);
+            const uint32_t first = (kb > 0 || (!lead && q > 0)) ? 1u : 0u;
+            if (PAIR) umma_f16_kblock_pair(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, first);
+            else umma_f16_kblock(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, first);
           }
         }
-        umma_commit(smem_u32(&empty[s]));
+        if (PAIR) {                                    // the stage is free in both CTAs
+          umma_commit_pair(smem_u32(&empty[s]));
+          umma_commit_pair(mapa_u32(smem_u32(&empty[s]), 1));
+        } else {
+          umma_commit(smem_u32(&empty[s]));
+        }
         soff += slot_step;
         if (++s == p.stages) s = 0, par ^= 1u, soff = 0;
       }
-      if (ok) umma_commit(smem_u32(acc_ready));
+      if (ok) {
+        if (PAIR) {
+          umma_commit_pair(smem_u32(acc_ready));
+          umma_commit_pair(mapa_u32(smem_u32(acc_ready), 1));
+        } else {
+          umma_commit(smem_u32(acc_ready));
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2-5)
@@ -315,14 +354,17 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();     // the peer's MMAs read this CTA's shared memory and signal its barriers until here
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    if (PAIR) tmem_dealloc_pair(own_tmem, (uint32_t)p.tmem_cols);
+    else tmem_dealloc(own_tmem, (uint32_t)p.tmem_cols);
   }
 }
 
 // ---------------------------------------------------------------- host side
 struct Plan {
+  bool pair;
   int MT, BN, planes, npairs, stages, tmem_cols;
   int a_bytes, b_tile, stage_bytes;
   int64_t Mp, Np, Kp;
@@ -335,16 +377,31 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   const bool exact = (dtype == kDenseF32 && mode != kDenseTcFast);
   pl.planes = exact ? 3 : 1;
   pl.npairs = exact ? 6 : 1;
+  const int sms = device_sm_count();
+  const int n16 = (int)((N + 15) / 16 * 16), n32 = (int)((N + 31) / 32 * 32);
+  static const bool no_pair = getenv("SMITH_DENSE_NO_PAIR") != nullptr;   // for A/B measurements
+  auto waves = [](int64_t tiles, int64_t units) { return (double)((tiles + units - 1) / units); };
   if (exact) {
-    pl.MT = 1, pl.BN = 128;                      // 6 tiles of 16 KB per stage
+    // One CTA: 128 x 128 tiles (six 16 KB plane tiles per stage, two stages).  A CTA pair: 256 x 256
+    // tiles, each CTA staging 48 KB of A and its 48 KB half of B per stage; the MMA thread then issues
+    // the same 24 instructions per stage for twice the tensor time, and that thread's instruction
+    // stream is what bounds the single-CTA form (measured: 62 % of the tensor pipe against 83 %).
+    // The pair's tile is four times as large, so it is taken where the waves it leaves cost less.
+    pl.MT = 1, pl.BN = (n16 < 128) ? n16 : 128;
+    const int bn2 = (n32 < 256) ? n32 : 256;
+    const double t1 = waves((M + 127) / 128 * ((N + 127) / 128), sms) / 0.62;
+    const double t2 = waves((M + 255) / 256 * ((N + bn2 - 1) / bn2), sms / 2) * 2.0 * (bn2 / 128.0) / 2.0 / 0.85;
+    pl.pair = !no_pair && M > kBM && N > 128 && t2 < t1;
+    if (pl.pair) pl.BN = bn2;
   } else {
+    // one plane per operand: 256 x 256 tiles on one CTA.  (512 x 256 tiles on a CTA pair, 48 KB instead
+    // of 64 KB staged per 256 x 256 x 64 of MMA work, measured SLOWER: 179 against 138 us at f16 4096^3.)
     pl.MT = (M > 128) ? 2 : 1;
-    pl.BN = 256;
+    pl.BN = (n16 < 256) ? n16 : 256;
+    pl.pair = false;
   }
-  const int n16 = (int)((N + 15) / 16 * 16);
-  if (n16 < pl.BN) pl.BN = n16;
   pl.a_bytes = pl.planes * pl.MT * kATile;
-  pl.b_tile = pl.BN * kBK * 2;
+  pl.b_tile = (pl.pair ? pl.BN / 2 : pl.BN) * kBK * 2;
   pl.b_tile = (pl.b_tile + 1023) / 1024 * 1024;  // every tile starts on 1024 bytes (the swizzle pattern's period)
   pl.stage_bytes = pl.a_bytes + pl.planes * pl.b_tile;
   int stages = (226 * 1024 - 1024) / pl.stage_bytes;
@@ -356,24 +413,37 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   pl.tmem_cols = cols;
   pl.smem = 1024 + (size_t)stages * pl.stage_bytes;
   pl.Kp = (K + 7) / 8 * 8;
-  pl.Mp = (M + 127) / 128 * 128;
+  pl.Mp = (M + 511) / 512 * 512;                 // whole row tiles of a pair, so a plane's boxes stay inside the plane
   pl.Np = (N + 31) / 32 * 32;
-  pl.grid = dim3((unsigned)((M + pl.MT * kBM - 1) / (pl.MT * kBM)), (unsigned)((N + pl.BN - 1) / pl.BN));
+  unsigned gx = (unsigned)((M + pl.MT * kBM - 1) / (pl.MT * kBM));
+  if (pl.pair) gx = (gx + 1) & ~1u;              // an odd last row tile gets a partner that stores nothing
+  pl.grid = dim3(gx, (unsigned)((N + pl.BN - 1) / pl.BN));
   return pl;
 }
 
 template <typename... Args>
-cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+cudaError_t launch_pdl_cluster(void (*kernel)(Args...), int cluster_x, dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                               Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster_x > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cluster_x, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
   count_launch();
   return e;
+}
+
+template <typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  return launch_pdl_cluster(kernel, 1, grid, block, smem, s, args...);
 }
 
 bool encode_2d(CUtensorMap* map, bool f16, const void* base, int64_t inner, int64_t rows, int64_t pitch_elems, int box_rows) {
@@ -449,7 +519,7 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
   } else {
     if (!encode_2d(&map_a, false, a_planes, K, (int64_t)pl.planes * pl.Mp, pl.Kp, kBM)) return cudaErrorInvalidValue;
   }
-  if (!encode_2d(&map_b, f16, b_planes, K, (int64_t)pl.planes * pl.Np, pl.Kp, pl.BN)) return cudaErrorInvalidValue;
+  if (!encode_2d(&map_b, f16, b_planes, K, (int64_t)pl.planes * pl.Np, pl.Kp, pl.pair ? pl.BN / 2 : pl.BN)) return cudaErrorInvalidValue;
 
   Params p{};
   p.C = C, p.M = (int)M, p.N = (int)N, p.K = (int)K, p.out_f16 = f16 ? 1 : 0;
@@ -464,7 +534,8 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
   // tcgen05.mma kind::f16 instruction descriptor: [4,6) D = f32; [7,10) A format, [10,13) B format
   // (0 = f16, 1 = bf16); both operands K-major; [17,23) N >> 3; [24,29) M >> 4
   const uint32_t fmt = f16 ? 0u : 1u;
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(pl.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(pl.BN >> 3) << 17) |
+            ((uint32_t)((pl.pair ? 2 * kBM : kBM) >> 4) << 24);
   p.status = kernel_status_ptr();
   if (!p.status) return cudaErrorUnknown;
 
@@ -472,11 +543,16 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
   bool* set = configured.here();
   if (!set) return cudaErrorInvalidDevice;
   if (!*set) {
-    e = cudaFuncSetAttribute(dense_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(dense_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(dense_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     *set = true;
   }
-  e = launch_pdl(dense_tc_kernel, pl.grid, dim3(kThreads), pl.smem, s, map_a, map_b, p);
+  if (pl.pair)
+    e = launch_pdl_cluster(dense_tc_kernel<true>, 2, pl.grid, dim3(kThreads), pl.smem, s, map_a, map_b, p);
+  else
+    e = launch_pdl(dense_tc_kernel<false>, pl.grid, dim3(kThreads), pl.smem, s, map_a, map_b, p);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 

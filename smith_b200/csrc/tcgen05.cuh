@@ -97,4 +97,84 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return d;
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 2i and 2i+1) act as one MMA unit: D has 256 rows, rows 0-127 in the
+// even ("leader") CTA's tensor memory and rows 128-255 in the odd one's; each CTA stages its own 128
+// rows of A and its own half of the N columns of B, at the same shared-memory offsets in both; one
+// thread of the leader issues the MMAs and the commits.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t caddr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(caddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cbar), "r"(bytes) : "memory");
+}
+// tensor-map load into this CTA's shared memory whose bytes are counted on a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cbar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// The four MMAs (256 x N x 16 each) of one 64-wide k-block, as umma_f16_kblock.
+__device__ __forceinline__ void umma_f16_kblock_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                     uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      ".reg .b32 ta, tb;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "setp.ne.b32 q, %4, 0;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n"
+      "add.u32 ta, %1, 2;\n"
+      "add.u32 tb, %2, 2;\n"
+      "mov.b64 da, {ta, %3};\n"
+      "mov.b64 db, {tb, %3};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, q;\n"
+      "add.u32 ta, %1, 4;\n"
+      "add.u32 tb, %2, 4;\n"
+      "mov.b64 da, {ta, %3};\n"
+      "mov.b64 db, {tb, %3};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, q;\n"
+      "add.u32 ta, %1, 6;\n"
+      "add.u32 tb, %2, 6;\n"
+      "mov.b64 da, {ta, %3};\n"
+      "mov.b64 db, {tb, %3};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, q;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+// mbarrier arrive (on a barrier of this or of the peer CTA, by its shared::cluster address) once every
+// MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t cbar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cbar) : "memory");
+}
+
 }  // namespace smith

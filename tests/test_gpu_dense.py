@@ -79,7 +79,10 @@ def test_batched_is_bit_exact(dtype):
 # one tile; ragged M, N and K (K not a multiple of 8 or 64; N not a multiple of 16); several row and
 # column tiles; a K longer than the ring; a large square
 TC_SHAPES = [(64, 64, 64), (128, 128, 128), (100, 200, 72), (130, 1001, 250), (257, 333, 129), (512, 4096, 1024),
-             (64, 8192, 64), (1024, 1024, 1024)]
+             (64, 8192, 64), (1024, 1024, 1024),
+             # more than one wave of 128 x 128 tiles: the three-plane mode then runs on CTA pairs
+             # (256 x 256 tiles); the second shape has an odd number of row tiles and a ragged last column tile
+             (2048, 256, 2048), (1300, 200, 1900)]
 
 
 def test_tensor_core_f32_three_planes():
@@ -103,6 +106,19 @@ def test_tensor_core_f32_is_closer_to_the_exact_product_than_the_sequential_sum_
     exact = a.astype(np.float64) @ b.astype(np.float64)
     bound = _norm_bound(a, b, 1e-6)
     assert float((np.abs(got - exact) / bound).max()) <= 1.0
+
+
+def test_tensor_core_f32_on_cta_pairs_with_non_finite_inputs():
+    M, K, N = 2048, 128, 2048
+    a, b = _data(9, (M, K), (K, N))
+    a[1500, 3] = np.nan                                     # a row of the second CTA of a pair
+    a[130, 5] = np.inf
+    got = dense_on_device(a, b, device.DENSE_TENSOR)
+    want = O.dense_matmul(a, b)
+    assert np.all(np.isnan(got[1500])) and np.all(np.isinf(got[130]) | np.isnan(got[130]))
+    rows = [r for r in range(M) if r not in (130, 1500)]
+    assert np.all(np.isfinite(got[rows]))
+    assert float((np.abs(got[rows].astype(np.float64) - want[rows]) / _norm_bound(a[rows], b, 4e-6)).max()) <= 1.0
 
 
 def test_tensor_core_fast_mode():
