@@ -29,7 +29,7 @@
 //               (128 x BN x 16) of each plane pair, then tcgen05.commit frees the stage
 //       warps 2-5  epilogue: tcgen05.ld their 32-lane quarter of the accumulators, turn 32 x 32
 //               chunks around in shared memory and store whole 128-byte row segments of C
-// No multicast, no clusters.  Every mbarrier wait is time-bounded (pipeline.cuh); on a give-up the
+// No multicast; clusters of two CTAs in the pair form only.  Every mbarrier wait is time-bounded (pipeline.cuh); on a give-up the
 // CTA skips to the end, frees its tensor memory and leaves the status word set.
 #include <cuda.h>
 #include <cuda_bf16.h>
