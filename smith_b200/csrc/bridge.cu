@@ -933,8 +933,22 @@ int32_t smith_qmatmul_multi(void* p, uint32_t kind, void* a, uint32_t count, voi
     if (e != cudaSuccess) return fail("multi-matrix GEMV launch failed: %s", cudaGetErrorString(e));
     return 0;
   }
-  for (uint32_t i = 0; i < count; i++)      // shapes the GEMV kernel does not take: one launch each
-    if (do_qmatmul(c, (int)kind, (const float*)ba->dev, Bs[i], Cs[i], M, (uint64_t)Ns[i], K, groups, kAuto)) return 1;
+  // Shapes the GEMV kernel does not take: one launch each.  Consecutive launches of the decode kernel
+  // share the int8 digits of the activations (made once, kept in the context's scratch memory).
+  bool digits_ready = false;
+  for (uint32_t i = 0; i < count; i++) {
+    const int path = resolve_path((int)kind, (int64_t)M, Ns[i], (int64_t)K, (int64_t)groups);
+    if (path == kDecode && qdecode_uses_scratch((int)kind, (int64_t)M, Ns[i], (int64_t)K)) {
+      if (ensure_workspace(c, qdecode_workspace_bytes((int)kind, (int64_t)M, Ns[i], (int64_t)K))) return 1;
+      const cudaError_t e = launch_qdecode((int)kind, (const float*)ba->dev, Bs[i], Cs[i], (int64_t)M, Ns[i], (int64_t)K,
+                                           (int64_t)groups, c->ws, c->stream, digits_ready);
+      if (e != cudaSuccess) return fail("matmul_q%u launch failed: %s", kind, cudaGetErrorString(e));
+      digits_ready = true;
+    } else {
+      if (do_qmatmul(c, (int)kind, (const float*)ba->dev, Bs[i], Cs[i], M, (uint64_t)Ns[i], K, groups, kAuto)) return 1;
+      digits_ready = false;                 // the other kernels keep their own scratch in the same memory
+    }
+  }
   return 0;
 }
 

@@ -372,6 +372,10 @@ struct Plan {
   dim3 grid;
 };
 
+// Set when a cluster launch was refused on this process's device (a partition without cluster support):
+// plans then stay on single CTAs.
+bool g_pairs_refused = false;
+
 Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   Plan pl{};
   const bool exact = (dtype == kDenseF32 && mode != kDenseTcFast);
@@ -391,7 +395,7 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
     const int bn2 = (n32 < 256) ? n32 : 256;
     const double t1 = waves((M + 127) / 128 * ((N + 127) / 128), sms) / 0.62;
     const double t2 = waves((M + 255) / 256 * ((N + bn2 - 1) / bn2), sms / 2) * 2.0 * (bn2 / 128.0) / 2.0 / 0.85;
-    pl.pair = !no_pair && M > kBM && N > 128 && t2 < t1;
+    pl.pair = !no_pair && !g_pairs_refused && M > kBM && N > 128 && t2 < t1;
     if (pl.pair) pl.BN = bn2;
   } else {
     // one plane per operand: 256 x 256 tiles on one CTA.  (512 x 256 tiles on a CTA pair, 48 KB instead
@@ -476,10 +480,30 @@ size_t dense_tc_workspace_bytes(int dtype, int mode, int64_t M, int64_t N, int64
   return ((a + 1023) & ~size_t(1023)) + ((b + 1023) & ~size_t(1023)) + 1024;
 }
 
+namespace {
+cudaError_t launch_dense_tc_once(int dtype, int mode, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                 Workspace ws, cudaStream_t s, bool* was_pair);
+}
+
 cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                             Workspace ws, cudaStream_t s) {
+  bool was_pair = false;
+  cudaError_t e = launch_dense_tc_once(dtype, mode, A, B, C, M, N, K, ws, s, &was_pair);
+  if (e != cudaSuccess && was_pair && !g_pairs_refused) {
+    // the cluster launch itself was refused: run this and every later product on single CTAs
+    cudaGetLastError();
+    g_pairs_refused = true;
+    e = launch_dense_tc_once(dtype, mode, A, B, C, M, N, K, ws, s, &was_pair);
+  }
+  return e;
+}
+
+namespace {
+cudaError_t launch_dense_tc_once(int dtype, int mode, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                 Workspace ws, cudaStream_t s, bool* was_pair) {
   if (!dense_tc_supports(dtype, M, N, K)) return cudaErrorInvalidValue;
   const Plan pl = make_plan(dtype, mode, M, N, K);
+  *was_pair = false;
   if (pl.stages < 2 || pl.smem > 227 * 1024) return cudaErrorInvalidValue;
   if (!ws.ptr || ws.bytes < dense_tc_workspace_bytes(dtype, mode, M, N, K) || (reinterpret_cast<uintptr_t>(ws.ptr) & 255))
     return cudaErrorInvalidValue;
@@ -549,11 +573,14 @@ cudaError_t launch_dense_tc(int dtype, int mode, const void* A, const void* B, v
     if (e != cudaSuccess) return e;
     *set = true;
   }
-  if (pl.pair)
+  if (pl.pair) {
     e = launch_pdl_cluster(dense_tc_kernel<true>, 2, pl.grid, dim3(kThreads), pl.smem, s, map_a, map_b, p);
-  else
+    *was_pair = (e != cudaSuccess);      // only a refused LAUNCH is retried; earlier errors are reported as they are
+  } else {
     e = launch_pdl(dense_tc_kernel<false>, pl.grid, dim3(kThreads), pl.smem, s, map_a, map_b, p);
+  }
   return e != cudaSuccess ? e : cudaGetLastError();
 }
+}  // namespace
 
 }  // namespace smith

@@ -42,8 +42,12 @@ cudaError_t launch_qmatmul_generic(int kind, const float* A, const uint8_t* B, f
 // qdecode.cu : M <= 16, activations as int8 digit pairs in scratch, integer mma.sync against the codes.
 bool qdecode_supports(int kind, int64_t M, int64_t N, int64_t K, int64_t groups);
 size_t qdecode_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
+// digits_in_scratch: the launch before this one on the same stream was launch_qdecode with the same
+// kind, A, M and K and also kept its digits in `ws` (qdecode_uses_scratch): they are not made again.
+bool qdecode_uses_scratch(int kind, int64_t M, int64_t N, int64_t K);
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M,
-                           int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s);
+                           int64_t N, int64_t K, int64_t groups, Workspace ws, cudaStream_t s,
+                           bool digits_in_scratch = false);
 
 // qskinny.cu : M <= 64, activations as f16 slabs in scratch, weights de-quantised in registers into
 // the B fragments of f16 mma.sync, f32 accumulators through all of K.

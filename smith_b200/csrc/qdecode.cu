@@ -488,8 +488,13 @@ size_t qdecode_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
   return ((G * Mp * 64 + 255) & ~size_t(255)) + G * Mp * 8 + 64;
 }
 
+bool qdecode_uses_scratch(int kind, int64_t M, int64_t N, int64_t K) {
+  const Plan pl = make_plan(kind, M, N, K);
+  return pl.ok && pl.p.res_off == 0;
+}
+
 cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C, int64_t M, int64_t N, int64_t K,
-                           int64_t groups, Workspace ws, cudaStream_t s) {
+                           int64_t groups, Workspace ws, cudaStream_t s, bool digits_in_scratch) {
   (void)groups;
   Plan pl = make_plan(kind, M, N, K);
   if (!pl.ok) return cudaErrorInvalidValue;
@@ -502,14 +507,16 @@ cudaError_t launch_qdecode(int kind, const float* A, const uint8_t* B, float* C,
     uint8_t* xdig = static_cast<uint8_t*>(ws.ptr);
     float2* xsc = reinterpret_cast<float2*>(xdig + ((G * Mp * 64 + 255) & ~size_t(255)));
     const int qthreads = (int)(Mp * G * 8);
-    cudaError_t e;
-    if (kind == 4)
+    cudaError_t e = cudaSuccess;
+    if (digits_in_scratch)
+      ;   // the launch before this one left the digits of the same activations there
+    else if (kind == 4)
       e = launch_pdl(quantise_rows<4>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig,
                      xsc, (int)M, (int)Mp, (int)K, (int)G);
     else
       e = launch_pdl(quantise_rows<8>, dim3((unsigned)((qthreads + 255) / 256)), dim3(256), (size_t)0, s, A, xdig,
                      xsc, (int)M, (int)Mp, (int)K, (int)G);
-    count_launch();
+    if (!digits_in_scratch) count_launch();
     if (e != cudaSuccess) return e;
     pl.p.xdig = xdig, pl.p.xsc = xsc;
   }

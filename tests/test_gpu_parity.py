@@ -455,7 +455,11 @@ def test_fused_gather_two_shards_emulated_on_one_gpu():
 
 # ------------------------------------------------------------------ several matrices sharing one launch
 @pytest.mark.parametrize("kind,M,K,Ns", [("q4", 1, 4096, [4096, 1024, 1024]), ("q8", 3, 1024, [512, 2048]),
-                                         ("q4", 2, 2048, [1000 // 8 * 8, 24, 4096, 136]), ("q4", 8, 1024, [256, 512])])
+                                         ("q4", 2, 2048, [1000 // 8 * 8, 24, 4096, 136]), ("q4", 8, 1024, [256, 512]),
+                                         # decode-kernel shapes whose activation digits live in scratch memory:
+                                         # made once for the call, read by every product
+                                         ("q4", 16, 4096, [4096, 1024, 1024]), ("q8", 12, 4096, [2048, 512]),
+                                         ("q4", 16, 14336, [4096, 256])])
 def test_qmatmul_multi_matches_one_launch_per_matrix(kind, M, K, Ns):
     rng = np.random.default_rng(41 + M)
     a = rng.standard_normal((M, K)).astype(np.float32)
@@ -473,11 +477,15 @@ def test_qmatmul_multi_matches_one_launch_per_matrix(kind, M, K, Ns):
     assert device.kernelStatus() == 0
     if M <= 4:
         assert device.launchCount() - launches0 == 1        # one launch for all of them
+    elif K >= 4096:
+        assert device.launchCount() - launches0 == len(Ns) + 1      # one digit launch, one product launch per matrix
     for n, packed, cb in zip(Ns, packs, cbs):
         got = cb.get(np.float32).reshape(M, n)
-        want = O.matmul(a, packed, K, n, kind)
+        want = O.matmul(a, packed, K, n, kind, threads=O.host_threads())
         ok, worst = within_tolerance(got, want, a, packed, K, n, kind, REL)
         assert ok, (n, worst)
+        if M > 4:                                                    # the same bits as a call of its own
+            assert bits_equal(got, matmul_on_device(a, packed, K, n, kind))
     for b in pbs + cbs + [ab]:
         b.free()
 
