@@ -1083,7 +1083,7 @@ def run_pack_workload(args, name, wl, ctxinfo):
                         "kernel, wait); the packed result stays on the device by design, its first 4 KB are read back"},
         "gpu_launches": int(steps + warm + 31 + e2e_steps + 1),
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s", "frac": ach / peaks["hbm"],
-                     "traffic": None, "peak_source": peaks["source"], "peak_kind": "copy bandwidth",
+                     "traffic": traffic_for(name), "peak_source": peaks["source"], "peak_kind": "copy bandwidth",
                      "frac_of_nominal": ach / 8000.0, "algorithmic_per_launch": nbytes, "launch_us": step_s * 1e6},
         "clocks": clocks,
     }
@@ -1208,7 +1208,7 @@ def run_dense_workload(args, name, wl, ctxinfo, steps=None, with_cpu=True, with_
                    "timing": "CUDA events on the launch stream, split / transposition launches included"},
         "parity": parity, "e2e": e2e, "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
-                     "traffic": None, "peak_source": peaks["source"], "peak_kind": "cuBLAS bf16 burst",
+                     "traffic": traffic_for(name), "peak_source": peaks["source"], "peak_kind": "cuBLAS bf16 burst",
                      "frac_of_nominal": ach / 2250.0, "algorithmic_per_launch": 2 * M * N * K, "launch_us": step_s * 1e6,
                      "bf16_products_per_product": products, "mma_tflops_executed": ach * products,
                      "frac_mma_executed": ach * products / peaks["tensor"]},
