@@ -46,6 +46,8 @@ const { symbols: lib } = dlopen(LIB_PATH, {
   smith_buffer_make_resident: { returns: T.i32, args: [T.ptr] },
   smith_buffer_evict: { returns: T.i32, args: [T.ptr] },
   smith_qmatmul: { returns: T.i32, args: [T.ptr, T.u32, T.ptr, T.ptr, T.ptr, T.u64, T.u64, T.u64, T.u64, T.u32] },
+  // dense matmul on device-side buffers: (ctx, dtype 0 = f32 / 1 = f16, a, b, c, M, N, K, batch, path)
+  smith_matmul: { returns: T.i32, args: [T.ptr, T.u32, T.ptr, T.ptr, T.ptr, T.u64, T.u64, T.u64, T.u64, T.u32] },
   smith_kernel_status: { returns: T.i32, args: [T.ptr] },
   smith_graph_begin: { returns: T.i32, args: [T.ptr] },
   smith_graph_end: { returns: T.ptr, args: [T.ptr] },
