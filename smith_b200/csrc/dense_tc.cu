@@ -48,7 +48,8 @@ constexpr int kBM = 128, kBK = 64;
 constexpr int kATile = kBM * kBK * 2;       // 16 KB: one plane's 128 x 64 tile
 constexpr int kMaxStages = 8;
 constexpr int kMaxPairs = 6;
-constexpr int kThreads = 6 * 32;
+constexpr int kThreads = 7 * 32;
+constexpr int kSecondIssuerWarp = 6;     // on another warp scheduler than warp 1 (warp % 4 picks the scheduler)
 
 struct Params {
   void* C;
@@ -57,6 +58,7 @@ struct Params {
   int MT, BN;
   int planes;              // 1 or 3 per operand
   int npairs;
+  int issuers;             // threads that issue MMAs: 2 in the single-CTA three-plane form (pairs 0-2 / 3-5), else 1
   uint32_t pair_a, pair_b;  // plane index of pair q in bits [4q, 4q+4)
   int a_plane_rows, b_plane_rows;   // row distance between planes in the stacked tensor maps
   int a_bytes, b_tile, stage_bytes, stages, tmem_cols;
@@ -173,9 +175,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < kMaxStages; s++) {
       mbar_init(smem_u32(&full[s]), PAIR ? 2 : 1);      // pair: one arrival per CTA's producer, on the leader's barrier
-      mbar_init(smem_u32(&empty[s]), 1);
+      mbar_init(smem_u32(&empty[s]), p.issuers);         // one commit per issuing thread
     }
-    mbar_init(smem_u32(acc_ready), 1);
+    mbar_init(smem_u32(acc_ready), p.issuers);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -232,8 +234,15 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
         if (++s == p.stages) s = 0, par ^= 1u;
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (pair: the leader's only)
+  } else if (warp == 1 || (warp == kSecondIssuerWarp && p.issuers == 2)) {
+    // ------------------------------------------------------------ MMA issuer(s) (pair: the leader's only)
+    // The single-CTA three-plane form has TWO issuing threads: 24 MMAs per stage with their address
+    // arithmetic and descriptor packing are more than one thread gets through in the stage's tensor
+    // time.  Thread 0 (warp 1) sends pairs 3-5 (two small products into its own accumulator, then the
+    // leading product), thread 1 sends pairs 0-2 (three small products into a third accumulator); the
+    // epilogue adds the accumulators.
+    const int who = (warp == 1) ? 0 : 1;
+    const int q_lo = (p.issuers == 2) ? (who == 0 ? 3 : 0) : 0, q_hi = (p.issuers == 2) ? (who == 0 ? 6 : 3) : p.npairs;
     if (lane == 0 && rank == 0) {
       int s = 0;
       uint32_t par = 0;
@@ -252,13 +261,13 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
           // small ones share a second: the tensor core truncates every f32 accumulation, so small
           // terms added to the large sum would each cost an ulp of the LARGE sum.
           const uint32_t d_main = tmem_base + (uint32_t)(t * p.BN);
-          const uint32_t d_corr = tmem_base + (uint32_t)((p.MT + t) * p.BN);
-          for (int q = 0; q < p.npairs; q++) {
+          const uint32_t d_corr = tmem_base + (uint32_t)(((1 + who) * p.MT + t) * p.BN);   // this thread's own
+          for (int q = q_lo; q < q_hi; q++) {
             const uint32_t pa = (p.pair_a >> (4 * q)) & 15u, pb = (p.pair_b >> (4 * q)) & 15u;
             const uint32_t a_lo = lo0 + soff + (uint32_t)((int)pa * p.MT + t) * a_tile_step;
             const uint32_t b_lo = lo0 + soff + b_off + pb * b_tile_step;
             const bool lead = (pa | pb) == 0u;
-            const uint32_t first = (kb > 0 || (!lead && q > 0)) ? 1u : 0u;
+            const uint32_t first = (kb > 0 || (!lead && q > q_lo)) ? 1u : 0u;
             if (PAIR) umma_f16_kblock_pair(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, first);
             else umma_f16_kblock(lead ? d_main : d_corr, a_lo, b_lo, desc_hi, p.idesc, first);
           }
@@ -281,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
         }
       }
     }
-  } else {
+  } else if (warp >= 2 && warp <= 5) {
     // ------------------------------------------------------------ epilogue (warps 2-5)
     const bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_ready), 0, abort_flag, p.status));
     tc_fence_after();
@@ -301,9 +310,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * p.BN + c), r);
           tmem_ld_wait();
-          if (p.npairs > 1) {
+          for (int extra = 1; extra <= (p.npairs > 1 ? p.issuers : 0); extra++) {   // the small products' accumulator(s)
             uint32_t r2[32];
-            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((p.MT + t) * p.BN + c), r2);
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((extra * p.MT + t) * p.BN + c), r2);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
@@ -365,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const __grid_cons
 // ---------------------------------------------------------------- host side
 struct Plan {
   bool pair;
-  int MT, BN, planes, npairs, stages, tmem_cols;
+  int MT, BN, planes, npairs, issuers, stages, tmem_cols;
   int a_bytes, b_tile, stage_bytes;
   int64_t Mp, Np, Kp;
   size_t smem;
@@ -388,12 +397,13 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   if (exact) {
     // One CTA: 128 x 128 tiles (six 16 KB plane tiles per stage, two stages).  A CTA pair: 256 x 256
     // tiles, each CTA staging 48 KB of A and its 48 KB half of B per stage; the MMA thread then issues
-    // the same 24 instructions per stage for twice the tensor time, and that thread's instruction
-    // stream is what bounds the single-CTA form (measured: 62 % of the tensor pipe against 83 %).
+    // the same 24 instructions per stage for twice the tensor time and each SM receives half the B
+    // bytes per MMA (measured: 84 % of the tensor pipe busy against 62 to 66 % for single CTAs, whose
+    // stages need 61 bytes per clock from L2 at the full MMA rate).
     // The pair's tile is four times as large, so it is taken where the waves it leaves cost less.
     pl.MT = 1, pl.BN = (n16 < 128) ? n16 : 128;
     const int bn2 = (n32 < 256) ? n32 : 256;
-    const double t1 = waves((M + 127) / 128 * ((N + 127) / 128), sms) / 0.62;
+    const double t1 = waves((M + 127) / 128 * ((N + 127) / 128), sms) / 0.66;
     const double t2 = waves((M + 255) / 256 * ((N + bn2 - 1) / bn2), sms / 2) * 2.0 * (bn2 / 128.0) / 2.0 / 0.85;
     pl.pair = !no_pair && !g_pairs_refused && M > kBM && N > 128 && t2 < t1;
     if (pl.pair) pl.BN = bn2;
@@ -412,7 +422,8 @@ Plan make_plan(int dtype, int mode, int64_t M, int64_t N, int64_t K) {
   if (stages > kMaxStages) stages = kMaxStages;
   pl.stages = stages;
   int cols = 32;                                 // the epilogue reads whole 32-column chunks
-  const int accs = pl.MT * (exact ? 2 : 1);      // three planes: a second accumulator for the small products
+  pl.issuers = (exact && !pl.pair) ? 2 : 1;
+  const int accs = pl.MT * (exact ? 1 + pl.issuers : 1);   // three planes: one more accumulator per issuing thread for the small products
   while (cols < (accs - 1) * pl.BN + (pl.BN + 31) / 32 * 32) cols <<= 1;
   pl.tmem_cols = cols;
   pl.smem = 1024 + (size_t)stages * pl.stage_bytes;
@@ -547,7 +558,7 @@ cudaError_t launch_dense_tc_once(int dtype, int mode, const void* A, const void*
 
   Params p{};
   p.C = C, p.M = (int)M, p.N = (int)N, p.K = (int)K, p.out_f16 = f16 ? 1 : 0;
-  p.MT = pl.MT, p.BN = pl.BN, p.planes = pl.planes, p.npairs = pl.npairs;
+  p.MT = pl.MT, p.BN = pl.BN, p.planes = pl.planes, p.npairs = pl.npairs, p.issuers = pl.issuers;
   // the five small products (smallest first), then the leading one
   static const int pa[kMaxPairs] = {1, 2, 0, 1, 0, 0}, pb[kMaxPairs] = {1, 0, 2, 0, 1, 0};
   p.pair_a = p.pair_b = 0;
