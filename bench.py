@@ -703,13 +703,13 @@ def parity_window(D, O, kind, M, K, Nl, a_dev, pack, read_out, c0=None, width=48
     return float((err / np.maximum(bound, 1e-300)).max())
 
 
+SETTLE_S = float(os.environ.get("SMITH_BENCH_SETTLE_S", "0.06"))
+
+
 def settle_steps(step_s, world, torch, dist):
-    """How many untimed steps make about 60 ms of load just before the timed region, so that the
-    clock samples (one per 20 ms) see load even when the timed region itself is a few milliseconds.
-    (Longer would not measure the same thing: after some tenths of a second of streaming at full
-    rate the part runs into its power cap and the SM clock drops by a tenth; the HBM peak this is
-    compared with is a burst figure too.)"""
-    n = int(min(20000, max(0, 0.06 / max(step_s, 1e-7))))
+    """How many untimed steps make SETTLE_S of load just before the timed region, so that the
+    clock samples (one per 20 ms) see load even when the timed region itself is a few milliseconds."""
+    n = int(min(200000, max(0, SETTLE_S / max(step_s, 1e-7))))
     if world > 1:
         t = torch.tensor([n], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
