@@ -136,6 +136,86 @@ __device__ __forceinline__ void block_dot(const uint8_t* __restrict__ blk, uint3
   }
 }
 
+// ---- the same block product on 32-bit shared-memory addresses (explicit ld.shared)
+__device__ __forceinline__ uint2 lds_b64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_b128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_b32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_b16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+
+// blk: shared address of the packed block; xd: shared address of the group's four digit words of row 0
+// (row m lies m * G * 64 bytes further); xs: shared address of its {scale, sum} pair (row m: + m * G * 8).
+template <int KIND, int MR>
+__device__ __forceinline__ void block_dot_s(uint32_t blk, uint32_t xd, uint32_t xs, int G, float (&acc)[MR]) {
+  if (KIND == 4) {
+    const uint2 n0 = lds_b64(blk), n1 = lds_b64(blk + 8), szb = lds_b64(blk + 16);
+    const float sc = __uint_as_float(szb.x), zp = __uint_as_float(szb.y);
+    const uint32_t w[4] = {n0.x, n0.y, n1.x, n1.y};
+    uint32_t be[4], bo[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      be[i] = w[i] & 0x0F0F0F0Fu;   // codes of even k
+      bo[i] = w[i] & 0xF0F0F0F0u;   // 16 * codes of odd k
+    }
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      int eh = 0, el = 0, oh = 0, ol = 0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint4 d = lds_b128(xd + (uint32_t)(m * G * 64 + i * 16));
+        eh = dp4a_su((int)d.x, be[i], eh);
+        el = dp4a_su((int)d.y, be[i], el);
+        oh = dp4a_su((int)d.z, bo[i], oh);
+        ol = dp4a_su((int)d.w, bo[i], ol);
+      }
+      const int dot = (eh * 128 + el) + ((oh * 128 + ol) >> 4);  // odd part is an exact multiple of 16
+      const uint2 sb = lds_b64(xs + (uint32_t)(m * G * 8));
+      acc[m] = fmaf(sc * __uint_as_float(sb.x), fmaf(-zp, __uint_as_float(sb.y), (float)dot), acc[m]);
+    }
+  } else {
+    // 34-byte blocks are only 2-byte aligned: read the aligned words around the 32 code bytes and shift
+    const uint32_t off = blk + 2;
+    const uint32_t sh = (off & 3u) * 8;
+    const uint32_t al = off & ~3u;
+    uint32_t raw[9];
+#pragma unroll
+    for (int i = 0; i < 9; i++) raw[i] = lds_b32(al + 4u * i);
+    uint32_t cw[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) cw[i] = __funnelshift_r(raw[i], raw[i + 1], sh);
+    const float scale = __half2float(__ushort_as_half((unsigned short)lds_b16(blk)));
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      int dh = 0, dl = 0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint4 d = lds_b128(xd + (uint32_t)(m * G * 64 + i * 16));
+        dh = dp4a_ss((int)d.x, (int)cw[2 * i], dh);
+        dl = dp4a_ss((int)d.y, (int)cw[2 * i], dl);
+        dh = dp4a_ss((int)d.z, (int)cw[2 * i + 1], dh);
+        dl = dp4a_ss((int)d.w, (int)cw[2 * i + 1], dl);
+      }
+      const uint2 sb = lds_b64(xs + (uint32_t)(m * G * 8));
+      acc[m] = fmaf(scale * __uint_as_float(sb.x), (float)(dh * 128 + dl), acc[m]);
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_box_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
                                            uint64_t policy) {
   asm volatile(

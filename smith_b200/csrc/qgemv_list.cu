@@ -212,29 +212,29 @@ template <int KIND, int MR>
 __device__ __forceinline__ void consume_stage(const uint8_t* stage, int st, int stage_rows, int rpp, int G, int phases,
                                               int phase, uint32_t base, uint32_t pitch, const uint4* xdig,
                                               const float2* xsc, float (&acc)[MR]) {
+  // 32-bit shared-memory addresses throughout: a per-thread base plus strides
   const int g0 = st * stage_rows + phase;
+  const uint32_t step = (uint32_t)phases * pitch;
+  uint32_t blk = smem_u32(stage) + base + (uint32_t)phase * pitch;
+  uint32_t xd = smem_u32(xdig) + (uint32_t)g0 * 64u, xs = smem_u32(xsc) + (uint32_t)g0 * 8u;
+  const uint32_t xd_step = (uint32_t)phases * 64u, xs_step = (uint32_t)phases * 8u;
   if (st * stage_rows + stage_rows <= G) {
     int rr = 0;
     for (; rr + 4 <= rpp; rr += 4) {
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        const uint32_t off = base + (uint32_t)(phase + (rr + u) * phases) * pitch;
-        const int g = g0 + (rr + u) * phases;
-        block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
+        block_dot_s<KIND, MR>(blk, xd, xs, G, acc);
+        blk += step, xd += xd_step, xs += xs_step;
       }
     }
     for (; rr < rpp; rr++) {
-      const uint32_t off = base + (uint32_t)(phase + rr * phases) * pitch;
-      const int g = g0 + rr * phases;
-      block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
+      block_dot_s<KIND, MR>(blk, xd, xs, G, acc);
+      blk += step, xd += xd_step, xs += xs_step;
     }
   } else {
     for (int rr = 0; rr < rpp; rr++) {
-      const int g = g0 + rr * phases;
-      if (g < G) {
-        const uint32_t off = base + (uint32_t)(phase + rr * phases) * pitch;
-        block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, G, acc);
-      }
+      if (g0 + rr * phases < G) block_dot_s<KIND, MR>(blk, xd, xs, G, acc);
+      blk += step, xd += xd_step, xs += xs_step;
     }
   }
 }
