@@ -344,24 +344,23 @@ __global__ void __launch_bounds__(kMaxConsumerThreads + 32, WIDE ? 1 : kCtasPerS
   for (int st = 0; st < nst && ok; st++, slot = (slot + 1 == p.stages) ? 0 : slot + 1, ring_par ^= (slot == 0)) {
     ok = mbar_wait(smem_u32(&full[slot]), ring_par, abort_flag, p.status);
     if (ok && active) {
-      const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+      // 32-bit shared-memory addresses throughout: a per-thread base plus strides
       const int g0 = st * p.stage_rows + phase;
+      const uint32_t step = (uint32_t)p.phases * (uint32_t)p.row_pitch;
+      uint32_t blk = smem_u32(ring) + (uint32_t)slot * (uint32_t)p.stage_bytes + (uint32_t)phase * (uint32_t)p.row_pitch +
+                     (uint32_t)col * BB;
+      uint32_t xd = smem_u32(xdig) + (uint32_t)g0 * 64u, xs = smem_u32(xsc) + (uint32_t)g0 * 8u;
+      const uint32_t xd_step = (uint32_t)p.phases * 64u, xs_step = (uint32_t)p.phases * 8u;
       if (st * p.stage_rows + p.stage_rows <= p.G) {
 #pragma unroll
         for (int rr = 0; rr < RPP; rr++) {
-          const int row = phase + rr * p.phases;
-          const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)col * BB;
-          const int g = g0 + rr * p.phases;
-          block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, p.G, acc);
+          block_dot_s<KIND, MR>(blk, xd, xs, p.G, acc);
+          blk += step, xd += xd_step, xs += xs_step;
         }
       } else {
         for (int rr = 0; rr < RPP; rr++) {
-          const int row = phase + rr * p.phases;
-          const int g = g0 + rr * p.phases;
-          if (g < p.G) {
-            const uint32_t off = (uint32_t)row * p.row_pitch + (uint32_t)col * BB;
-            block_dot<KIND, MR>(stage + off, off, xdig + (size_t)g * 4, xsc + g, p.G, acc);
-          }
+          if (g0 + rr * p.phases < p.G) block_dot_s<KIND, MR>(blk, xd, xs, p.G, acc);
+          blk += step, xd += xd_step, xs += xs_step;
         }
       }
     }
