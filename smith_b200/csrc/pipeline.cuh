@@ -35,26 +35,42 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may stay suspended that long, and is
+// resumed as soon as the phase completes.  Without the hint a waiting thread comes back after a short
+// system-chosen time and polls again, and the polls of a CTA's waiting warps take issue slots (and
+// power) from the warps that work: a quarter of all instructions of the list kernel were such polls.
+__device__ __forceinline__ bool mbar_try_suspended(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t kSuspendNs = 20000;   // per try; the limit below is checked after each
+
 // Bounded wait.  Returns false if the limit ran out or another thread of the
-// CTA gave up.  The limit is counted on the SM's cycle counter (cheap to read,
-// unlike the global nanosecond timer) and only consulted every 256 failed polls;
-// each poll itself suspends the thread for a hardware-chosen time.
+// CTA gave up.  The limit is counted on the SM's cycle counter, consulted after
+// every suspended try.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status) {
+  // short waits (a stage that is about to land) keep the plain poll and its wake-up latency ...
 #pragma unroll 1
   for (int spin = 0; spin < 64; spin++)
     if (mbar_try(bar, parity)) return true;
+  // ... long ones (an epilogue warp during the main loop, a producer behind a full ring) go to sleep
   const long long t0 = clock64();
 #pragma unroll 1
-  for (int spin = 0;; spin++) {
-    if (mbar_try(bar, parity)) return true;
-    if ((spin & 255) == 255) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *abort_flag = 1;
-        atomicExch(status, 1);
-        return false;
-      }
+  for (;;) {
+    if (mbar_try_suspended(bar, parity, kSuspendNs)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      atomicExch(status, 1);
+      return false;
     }
   }
 }
